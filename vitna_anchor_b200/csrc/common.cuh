@@ -1,0 +1,70 @@
+// Shared device helpers for the sm_100a kernels of this engine.
+//
+// Storage types are float and __nv_bfloat16; arithmetic is always float32.
+// A bfloat16 value is widened exactly (its 16 bits are the high half of a
+// float32), as the reference widens stored weights (engine/src/ops.c:25-30).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define VK_API extern "C" __attribute__((visibility("default")))
+
+// Status codes returned by every launcher.  0 is success; positive values are
+// cudaError_t of the launch; negative values are refusals decided on the host
+// before anything was launched.
+#define VK_OK 0
+#define VK_BAD_SHAPE (-1)      // a size this kernel does not take
+#define VK_BAD_ALIGNMENT (-2)  // a pointer or stride that is not aligned as needed
+#define VK_TOO_LARGE (-3)      // beyond a stated maximum
+
+namespace vk {
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// `scratch` holds at least 32 floats and may be reused after the call returns.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : 0.0f;
+    r = warp_sum(r);
+    return r;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : -INFINITY;
+    r = warp_max(r);
+    return r;
+}
+
+inline int launch_status() { return (int)cudaGetLastError(); }
+
+}  // namespace vk

@@ -1,0 +1,213 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+A step takes any mixture of prompt portions and single decoded tokens, cut
+anywhere, runs exactly the tokens it is given as one batch, and returns
+float32 logits at the places asked for.  Before anything is launched it
+checks the tokens and the room, and holds pages for the new positions; if the
+pools cannot give them it raises OutOfPages and nothing has changed.  A
+request's length advances only when the step has been issued in full.
+
+The reference has three calls for this (one token, engine/src/model.c:866;
+a run of one sequence's tokens, model.c:982-1040; one token of each of
+several sequences, model.c:1149-1172) and never mixes a prompt piece with
+decode rows in one pass (engine/src/api.c:2216-2225).  Here they are one call.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, KVSpec
+from ..cache.pages import OutOfPages, UNMAPPED
+from ..models.decoder import DecoderModel
+from ..parts.base import GroupMeta, StepContext, Workspace
+
+
+class StepError(RuntimeError):
+    """The step was refused before anything ran (bad token, no room, unknown request)."""
+
+
+class StepFailed(RuntimeError):
+    """The step failed as a test asked it to; nothing ran and nothing changed
+    (cf. vitna_llama_fail_step_once, engine/src/model.c:471-493)."""
+
+
+@dataclass
+class StepEntry:
+    request_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()      # places among `tokens` whose logits are returned
+
+
+class _Staging:
+    """A pinned host buffer and the event that tells when its last copy to the device is done."""
+
+    def __init__(self, n: int, pinned: bool):
+        self.host = torch.empty(n, dtype=torch.int32, pin_memory=pinned)
+        self.np = self.host.numpy()
+        self.event: Optional[torch.cuda.Event] = None
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, *, page_size: int = 16, num_pages: Optional[int] = None,
+                 max_requests: int = 64, max_batch_tokens: int = 2048, max_model_len: Optional[int] = None,
+                 device="cuda", cache_tokens: Optional[int] = None):
+        self.model = model
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise StepError("the engine runs on a CUDA device only; there is no CPU path")
+        self.max_model_len = min(max_model_len or model.max_positions, model.max_positions)
+        self.max_batch_tokens = max_batch_tokens
+        self.page_size = page_size
+        if num_pages is None:
+            tokens = cache_tokens if cache_tokens is not None else self.max_model_len * max_requests
+            num_pages = -(-tokens // page_size)
+        self.cache = CacheManager(model.cache_specs(), page_size=page_size, num_pages=num_pages, max_requests=max_requests,
+                                  dtype=model.dtype, device=self.device)
+        self.max_blocks = -(-self.max_model_len // page_size)
+        self.workspace = Workspace(self.device, max_batch_tokens)
+        self.max_segments = max_requests
+        n_groups = len(self.cache.groups)
+        self._meta_len = (3 * max_batch_tokens + 3 * self.max_segments + 1 + max_batch_tokens
+                          + n_groups * (max_batch_tokens + self.max_segments * self.max_blocks))
+        self._staging = [_Staging(self._meta_len, True) for _ in range(4)]
+        self._stage_i = 0
+        self._meta_dev = torch.zeros(self._meta_len, dtype=torch.int32, device=self.device)
+        self._fail_at: Optional[int] = None
+        env = os.environ.get("VITNA_TEST_FAIL_STEP")
+        if env is not None:
+            self._fail_at = int(env) if env.strip() else 0
+        self.steps_run = 0
+
+    # -- requests ---------------------------------------------------------------------------
+    def open(self, request_id: Hashable) -> int:
+        return self.cache.open(request_id)
+
+    def close(self, request_id: Hashable) -> None:
+        self.cache.close(request_id)
+
+    def length(self, request_id: Hashable) -> int:
+        return self.cache.length(request_id)
+
+    def fail_step_once(self, position: int = 0) -> None:
+        """The next step that would compute `position` of any request raises StepFailed instead."""
+        self._fail_at = position
+
+    # -- the step ---------------------------------------------------------------------------
+    def _validate(self, entries: Sequence[StepEntry]) -> Tuple[int, int]:
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        if len(entries) > self.max_segments:
+            raise StepError(f"{len(entries)} entries in a step; the limit is {self.max_segments}")
+        seen = set()
+        T = R = 0
+        V = self.model.vocab_size
+        for e in entries:
+            if e.request_id in seen:
+                raise StepError(f"request {e.request_id!r} is in the step twice")
+            seen.add(e.request_id)
+            if not self.cache.is_open(e.request_id):
+                raise StepError(f"request {e.request_id!r} is not open")
+            n = len(e.tokens)
+            if n < 1:
+                raise StepError(f"request {e.request_id!r} brings no token")
+            for t in e.tokens:
+                if not (0 <= int(t) < V):
+                    raise StepError(f"token {t} of request {e.request_id!r} is outside the vocabulary of {V}")
+            for w in e.want:
+                if not (0 <= int(w) < n):
+                    raise StepError(f"request {e.request_id!r} wants place {w} of {n} tokens")
+            if self.cache.length(e.request_id) + n > self.max_model_len:
+                raise StepError(f"request {e.request_id!r} would pass the context of {self.max_model_len} positions")
+            T += n
+            R += len(e.want)
+        if T > self.max_batch_tokens:
+            raise StepError(f"{T} tokens in a step; the limit is {self.max_batch_tokens}")
+        return T, R
+
+    def _build_context(self, entries: Sequence[StepEntry], T: int, R: int,
+                       fixed_blocks: Optional[int] = None) -> Tuple[StepContext, Optional[torch.Tensor]]:
+        S = len(entries)
+        ps = self.page_size
+        tables = self.cache.tables
+        lens = [len(e.tokens) for e in entries]
+        first = [tables.get(e.request_id).length for e in entries]
+        slots = [tables.get(e.request_id).slot for e in entries]
+        context = [f + n for f, n in zip(first, lens)]
+        maxb = fixed_blocks or max(1, max(-(-c // ps) for c in context))
+
+        st = self._staging[self._stage_i]
+        self._stage_i = (self._stage_i + 1) % len(self._staging)
+        if st.event is not None:
+            st.event.synchronize()
+        buf = st.np
+        off = 0
+
+        def put(values, count) -> slice:
+            nonlocal off
+            sl = slice(off, off + count)
+            buf[sl] = values
+            off += count
+            return sl
+
+        seg_starts = np.zeros(S + 1, dtype=np.int32)
+        np.cumsum(lens, out=seg_starts[1:])
+        s_tokens = put(np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries]), T)
+        s_pos = put(np.concatenate([np.arange(f, f + n, dtype=np.int32) for f, n in zip(first, lens)]), T)
+        s_seg = put(np.repeat(np.arange(S, dtype=np.int32), lens), T)
+        s_starts = put(seg_starts, S + 1)
+        s_ctx = put(np.asarray(context, dtype=np.int32), S)
+        s_slots = put(np.asarray(slots, dtype=np.int32), S)
+        rows = [int(seg_starts[i]) + int(w) for i, e in enumerate(entries) for w in e.want]
+        s_rows = put(np.asarray(rows, dtype=np.int32), R) if R else slice(off, off)
+        group_slices = []
+        for g in range(len(self.cache.groups)):
+            bt = np.zeros((S, maxb), dtype=np.int32)
+            sm = np.empty(T, dtype=np.int32)
+            for i, e in enumerate(entries):
+                blocks = tables.get(e.request_id).tables[g].blocks
+                row = np.asarray(blocks[:maxb], dtype=np.int32)
+                pos = np.arange(first[i], first[i] + lens[i])
+                sm[seg_starts[i]:seg_starts[i + 1]] = row[pos // ps] * ps + pos % ps
+                row = np.where(row == UNMAPPED, 0, row)      # pages behind a window are never read
+                bt[i, :len(row)] = row
+            group_slices.append((put(sm, T), put(bt.reshape(-1), S * maxb)))
+
+        dev = self._meta_dev
+        dev[:off].copy_(st.host[:off], non_blocking=True)
+        st.event = torch.cuda.Event()
+        st.event.record()
+
+        groups = [GroupMeta(dev[a], dev[b].view(S, maxb), maxb) for a, b in group_slices]
+        ctx = StepContext(
+            num_tokens=T, num_segments=S, dtype=self.model.dtype, tokens=dev[s_tokens], positions=dev[s_pos],
+            token_seg=dev[s_seg], seg_starts=dev[s_starts], seg_context=dev[s_ctx], seg_slots=dev[s_slots], groups=groups,
+            caches=self.cache.views, workspace=self.workspace, host_seg_lens=lens, host_seg_first_pos=first,
+            host_seg_slots=slots, max_seg_len=max(lens), max_context=max(context), decode_only=all(n == 1 for n in lens))
+        return ctx, (dev[s_rows] if R else None)
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run the batch.  Returns float32 logits [wanted places, vocab] on the device, in the order of the
+        entries and of each entry's `want`, or None when nothing is wanted."""
+        T, R = self._validate(entries)
+        plan = [(e.request_id, len(e.tokens)) for e in entries]
+        if self._fail_at is not None:
+            for e in entries:
+                lo = self.cache.length(e.request_id)
+                if lo <= self._fail_at < lo + len(e.tokens):
+                    self._fail_at = None
+                    raise StepFailed(f"the step that computes position {lo} failed as the test asked")
+        self.cache.reserve_step(plan)         # OutOfPages leaves everything as it was
+        try:
+            ctx, rows = self._build_context(entries, T, R)
+            logits = self.model.forward(ctx, rows)
+        except BaseException:
+            self.cache.rollback_step(plan)
+            raise
+        self.cache.commit_step(plan)
+        self.steps_run += 1
+        return logits

@@ -1,0 +1,222 @@
+"""Python faces of the engine's CUDA kernels.
+
+The kernels live in one shared library (csrc/, built by ops.build) with a C
+interface; this module checks tensors (device, dtype, contiguity, shapes) and
+passes raw pointers and the current CUDA stream.  There is no CPU fallback and
+no library stand-in: if the library cannot be built or loaded, or a tensor is
+not on a CUDA device, the call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+_lib = None
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded kernel library; built at the first call if need be."""
+    global _lib
+    if _lib is None:
+        path = _build.library_path(build=True)
+        try:
+            _lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"the kernel library {path} could not be loaded: {e}") from None
+    return _lib
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    fn = lib().vk_error_string
+    fn.restype = ctypes.c_char_p
+    text = fn(status).decode()
+    if status < 0:
+        raise KernelError(f"{what}: refused, {text}")
+    raise KernelError(f"{what}: CUDA error {status}: {text}")
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"dtype {t.dtype} is not one of float32, bfloat16")
+
+
+def _p(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _req(t: torch.Tensor, name: str, dtype=None, dims: Optional[int] = None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} is not on a CUDA device; the engine has no CPU path")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} is not contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} is {t.dtype}, expected {dtype}")
+    if dims is not None and t.dim() != dims:
+        raise KernelError(f"{name} has {t.dim()} dimensions, expected {dims}")
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+# ---------------------------------------------------------------------------
+
+def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, :] = float32(table[ids[t], :]); table [V, H] (float32 or bfloat16), ids int32 [T], out float32 [T, H]."""
+    _req(table, "table", dims=2); _req(ids, "ids", torch.int32, 1); _req(out, "out", torch.float32, 2)
+    if out.shape != (ids.shape[0], table.shape[1]):
+        raise KernelError("embed_rows: out is not [tokens, hidden]")
+    _check(lib().vk_embed_rows(_p(table), _p(ids), _p(out), ids.shape[0], table.shape[1], table.shape[0], _dt(table),
+                               _stream()), "embed_rows")
+    return out
+
+
+def rmsnorm_rows(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
+                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r, :] = rmsnorm(x[rows[r], :]) * w; x float32 [T, n], w float32 [n], out [R, n] float32 or bfloat16."""
+    _req(x, "x", torch.float32, 2); _req(w, "w", torch.float32, 1); _req(out, "out", dims=2)
+    n = x.shape[1]
+    if w.shape[0] != n or out.shape[1] != n:
+        raise KernelError("rmsnorm_rows: widths differ")
+    if rows is not None:
+        _req(rows, "rows", torch.int32, 1)
+        if rows.shape[0] != out.shape[0]:
+            raise KernelError("rmsnorm_rows: rows and out differ in length")
+    elif out.shape[0] != x.shape[0]:
+        raise KernelError("rmsnorm_rows: out and x differ in rows")
+    _check(lib().vk_rmsnorm_rows(_p(x), _p(w), _p(rows), _p(out), out.shape[0], n, ctypes.c_float(eps), _dt(out),
+                                 _stream()), "rmsnorm_rows")
+    return out
+
+
+LINEAR_SAME, LINEAR_F32, LINEAR_ACC_F32 = 0, 1, 2
+
+
+def linear_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, few_rows: int = 8) -> torch.Tensor:
+    """out = x @ w.T on CUDA cores in float32 arithmetic.  x [M, K] (rows may be strided), w [N, K],
+    out [M, N]: mode 0 stores in x's dtype, 1 stores float32, 2 adds into a float32 out."""
+    if not x.is_cuda or x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("linear: x must be a CUDA matrix with unit column stride")
+    _req(w, "w", x.dtype, 2); _req(out, "out", x.dtype if mode == LINEAR_SAME else torch.float32, 2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"linear: shapes x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
+    ldx = x.stride(0) if M > 1 else max(K, x.stride(0))
+    _check(lib().vk_linear_simt(_p(x), _p(w), _p(out), M, N, K, ldx, _dt(x), mode, few_rows, _stream()), "linear_simt")
+    return out
+
+
+def rope_store(qkv: torch.Tensor, positions: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+               slot_mapping: Optional[torch.Tensor], q_out: torch.Tensor, cache_layer: Optional[torch.Tensor],
+               nh: int, nkv: int, hd: int, rot: int, page_size: int) -> torch.Tensor:
+    """Rotate q and k (half-split pairs within the first `rot` dimensions), write q to q_out and k, v into
+    the layer's pages at slot_mapping (page * page_size + offset, or -1 for no write)."""
+    _req(qkv, "qkv", dims=2); _req(positions, "positions", torch.int32, 1); _req(q_out, "q_out", qkv.dtype, 2)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (nh + 2 * nkv) * hd or q_out.shape != (T, nh * hd) or positions.shape[0] != T:
+        raise KernelError("rope_store: shapes do not fit the head counts")
+    if rot > 0:
+        _req(cos, "cos", torch.float32, 2); _req(sin, "sin", torch.float32, 2)
+        if cos.shape[1] != rot // 2 or sin.shape != cos.shape:
+            raise KernelError("rope_store: tables are not [positions, rot/2]")
+    if cache_layer is not None:
+        _req(cache_layer, "cache_layer", qkv.dtype)
+        _req(slot_mapping, "slot_mapping", torch.int32, 1)
+        if tuple(cache_layer.shape[1:]) != (2, nkv, page_size, hd) or slot_mapping.shape[0] != T:
+            raise KernelError("rope_store: the cache layer is not [pages, 2, nkv, page_size, hd]")
+    _check(lib().vk_rope_store(_p(qkv), _p(positions), _p(cos if rot > 0 else None), _p(sin if rot > 0 else None),
+                               _p(slot_mapping if cache_layer is not None else None), _p(q_out), _p(cache_layer), T, nh,
+                               nkv, hd, rot, page_size, _dt(qkv), _stream()), "rope_store")
+    return q_out
+
+
+def attention_rows(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: torch.Tensor, token_seg: torch.Tensor,
+                   positions: torch.Tensor, out: torch.Tensor, nh: int, nkv: int, hd: int, scale: float,
+                   window: int = 0) -> torch.Tensor:
+    """Causal attention of every token over its request's pages (any sizes, float32 arithmetic)."""
+    _req(q, "q", dims=2); _req(cache_layer, "cache_layer", q.dtype, 5); _req(block_tables, "block_tables", torch.int32, 2)
+    _req(token_seg, "token_seg", torch.int32, 1); _req(positions, "positions", torch.int32, 1); _req(out, "out", q.dtype, 2)
+    T = q.shape[0]
+    page_size = cache_layer.shape[3]
+    if q.shape[1] != nh * hd or out.shape != q.shape or tuple(cache_layer.shape[1:]) != (2, nkv, page_size, hd):
+        raise KernelError("attention_rows: shapes do not fit the head counts")
+    if token_seg.shape[0] != T or positions.shape[0] != T:
+        raise KernelError("attention_rows: per-token arrays differ in length")
+    _check(lib().vk_attention_rows(_p(q), _p(cache_layer), _p(block_tables), _p(token_seg), _p(positions), _p(out), T, nh,
+                                   nkv, hd, page_size, block_tables.shape[1], ctypes.c_float(scale), window, _dt(q),
+                                   _stream()), "attention_rows")
+    return out
+
+
+def silu_mul(gu: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = silu(gu[:, :I]) * gu[:, I:]."""
+    _req(gu, "gu", dims=2); _req(out, "out", gu.dtype, 2)
+    T, two_i = gu.shape
+    if two_i % 2 or out.shape != (T, two_i // 2):
+        raise KernelError("silu_mul: out is not [tokens, width/2]")
+    _check(lib().vk_silu_mul(_p(gu), _p(out), T, two_i // 2, _dt(gu), _stream()), "silu_mul")
+    return out
+
+
+def add_inplace(y: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """y (float32) += x (float32 or bfloat16)."""
+    _req(y, "y", torch.float32); _req(x, "x")
+    if y.numel() != x.numel():
+        raise KernelError("add_inplace: sizes differ")
+    _check(lib().vk_add_inplace(_p(y), _p(x), ctypes.c_size_t(y.numel()), _dt(x), _stream()), "add_inplace")
+    return y
+
+
+def argmax_rows(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r] = the lowest id among the maxima of logits[r, :]."""
+    _req(logits, "logits", torch.float32, 2); _req(out, "out", torch.int32, 1)
+    if out.shape[0] != logits.shape[0]:
+        raise KernelError("argmax_rows: out and logits differ in rows")
+    _check(lib().vk_argmax_rows(_p(logits), _p(out), logits.shape[0], logits.shape[1], _stream()), "argmax_rows")
+    return out
+
+
+def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+                uniform: torch.Tensor, probs_scratch: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """One token per row: greedy where temperature <= 0, else temperature / top-k / top-p with the row's uniform."""
+    _req(logits, "logits", torch.float32, 2)
+    R, V = logits.shape
+    _req(temperature, "temperature", torch.float32, 1); _req(top_k, "top_k", torch.int32, 1)
+    _req(top_p, "top_p", torch.float32, 1); _req(uniform, "uniform", torch.float64, 1)
+    _req(probs_scratch, "probs_scratch", torch.float32); _req(out, "out", torch.int32, 1)
+    if min(temperature.shape[0], top_k.shape[0], top_p.shape[0], uniform.shape[0], out.shape[0]) < R:
+        raise KernelError("sample_rows: a per-row array is shorter than the rows")
+    if probs_scratch.numel() < R * V:
+        raise KernelError("sample_rows: the scratch is smaller than [rows, vocab]")
+    _check(lib().vk_sample_rows(_p(logits), _p(temperature), _p(top_k), _p(top_p), _p(uniform), _p(probs_scratch), _p(out),
+                                R, V, _stream()), "sample_rows")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# Dispatch: which kernel a part's call runs, by dtype and size.
+# ---------------------------------------------------------------------------
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> torch.Tensor:
+    """out (=, or += in mode LINEAR_ACC_F32) x @ w.T.  float32 runs on CUDA cores in float32 arithmetic
+    (no reduced-precision matrix mode); bfloat16 runs the tensor-core kernel where it takes the sizes."""
+    return linear_simt(x, w, out, mode)
+
+
+def attention(q: torch.Tensor, pages: torch.Tensor, meta, ctx, out: torch.Tensor, nh: int, nkv: int, hd: int,
+              scale: float, window: int = 0) -> torch.Tensor:
+    """Causal attention of a mixed batch over the paged cache; `meta` is the page group's GroupMeta."""
+    return attention_rows(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, nh, nkv, hd, scale, window)

@@ -1,0 +1,137 @@
+"""Interfaces of the parts a decoder is put together from, and what a part sees of a step.
+
+A part knows its own sizes and constants and nothing about the model it is in.
+The residual stream is float32 [tokens, hidden]; a norm reads it and writes the
+compute dtype (float32 or bfloat16); a mixer or feed-forward reads normed
+activations and ADDS its result into the residual stream, so that a kernel may
+do the sum in its epilogue (float32 either way).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheSpec, LayerCacheView
+
+
+class Workspace:
+    """Named device buffers, made once at their largest size and handed out as views.
+
+    Addresses never change after the first use, which is what replaying a
+    captured CUDA graph needs."""
+
+    def __init__(self, device: torch.device, max_tokens: int):
+        self.device = device
+        self.max_tokens = max_tokens
+        self._bufs: Dict[str, torch.Tensor] = {}
+
+    def rows(self, name: str, rows: int, width: int, dtype: torch.dtype) -> torch.Tensor:
+        """A [rows, width] view of the buffer `name` (rows <= max_tokens)."""
+        if rows > self.max_tokens:
+            raise ValueError(f"workspace {name}: {rows} rows exceed the step limit of {self.max_tokens}")
+        key = f"{name}/{width}/{dtype}"
+        buf = self._bufs.get(key)
+        if buf is None:
+            buf = torch.empty((self.max_tokens, width), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:rows]
+
+    def flat(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        key = f"{name}/flat/{dtype}"
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < numel:
+            if buf is not None and self.frozen:
+                raise ValueError(f"workspace {name} would move after a graph was captured")
+            buf = torch.empty((numel,), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:numel]
+
+    frozen = False
+
+
+@dataclass
+class GroupMeta:
+    """Per page group: where each token's keys and values go, and each segment's block table."""
+    slot_mapping: torch.Tensor      # int32 [T]: page * page_size + offset
+    block_tables: torch.Tensor      # int32 [S, max_blocks]
+    max_blocks: int
+
+
+@dataclass
+class StepContext:
+    """One batch: S segments (request, its next tokens), T tokens in all, flat and in segment order."""
+    num_tokens: int
+    num_segments: int
+    dtype: torch.dtype                       # compute dtype
+    tokens: torch.Tensor                     # int32 [T]
+    positions: torch.Tensor                  # int32 [T] position of each token in its request
+    token_seg: torch.Tensor                  # int32 [T] segment of each token
+    seg_starts: torch.Tensor                 # int32 [S+1] first token of each segment (cumulative)
+    seg_context: torch.Tensor                # int32 [S] positions of the request after this step
+    seg_slots: torch.Tensor                  # int32 [S] state slot of each segment's request
+    groups: List[GroupMeta]
+    caches: List[LayerCacheView]
+    workspace: Workspace
+    # the same on the host, for parts that plan launches per segment
+    host_seg_lens: Sequence[int] = ()
+    host_seg_first_pos: Sequence[int] = ()
+    host_seg_slots: Sequence[int] = ()
+    max_seg_len: int = 0
+    max_context: int = 0
+    decode_only: bool = False                # every segment is a single token
+    extra: dict = field(default_factory=dict)
+
+
+class Part:
+    """Common base: a part may hold device tensors and says how many bytes of weights it reads per step."""
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.tensors())
+
+    def tensors(self) -> List[torch.Tensor]:
+        return []
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, ctx: StepContext, name: str, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x float32 [T, width] -> compute dtype [T or len(rows), width]."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Either rotation tables that the mixer applies to q and k, or a change to the embeddings, or both."""
+
+    def rotary_tables(self):
+        """None, or (cos, sin, rot_dim): float32 [max_positions, rot_dim/2] tables for half-split pairs."""
+        return None
+
+    def on_embeddings(self, x: torch.Tensor, ctx: StepContext) -> None:
+        """Absolute encodings add to the float32 embeddings here, in place."""
+
+
+class Mixer(Part):
+    """Mixes information between positions of a request (attention, or anything with a state)."""
+
+    def cache_spec(self) -> CacheSpec:
+        return None
+
+    def forward(self, xn: torch.Tensor, ctx: StepContext, cache: Optional[LayerCacheView], residual: torch.Tensor,
+                write_cache: bool = True) -> None:
+        """xn [T, hidden] in the compute dtype; adds the result into residual (float32 [T, hidden])."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, xn: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+class Block(Part):
+    """An arrangement of norms, a mixer and a feed-forward around the residual stream."""
+
+    mixer: Mixer
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCacheView], write_cache: bool = True) -> None:
+        raise NotImplementedError

@@ -1,0 +1,41 @@
+"""Token embedding and the output matrix.
+
+x = the token's row, widened to float32, unscaled (engine/src/model.c:893-895);
+logits = W_out xn in float32, where W_out is lm_head.weight or, when the model
+ties them, the embedding table itself (engine/src/model.c:315-321, 975-978).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import Part, StepContext
+
+
+class Embedding(Part):
+    def __init__(self, vocab: int, hidden: int, table: torch.Tensor):
+        if table.shape != (vocab, hidden):
+            raise ValueError("the embedding table does not fit the sizes")
+        self.vocab, self.hidden, self.table = vocab, hidden, table.contiguous()
+
+    def tensors(self):
+        return [self.table]
+
+    def forward(self, ctx: StepContext) -> torch.Tensor:
+        x = ctx.workspace.rows("x", ctx.num_tokens, self.hidden, torch.float32)
+        return ops.embed_rows(self.table, ctx.tokens, x)
+
+
+class LMHead(Part):
+    def __init__(self, vocab: int, hidden: int, weight: torch.Tensor):
+        if weight.shape != (vocab, hidden):
+            raise ValueError("the output matrix does not fit the sizes")
+        self.vocab, self.hidden, self.weight = vocab, hidden, weight.contiguous()
+
+    def tensors(self):
+        return [self.weight]
+
+    def forward(self, xn: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        """xn [R, hidden] in the compute dtype -> float32 logits [R, vocab] (a new tensor each call)."""
+        out = torch.empty((xn.shape[0], self.vocab), dtype=torch.float32, device=xn.device)
+        return ops.linear(xn, self.weight, out, ops.LINEAR_F32)

@@ -1,0 +1,27 @@
+"""SwiGLU feed-forward: y = W_down (silu(W_gate xn) * (W_up xn)), added into the residual stream
+(engine/src/model.c:962-972; silu(g) = g / (1 + exp(-g)), engine/src/ops.c:283-288).
+The gate and up matrices are stacked by rows so that one product reads xn once."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import FeedForward, StepContext
+
+
+class SwiGLU(FeedForward):
+    def __init__(self, hidden: int, intermediate: int, w_gate_up: torch.Tensor, w_down: torch.Tensor):
+        if w_gate_up.shape != (2 * intermediate, hidden) or w_down.shape != (hidden, intermediate):
+            raise ValueError("feed-forward weights do not fit the sizes")
+        self.hidden, self.intermediate = hidden, intermediate
+        self.w_gate_up, self.w_down = w_gate_up.contiguous(), w_down.contiguous()
+
+    def tensors(self):
+        return [self.w_gate_up, self.w_down]
+
+    def forward(self, xn: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
+        T = ctx.num_tokens
+        ws = ctx.workspace
+        gu = ops.linear(xn, self.w_gate_up, ws.rows("ffn.gu", T, 2 * self.intermediate, ctx.dtype), ops.LINEAR_SAME)
+        act = ops.silu_mul(gu, ws.rows("ffn.act", T, self.intermediate, ctx.dtype))
+        ops.linear(act, self.w_down, residual, ops.LINEAR_ACC_F32)
