@@ -1,0 +1,159 @@
+"""The engine through its entry points: greedy and sampled generation against the plain implementation,
+long decoding, the first tokens of a sequence, several requests with too few pages (preemption),
+a failed step, and the command line."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import plain_llama as P
+from tiny_configs import TINIES, write_tiny
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def sharp_dirs(tmp_path_factory):
+    root = tmp_path_factory.mktemp("sharp_engine")
+    return {name: write_tiny(str(root / name), tiny, std=0.15) for name, tiny in TINIES.items()}
+
+
+def plain_generate(cfg, W, prompt, max_new, temperature=0.0, top_k=0, top_p=1.0, seed=0):
+    """Greedy or sampled continuation by running the whole sequence again for every new token."""
+    ids, out, rows = list(prompt), [], []
+    sampler = P.PlainSampler(seed)
+    for _ in range(max_new):
+        row = P.forward(cfg, W, ids)[-1]
+        tok = sampler.sample(row, temperature, top_k, top_p)
+        rows.append(row); out.append(tok); ids.append(tok)
+    return out, np.stack(rows)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tinyA", "tinyB"])
+def test_greedy_generation_matches_plain(name, dtype, sharp_dirs, tmp_path):
+    from vitna_anchor_b200.engine.engine import Engine
+    cfg, W = P.read_model(sharp_dirs[name])
+    rng = np.random.default_rng(11)
+    prompt = [int(t) for t in rng.integers(0, cfg["V"], 9)]
+    eng = Engine(sharp_dirs[name], dtype=dtype, kv_block=TINIES[name]["page_size"], parallel=2)
+    out_file = str(tmp_path / "rows.f32")
+    got = eng.generate(prompt, max_new=40, logits_out=out_file)
+    want, rows = plain_generate(cfg, W, prompt, 40)
+    mine = np.fromfile(out_file, "<f4").reshape(40, cfg["V"])
+    if dtype == "float32":
+        assert got == want
+        assert np.abs(mine - rows).max() <= 2e-5 * max(1.0, np.abs(rows).max())
+    else:
+        # the same tokens as long as the plain margin between the best two is not within bfloat16's error
+        for i, (g, w) in enumerate(zip(got, want)):
+            if g != w:
+                top2 = np.sort(rows[i])[-2:]
+                assert top2[1] - top2[0] < 0.16 * max(1.0, np.abs(rows[i]).max()), f"token {i}: {g} != {w}"
+                break
+            assert np.abs(mine[i] - rows[i]).max() <= 8e-2 * max(1.0, np.abs(rows).max())
+    assert eng.runner.graph_replays > 20            # decoding went through captured graphs
+    assert eng.runner.cache.free_pages() == [eng.runner.cache.tables.pools[0].num_pages]
+
+
+def test_sampled_generation_matches_plain_sampler(sharp_dirs):
+    from vitna_anchor_b200.engine.engine import Engine
+    cfg, W = P.read_model(sharp_dirs["tinyB"])
+    prompt = [5, 9, 200, 31, 7]
+    eng = Engine(sharp_dirs["tinyB"], dtype="float32", kv_block=8, parallel=2)
+    for kw in (dict(temperature=0.8, seed=7), dict(temperature=1.1, top_k=20, seed=3), dict(temperature=0.8, top_p=0.9, seed=5)):
+        got = eng.generate(prompt, max_new=16, **kw)
+        want, _ = plain_generate(cfg, W, prompt, 16, **kw)
+        assert got == want, kw
+    again = eng.generate(prompt, max_new=16, temperature=0.8, seed=7)
+    assert again == eng.generate(prompt, max_new=16, temperature=0.8, seed=7)       # a seed gives the same tokens
+
+
+def test_long_decoding_and_first_tokens(sharp_dirs):
+    """A prompt of one token, then 150 decoded tokens across many pages: every logits row against plain."""
+    from vitna_anchor_b200.engine.runner import ModelRunner, StepEntry
+    from vitna_anchor_b200.engine.loading import load_model
+    cfg, W = P.read_model(sharp_dirs["tinyB"])
+    rng = np.random.default_rng(2)
+    ids = [int(t) for t in rng.integers(0, cfg["V"], 151)]
+    plain = P.forward(cfg, W, ids)
+    for dtype, tol in (("float32", 2e-5), ("bfloat16", 8e-2)):
+        runner = ModelRunner(load_model(sharp_dirs["tinyB"], dtype), page_size=8, num_pages=24, max_requests=2, max_batch_tokens=64)
+        runner.open("r")
+        worst = 0.0
+        for p, t in enumerate(ids):
+            row = runner.step([StepEntry("r", [t], [0])])[0].cpu().numpy()
+            worst = max(worst, np.abs(row - plain[p]).max())
+        assert worst <= tol * max(1.0, np.abs(plain).max()), (dtype, worst)
+        assert runner.graph_replays >= 149
+        runner.close("r")
+        runner.cache.check()
+
+
+def test_requests_together_with_few_pages_equal_requests_alone(sharp_dirs):
+    """Six requests, four at a time, in a pool so small that the newest is preempted and recomputed:
+    every request's tokens are those it gets alone (float32: greedy and seeded sampling)."""
+    from vitna_anchor_b200.engine.engine import Engine
+    rng = np.random.default_rng(4)
+    cfgA = TINIES["tinyA"]["config"]
+    prompts = [[int(t) for t in rng.integers(0, cfgA["vocab_size"], n)] for n in (5, 17, 33, 12, 26, 8)]
+    alone = Engine(sharp_dirs["tinyA"], dtype="float32", kv_block=4, parallel=1)
+    want_greedy = [alone.generate(p, max_new=20) for p in prompts]
+    want_sampled = [alone.generate(p, max_new=20, temperature=0.8, seed=100 + i) for i, p in enumerate(prompts)]
+    small = Engine(sharp_dirs["tinyA"], dtype="float32", kv_block=4, parallel=4, num_pages=34, max_batch_tokens=24)
+    assert small.generate(prompts, max_new=20) == want_greedy
+    assert small.scheduler.preempted_total > 0, "the pool was meant to be too small"
+    assert small.generate(prompts, max_new=20, temperature=0.8, seed=100) == want_sampled
+    small.runner.cache.check()
+    assert small.runner.cache.free_pages() == [34]
+
+
+def test_failed_step_ends_the_request_and_changes_nothing(sharp_dirs):
+    from vitna_anchor_b200.engine.engine import Engine
+    from vitna_anchor_b200.engine.runner import StepFailed
+    eng = Engine(sharp_dirs["tinyA"], dtype="float32", kv_block=4, parallel=2)
+    want = eng.generate([1, 2, 3, 4], max_new=8)
+    eng.runner.fail_step_once(6)                   # the step that computes position 6: the third decoded token
+    with pytest.raises(StepFailed):
+        eng.generate([1, 2, 3, 4], max_new=8)
+    assert eng.scheduler.finished[-1].output == want[:3]
+    assert eng.runner.cache.free_pages() == [eng.runner.cache.tables.pools[0].num_pages]
+    assert eng.generate([1, 2, 3, 4], max_new=8) == want          # the engine goes on
+
+
+def test_refusals(sharp_dirs):
+    from vitna_anchor_b200.engine.engine import Engine, RequestRefused
+    eng = Engine(sharp_dirs["tinyA"], dtype="float32", kv_block=4, parallel=1, ctx=64)
+    with pytest.raises(RequestRefused):
+        eng.generate([1] * 60, max_new=8)
+    with pytest.raises(RequestRefused):
+        eng.generate([1, 999], max_new=2)
+    with pytest.raises(ValueError):
+        Engine(sharp_dirs["tinyA"], device="cpu")
+
+
+def test_command_line(sharp_dirs, tmp_path):
+    exe = [sys.executable, os.path.join(ROOT, "bin", "vitna-anchor")]
+    model = sharp_dirs["tinyB"]
+    cfg, W = P.read_model(model)
+    ids = [3, 1, 4, 1, 5, 9, 2, 6]
+    r = subprocess.run(exe + ["generate", "--model", model, "--ids", ",".join(map(str, ids)), "--max-new", "6", "--greedy",
+                              "--dtype", "float32", "--timing"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    assert out["prompt_ids"] == ids and out["ids"] == plain_generate(cfg, W, ids, 6)[0]
+    assert "timing: 8 prompt tokens in" in r.stderr
+    f = tmp_path / "l.f32"
+    r = subprocess.run(exe + ["logits", "--model", model, "--ids", ",".join(map(str, ids)), "--out", str(f), "--dtype", "float32"],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    rows = np.fromfile(str(f), "<f4").reshape(len(ids), cfg["V"])
+    assert np.abs(rows - P.forward(cfg, W, ids)).max() <= 2e-5 * 5
+    r = subprocess.run(exe + ["generate", "--model", model, "--ids", "1,2", "--device", "cpu"], capture_output=True, text=True)
+    assert r.returncode == 1 and "cuda" in r.stderr
+    r = subprocess.run(exe + ["generate", "--model", model, "--ids", "1,2", "--speculate", "4"], capture_output=True, text=True)
+    assert r.returncode == 1 and "Unknown or incomplete option: --speculate" in r.stderr

@@ -1,0 +1,277 @@
+"""Each kernel alone against a plain float32 statement of the same operation, at sizes other than
+the engine's own: odd widths, head sizes in steps of 16, many groups, page sizes that do not divide
+the length, and inputs made so that a wrong key, page or window edge shows."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+
+DT = [torch.float32, torch.bfloat16]
+
+
+def dev(a, dtype=None):
+    t = torch.as_tensor(a).cuda()
+    return t.to(dtype) if dtype is not None else t
+
+
+def tol(dtype):
+    return 2e-5 if dtype == torch.float32 else 1e-2
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from vitna_anchor_b200 import ops
+    ops.lib()
+    return ops
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_embed_rows(ops, dtype):
+    table = torch.randn(77, 53).to(dtype).cuda()
+    ids = dev(np.array([0, 76, 5, 5, 31], dtype=np.int32))
+    out = torch.empty(5, 53, device="cuda")
+    ops.embed_rows(table, ids, out)
+    assert torch.equal(out, table.float()[ids.long()])
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("n", [37, 576, 1000])
+def test_rmsnorm_rows(ops, dtype, n):
+    x = (torch.randn(9, n) * 3).cuda()
+    w = (1 + 0.1 * torch.randn(n)).cuda()
+    want = torch.from_numpy(P.rms_norm(x.cpu().numpy(), w.cpu().numpy(), 1e-5))
+    out = torch.empty(9, n, dtype=dtype, device="cuda")
+    ops.rmsnorm_rows(x, w, 1e-5, out)
+    assert (out.float().cpu() - want).abs().max() <= tol(dtype) * want.abs().max()
+    rows = dev(np.array([8, 0, 3], dtype=np.int32))
+    out2 = torch.empty(3, n, dtype=dtype, device="cuda")
+    ops.rmsnorm_rows(x, w, 1e-5, out2, rows)
+    assert torch.equal(out2, out[rows.long()])
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("shape", [(3, 5, 7), (67, 131, 33), (64, 576, 576), (17, 1536, 100), (1, 960, 576), (8, 49, 128),
+                                   (5, 200, 50), (130, 70, 300)])
+def test_linear_simt(ops, dtype, shape):
+    M, N, K = shape
+    x = torch.randn(M, K).to(dtype).cuda()
+    w = (torch.randn(N, K) / math.sqrt(K)).to(dtype).cuda()
+    want = x.double() @ w.double().T
+    scale = float(want.abs().max())
+    same = torch.empty(M, N, dtype=dtype, device="cuda")
+    ops.linear_simt(x, w, same, ops.LINEAR_SAME)
+    assert (same.double() - want).abs().max() <= tol(dtype) * scale
+    f32 = torch.empty(M, N, device="cuda")
+    ops.linear_simt(x, w, f32, ops.LINEAR_F32)
+    assert (f32.double() - want).abs().max() <= 2e-5 * scale       # float32 sums of exact products in both dtypes
+    acc = torch.ones(M, N, device="cuda")
+    ops.linear_simt(x, w, acc, ops.LINEAR_ACC_F32)
+    assert (acc.double() - 1 - want).abs().max() <= 2e-5 * scale
+    if M <= 8:      # the same rows through the tile kernel agree to rounding
+        tile = torch.empty(M, N, device="cuda")
+        ops.linear_simt(x, w, tile, ops.LINEAR_F32, few_rows=0)
+        assert (tile - f32).abs().max() <= 2e-5 * scale
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_linear_rows_do_not_depend_on_the_batch(ops, dtype):
+    """A row's result is the same bits whatever else is in the batch (same kernel)."""
+    x = torch.randn(40, 96).to(dtype).cuda()
+    w = torch.randn(50, 96).to(dtype).cuda()
+    a = torch.empty(40, 50, device="cuda")
+    ops.linear_simt(x, w, a, ops.LINEAR_F32)
+    b = torch.empty(13, 50, device="cuda")
+    ops.linear_simt(x[20:33].contiguous(), w, b, ops.LINEAR_F32)
+    assert torch.equal(a[20:33], b)
+    xs = x[:, :64]                        # strided rows
+    c = torch.empty(40, 50, device="cuda")
+    ops.linear_simt(xs, w[:, :64].contiguous(), c, ops.LINEAR_F32)
+    assert (c.double() - xs.double() @ w[:, :64].double().T).abs().max() < 1e-3
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nh,nkv,hd,rot,ps", [(4, 2, 16, 16, 4), (3, 1, 32, 32, 8), (9, 3, 64, 64, 16), (5, 5, 48, 32, 16), (2, 1, 80, 80, 3)])
+def test_rope_store(ops, dtype, nh, nkv, hd, rot, ps):
+    T, pages = 11, 9
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd).to(dtype)
+    positions = np.array([0, 1, 2, 77, 5, 300, 6, 7, 8, 9, 10], dtype=np.int32)
+    cos, sin = P.rope_tables(np.arange(400), rot, 50000.0)
+    slots = np.random.default_rng(0).permutation(pages * ps)[:T].astype(np.int32)
+    slots[4] = -1
+    cache = torch.full((pages, 2, nkv, ps, hd), 7.0, dtype=dtype, device="cuda")
+    q_out = torch.empty(T, nh * hd, dtype=dtype, device="cuda")
+    ops.rope_store(qkv.cuda(), dev(positions), dev(cos), dev(sin), dev(slots), q_out, cache, nh, nkv, hd, rot, ps)
+    f = qkv.float().numpy()
+    q = f[:, :nh * hd].reshape(T, nh, hd)
+    k = f[:, nh * hd:(nh + nkv) * hd].reshape(T, nkv, hd)
+    v = f[:, (nh + nkv) * hd:].reshape(T, nkv, hd)
+    c, s = cos[positions], sin[positions]
+
+    def rotate(a):
+        out = a.copy()
+        out[..., :rot] = P.rope_half(a[..., :rot], c, s)
+        return out
+    qr, kr = rotate(q), rotate(k)
+    t = tol(dtype) * 4
+    assert np.abs(q_out.float().cpu().numpy().reshape(T, nh, hd) - qr).max() <= t
+    got = cache.float().cpu().numpy()
+    touched = np.zeros((pages, ps), bool)
+    for i in range(T):
+        if slots[i] < 0:
+            continue
+        pg, off = slots[i] // ps, slots[i] % ps
+        touched[pg, off] = True
+        assert np.abs(got[pg, 0, :, off, :] - kr[i]).max() <= t
+        assert np.abs(got[pg, 1, :, off, :] - v[i]).max() <= t
+    untouched = got.transpose(0, 3, 1, 2, 4)[~touched]
+    assert np.all(untouched == 7.0)           # no slot but the tokens' own was written
+
+
+def _paged(k, v, ps, pages, rng, dtype):
+    """Scatter k, v [n, nkv, hd] into a pool through a shuffled block table."""
+    n, nkv, hd = k.shape
+    nb = -(-n // ps)
+    table = rng.permutation(pages)[:nb].astype(np.int32)
+    cache = torch.zeros(pages, 2, nkv, ps, hd, dtype=dtype)
+    cache += 1000.0      # a read outside the request's own slots shows
+    for p in range(n):
+        cache[table[p // ps], 0, :, p % ps] = torch.from_numpy(k[p]).to(dtype)
+        cache[table[p // ps], 1, :, p % ps] = torch.from_numpy(v[p]).to(dtype)
+    return cache.cuda(), table
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(4, 2, 16, 4, 0), (3, 1, 32, 8, 0), (9, 3, 64, 16, 0), (6, 2, 48, 16, 0),
+                                                 (2, 2, 80, 5, 0), (8, 1, 256, 16, 0), (4, 2, 16, 4, 5), (3, 3, 64, 16, 130)])
+def test_attention_rows_mixed_batch(ops, dtype, nh, nkv, hd, ps, window):
+    """Three requests in one batch: a decoded token far into a context, a prompt portion in mid-request,
+    and a whole short prompt.  Scores are made sharp so that one wrong key changes the result."""
+    rng = np.random.default_rng(3)
+    lens = [301, 140, 9]                    # context after the step
+    news = [1, 37, 9]                       # tokens of this step
+    pages = sum(-(-n // ps) for n in lens) + 7
+    pool = torch.zeros(pages, 2, nkv, ps, hd, dtype=dtype) + 1000.0
+    free = list(rng.permutation(pages))
+    maxb = max(-(-n // ps) for n in lens)
+    bt = np.zeros((3, maxb), dtype=np.int32)
+    q_all, seg, pos, want = [], [], [], []
+    for s, (n, new) in enumerate(zip(lens, news)):
+        k = (rng.standard_normal((n, nkv, hd)) * 2.0).astype(np.float32)
+        v = rng.standard_normal((n, nkv, hd)).astype(np.float32)
+        q = (rng.standard_normal((n, nh, hd)) * 2.0).astype(np.float32)
+        if s == 0:      # one far key stands out for the decoded token
+            k[3] = q[n - 1, 0::max(1, nh // nkv)][:nkv] * 3.0
+        k = torch.from_numpy(k).to(dtype).float().numpy()
+        v = torch.from_numpy(v).to(dtype).float().numpy()
+        q = torch.from_numpy(q).to(dtype).float().numpy()
+        for b in range(-(-n // ps)):
+            bt[s, b] = free.pop()
+        for p in range(n):
+            pool[bt[s, p // ps], 0, :, p % ps] = torch.from_numpy(k[p]).to(dtype)
+            pool[bt[s, p // ps], 1, :, p % ps] = torch.from_numpy(v[p]).to(dtype)
+        ref = P.causal_attention(q, k, v, window=window or None).reshape(n, nh * hd)
+        for p in range(n - new, n):
+            q_all.append(q[p].reshape(-1)); seg.append(s); pos.append(p); want.append(ref[p])
+    q_all = torch.from_numpy(np.stack(q_all)).to(dtype).cuda()
+    out = torch.empty_like(q_all)
+    ops.attention_rows(q_all, pool.cuda(), dev(bt), dev(np.array(seg, np.int32)), dev(np.array(pos, np.int32)), out, nh, nkv,
+                       hd, 1.0 / math.sqrt(hd), window)
+    want = np.stack(want)
+    err = np.abs(out.float().cpu().numpy() - want).max()
+    assert err <= (1e-5 if dtype == torch.float32 else 2e-2) * max(1.0, np.abs(want).max()), err
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_attention_window_edge(ops, dtype):
+    """The key just inside the window is read, the key just outside is not."""
+    nh = nkv = 1; hd = 16; ps = 4; n = 40; window = 8
+    k = np.zeros((n, 1, hd), np.float32); v = np.zeros((n, 1, hd), np.float32)
+    q = np.zeros((1, hd), np.float32); q[0, 0] = 8.0
+    pos = n - 1
+    k[pos - window + 1, 0, 0] = 8.0; v[pos - window + 1, 0, 1] = 1.0       # inside, strong
+    k[pos - window, 0, 0] = 16.0; v[pos - window, 0, 2] = 1.0               # outside, stronger
+    cache, table = _paged(k, v, ps, 20, np.random.default_rng(0), dtype)
+    out = torch.empty(1, hd, dtype=dtype, device="cuda")
+    ops.attention_rows(dev(q, dtype), cache, dev(table[None, :]), dev(np.array([0], np.int32)), dev(np.array([pos], np.int32)),
+                       out, nh, nkv, hd, 0.25, window)
+    o = out.float().cpu().numpy()[0]
+    assert o[1] > 0.99 and abs(o[2]) < 1e-6
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_silu_mul(ops, dtype):
+    gu = (torch.randn(7, 2 * 93) * 3).to(dtype).cuda()
+    out = torch.empty(7, 93, dtype=dtype, device="cuda")
+    ops.silu_mul(gu, out)
+    g, u = gu.float()[:, :93], gu.float()[:, 93:]
+    want = g / (1 + torch.exp(-g)) * u
+    assert (out.float() - want).abs().max() <= tol(dtype) * want.abs().max()
+
+
+def test_add_inplace(ops):
+    y = torch.randn(1000, device="cuda"); x = torch.randn(1000, device="cuda"); y0 = y.clone()
+    ops.add_inplace(y, x)
+    assert torch.equal(y, y0 + x)
+    xb = x.to(torch.bfloat16)
+    ops.add_inplace(y, xb)
+    assert torch.equal(y, y0 + x + xb.float())
+
+
+def test_argmax_takes_the_lowest_id_of_equal_maxima(ops):
+    l = torch.randn(5, 49155).cuda()
+    l[0, 777] = 50.0; l[0, 40000] = 50.0; l[0, 12] = 50.0
+    l[1, 49154] = 60.0
+    l[2, 0] = 60.0
+    out = torch.empty(5, dtype=torch.int32, device="cuda")
+    ops.argmax_rows(l, out)
+    assert out.tolist()[:3] == [12, 49154, 0]
+    assert out.tolist()[3:] == l[3:].argmax(-1).tolist()
+
+
+@pytest.mark.parametrize("vocab", [384, 49152, 1000])
+def test_sample_rows_matches_the_plain_sampler(ops, vocab):
+    rng = np.random.default_rng(9)
+    settings = [(0.0, 0, 1.0), (0.8, 0, 1.0), (1.0, 5, 1.0), (0.7, 0, 0.9), (1.3, 50, 0.5), (0.8, 1, 1.0), (0.8, 0, 1e-6), (2.0, 0, 0.999)]
+    rows = len(settings) * 4
+    logits = (rng.standard_normal((rows, vocab)) * 3).astype(np.float32)
+    logits[5, 100:110] = logits[5, 100]          # equal probabilities: the lower id comes first
+    temp = np.array([settings[r % len(settings)][0] for r in range(rows)], np.float32)
+    top_k = np.array([settings[r % len(settings)][1] for r in range(rows)], np.int32)
+    top_p = np.array([settings[r % len(settings)][2] for r in range(rows)], np.float32)
+    sampler = P.PlainSampler(1234)
+    u = np.array([sampler.uniform() for _ in range(rows)], np.float64)
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    scratch = torch.empty(rows * vocab, device="cuda")
+    ops.sample_rows(dev(logits), dev(temp), dev(top_k), dev(top_p), dev(u), scratch, out)
+    got = out.tolist()
+    for r in range(rows):
+        if temp[r] <= 0:
+            assert got[r] == int(np.argmax(logits[r]))
+            continue
+        order, p, keep, mass = sampler.distribution(logits[r], float(temp[r]), int(top_k[r]), float(top_p[r]))
+        cum = np.cumsum(p[:keep])
+        target = u[r] * mass
+        hit = np.nonzero(target < cum)[0]
+        want = int(order[hit[0]] if len(hit) else order[keep - 1])
+        if got[r] != want:
+            # only when u falls within rounding of a boundary of the cumulative distribution
+            i = list(order[:keep]).index(got[r]) if got[r] in order[:keep] else -1
+            assert i >= 0 and min(abs(target - cum[i]), abs(target - (cum[i - 1] if i else 0.0))) < 1e-6, (r, got[r], want)
+
+
+def test_sampling_proportions(ops):
+    vocab, rows = 50, 4000
+    logits = np.tile(np.linspace(-2, 2, vocab).astype(np.float32), (rows, 1))
+    s = P.PlainSampler(5)
+    u = np.array([s.uniform() for _ in range(rows)], np.float64)
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    ops.sample_rows(dev(logits), dev(np.full(rows, 1.0, np.float32)), dev(np.zeros(rows, np.int32)),
+                    dev(np.ones(rows, np.float32)), dev(u), torch.empty(rows * vocab, device="cuda"), out)
+    freq = np.bincount(out.cpu().numpy(), minlength=vocab) / rows
+    p = np.exp(logits[0] - logits[0].max()); p /= p.sum()
+    assert np.abs(freq - p).max() < 0.02

@@ -55,7 +55,7 @@ class _Staging:
 class ModelRunner:
     def __init__(self, model: DecoderModel, *, page_size: int = 16, num_pages: Optional[int] = None,
                  max_requests: int = 64, max_batch_tokens: int = 2048, max_model_len: Optional[int] = None,
-                 device="cuda", cache_tokens: Optional[int] = None):
+                 device="cuda", cache_tokens: Optional[int] = None, cuda_graphs: bool = True):
         self.model = model
         self.device = torch.device(device)
         if self.device.type != "cuda":
@@ -72,8 +72,8 @@ class ModelRunner:
         self.workspace = Workspace(self.device, max_batch_tokens)
         self.max_segments = max_requests
         n_groups = len(self.cache.groups)
-        self._meta_len = (3 * max_batch_tokens + 3 * self.max_segments + 1 + max_batch_tokens
-                          + n_groups * (max_batch_tokens + self.max_segments * self.max_blocks))
+        most = max(max_batch_tokens, self.max_segments)
+        self._meta_len = 4 * most + 3 * self.max_segments + 1 + n_groups * (most + self.max_segments * self.max_blocks)
         self._staging = [_Staging(self._meta_len, True) for _ in range(4)]
         self._stage_i = 0
         self._meta_dev = torch.zeros(self._meta_len, dtype=torch.int32, device=self.device)
@@ -82,6 +82,9 @@ class ModelRunner:
         if env is not None:
             self._fail_at = int(env) if env.strip() else 0
         self.steps_run = 0
+        self.cuda_graphs = cuda_graphs
+        self._graphs: Dict[int, tuple] = {}      # decode batch bucket -> (graph, logits)
+        self.graph_replays = 0
 
     # -- requests ---------------------------------------------------------------------------
     def open(self, request_id: Hashable) -> int:
@@ -203,11 +206,94 @@ class ModelRunner:
                     raise StepFailed(f"the step that computes position {lo} failed as the test asked")
         self.cache.reserve_step(plan)         # OutOfPages leaves everything as it was
         try:
-            ctx, rows = self._build_context(entries, T, R)
-            logits = self.model.forward(ctx, rows)
+            if self.cuda_graphs and T == len(entries) == R and all(len(e.want) == 1 for e in entries):
+                logits = self._decode_step(entries)
+            else:
+                ctx, rows = self._build_context(entries, T, R)
+                logits = self.model.forward(ctx, rows)
         except BaseException:
             self.cache.rollback_step(plan)
             raise
         self.cache.commit_step(plan)
         self.steps_run += 1
         return logits
+
+    # -- decoding through CUDA graphs -----------------------------------------------------------
+    def _decode_context(self, entries: Sequence[StepEntry], B: int) -> Tuple[StepContext, torch.Tensor]:
+        """The context of a batch of single tokens, padded to B segments, at fixed offsets in the
+        metadata buffer so that a captured graph finds every array where it was at capture.  A padding
+        segment has one token at position 0 that writes nothing (slot -1) and reads page 0."""
+        S, ps, maxb = len(entries), self.page_size, self.max_blocks
+        tables = self.cache.tables
+        st = self._staging[self._stage_i]
+        self._stage_i = (self._stage_i + 1) % len(self._staging)
+        if st.event is not None:
+            st.event.synchronize()
+        buf = st.np
+        n_groups = len(self.cache.groups)
+        total = 7 * B + 1 + n_groups * (B + B * maxb)
+        buf[:total] = 0
+        o_tok, o_pos, o_seg, o_starts = 0, B, 2 * B, 3 * B
+        o_ctx, o_slots, o_rows = 4 * B + 1, 5 * B + 1, 6 * B + 1
+        o_groups = 7 * B + 1
+        ar = np.arange(B + 1, dtype=np.int32)
+        buf[o_seg:o_seg + B] = ar[:B]
+        buf[o_starts:o_starts + B + 1] = ar
+        buf[o_rows:o_rows + B] = ar[:B]
+        buf[o_ctx:o_ctx + B] = 1
+        rcs = [tables.get(e.request_id) for e in entries]
+        first = [rc.length for rc in rcs]
+        buf[o_tok:o_tok + S] = [int(e.tokens[0]) for e in entries]
+        buf[o_pos:o_pos + S] = first
+        buf[o_ctx:o_ctx + S] = [f + 1 for f in first]
+        buf[o_slots:o_slots + S] = [rc.slot for rc in rcs]
+        for g in range(n_groups):
+            o_sm = o_groups + g * (B + B * maxb)
+            o_bt = o_sm + B
+            buf[o_sm:o_sm + B] = -1
+            bt = buf[o_bt:o_bt + B * maxb].reshape(B, maxb)
+            for i, rc in enumerate(rcs):
+                blocks = rc.tables[g].blocks
+                row = np.asarray(blocks, dtype=np.int32)
+                buf[o_sm + i] = row[first[i] // ps] * ps + first[i] % ps
+                np.maximum(row, 0, out=row)
+                bt[i, :len(row)] = row
+        dev = self._meta_dev
+        dev[:total].copy_(st.host[:total], non_blocking=True)
+        st.event = torch.cuda.Event()
+        st.event.record()
+        groups = []
+        for g in range(n_groups):
+            o_sm = o_groups + g * (B + B * maxb)
+            groups.append(GroupMeta(dev[o_sm:o_sm + B], dev[o_sm + B:o_sm + B + B * maxb].view(B, maxb), maxb))
+        ctx = StepContext(
+            num_tokens=B, num_segments=B, dtype=self.model.dtype, tokens=dev[o_tok:o_tok + B], positions=dev[o_pos:o_pos + B],
+            token_seg=dev[o_seg:o_seg + B], seg_starts=dev[o_starts:o_starts + B + 1], seg_context=dev[o_ctx:o_ctx + B],
+            seg_slots=dev[o_slots:o_slots + B], groups=groups, caches=self.cache.views, workspace=self.workspace,
+            host_seg_lens=[1] * B, host_seg_first_pos=first + [0] * (B - S), host_seg_slots=[rc.slot for rc in rcs] + [0] * (B - S),
+            max_seg_len=1, max_context=self.max_model_len, decode_only=True)
+        return ctx, dev[o_rows:o_rows + B]
+
+    def _decode_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        S = len(entries)
+        B = 1
+        while B < S:
+            B *= 2
+        B = min(B, self.max_segments) if S <= self.max_segments else S
+        ctx, rows = self._decode_context(entries, B)
+        held = self._graphs.get(B)
+        if held is None:
+            # the first batch of this size runs eagerly (it also makes the workspace buffers), then the
+            # same launches are captured; the captured graph is replayed from the next step on
+            logits = self.model.forward(ctx, rows)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_logits = self.model.forward(ctx, rows)
+            # capture does not run the kernels, and `logits` above is this step's result
+            self._graphs[B] = (graph, static_logits)
+            return logits[:S]
+        graph, static_logits = held
+        graph.replay()
+        self.graph_replays += 1
+        return static_logits[:S]
