@@ -21,6 +21,7 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from .. import ops
 from ..cache.manager import CacheManager, KVSpec
 from ..cache.pages import OutOfPages, UNMAPPED
 from ..models.decoder import DecoderModel
@@ -288,12 +289,15 @@ class ModelRunner:
             logits = self.model.forward(ctx, rows)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count()
             with torch.cuda.graph(graph):
                 static_logits = self.model.forward(ctx, rows)
-            # capture does not run the kernels, and `logits` above is this step's result
-            self._graphs[B] = (graph, static_logits)
+            kernels = ops.launch_count() - before
+            ops.add_launches(-kernels)            # capture does not run the kernels; `logits` above is this step's result
+            self._graphs[B] = (graph, static_logits, kernels)
             return logits[:S]
-        graph, static_logits = held
+        graph, static_logits, kernels = held
         graph.replay()
+        ops.add_launches(kernels)
         self.graph_replays += 1
         return static_logits[:S]

@@ -33,8 +33,23 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far by this process (a graph replay counts the kernels it holds)."""
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
 def _check(status: int, what: str) -> None:
+    global _launches
     if status == 0:
+        _launches += 1
         return
     fn = lib().vk_error_string
     fn.restype = ctypes.c_char_p
