@@ -275,3 +275,61 @@ def test_sampling_proportions(ops):
     freq = np.bincount(out.cpu().numpy(), minlength=vocab) / rows
     p = np.exp(logits[0] - logits[0].max()); p /= p.sum()
     assert np.abs(freq - p).max() < 0.02
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(4, 2, 16, 4, 0), (3, 1, 32, 8, 0), (9, 3, 64, 16, 0), (6, 2, 48, 16, 0),
+                                                 (2, 2, 80, 5, 0), (18, 2, 128, 16, 0), (8, 1, 256, 16, 0), (4, 2, 16, 4, 5),
+                                                 (3, 3, 64, 16, 300), (9, 3, 64, 16, 700)])
+def test_attention_decode_split_keys(ops, dtype, nh, nkv, hd, ps, window):
+    """Single decoded tokens at contexts that end inside the first run of 256 keys, exactly on a run's edge,
+    just past it, and far beyond; one key made to stand out in each; listed among tokens that are not run."""
+    if not ops.attention_decode_takes(dtype, hd):
+        pytest.skip("the split-key kernel does not take this head size in this dtype; attention_rows does")
+    rng = np.random.default_rng(8)
+    lens = [1, 7, 256, 257, 600, 1023]
+    pages = sum(-(-n // ps) for n in lens) + 5
+    pool = torch.zeros(pages, 2, nkv, ps, hd, dtype=dtype) + 1000.0
+    free = list(rng.permutation(pages))
+    maxb = max(-(-n // ps) for n in lens)
+    bt = np.zeros((len(lens), maxb), dtype=np.int32)
+    qs, want = [], []
+    g = nh // nkv
+    for s, n in enumerate(lens):
+        k = (rng.standard_normal((n, nkv, hd)) * 1.5).astype(np.float32)
+        v = rng.standard_normal((n, nkv, hd)).astype(np.float32)
+        q = (rng.standard_normal((1, nh, hd)) * 1.5).astype(np.float32)
+        far = min(n - 1, 3 if s % 2 else max(0, n - 260))
+        k[far] = q[0, ::g][:nkv] * 2.0
+        k, v, q = (torch.from_numpy(a).to(dtype).float().numpy() for a in (k, v, q))
+        for b in range(-(-n // ps)):
+            bt[s, b] = free.pop()
+        kk = torch.from_numpy(k).to(dtype); vv = torch.from_numpy(v).to(dtype)
+        for p in range(n):
+            pool[bt[s, p // ps], 0, :, p % ps] = kk[p]
+            pool[bt[s, p // ps], 1, :, p % ps] = vv[p]
+        lo = max(0, n - window) if window else 0
+        ref = P.causal_attention(np.concatenate([np.zeros((n - 1 - lo, nh, hd), np.float32), q]), k[lo:], v[lo:])[-1]
+        qs.append(q.reshape(-1)); want.append(ref)
+    # tokens 0, 2, 4, ... are the decoded ones; odd tokens are fillers that must be left alone
+    T = 2 * len(lens)
+    q_all = torch.zeros(T, nh * hd, dtype=dtype)
+    q_all[0::2] = torch.from_numpy(np.stack(qs)).to(dtype)
+    seg = np.repeat(np.arange(len(lens), dtype=np.int32), 2)
+    pos = np.repeat(np.array(lens, np.int32) - 1, 2)
+    out = torch.full((T, nh * hd), 5.0, dtype=dtype, device="cuda")
+    cap, max_ctx = 8, 2048
+    scratch = torch.zeros(ops.attention_decode_scratch_bytes(cap, nh, nkv, hd, max_ctx), dtype=torch.uint8, device="cuda")
+    args = (q_all.cuda(), pool.cuda(), dev(bt), dev(seg), dev(pos))
+    tok = dev(np.arange(0, T, 2, dtype=np.int32))
+    for launch in range(2):          # twice: the scratch is left ready for the next launch
+        out.fill_(5.0)
+        ops.attention_decode(*args, out, scratch, cap, nh, nkv, hd, 1.0 / math.sqrt(hd), max_ctx, 1024 if launch else 2048,
+                             window, tok)
+        got = out.float().cpu().numpy()
+        assert np.all(got[1::2] == 5.0)
+        err = np.abs(got[0::2] - np.stack(want)).max()
+        assert err <= (1e-5 if dtype == torch.float32 else 2e-2) * max(1.0, np.abs(np.stack(want)).max()), (launch, err)
+    rows = torch.empty_like(out)
+    ops.attention_rows(*args, rows, nh, nkv, hd, 1.0 / math.sqrt(hd), window, tok)
+    assert (rows.float()[0::2] - out.float()[0::2]).abs().max() <= (1e-5 if dtype == torch.float32 else 2e-2)

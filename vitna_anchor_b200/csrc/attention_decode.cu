@@ -1,0 +1,258 @@
+// Attention of single decoded tokens over the paged cache, split over the keys.
+//
+// grid = (splits, kv-head tiles, tokens).  A block handles one token, one key-value head (up to
+// G_TILE of the query heads that read it; a larger group takes several blocks) and one run of
+// SPLIT keys whose boundaries are multiples of SPLIT in absolute position, so that the sums of a
+// (request, position) do not depend on the batch.  The group's query heads share every key and
+// value load.  Each block leaves an unnormalised partial (max, sum, sum of p*v); the block that
+// finishes last for its (token, kv-head tile) adds the partials in split order and writes the
+// output.  There is no waiting on other blocks: the last one to arrive does the work.
+//
+// Scores are q.k * scale with the scale applied after the sum; softmax with the maximum taken
+// out; everything in float32 (engine/src/model.c:932-956; the reference's decode kernel splits
+// the keys the same way, engine/src/model_cuda.cu:942-1067).
+//
+// Scratch (global memory beyond inputs and outputs), sized for `tokens` and `max_splits`:
+//   part_o  float [tokens][nh][max_splits][hd]      part_ml  float [tokens][nh][max_splits][2]
+//   (indexed by the token's place in the launch's list, not by its index in the batch)
+//   counters int [tokens][kv-head tiles], zero before the first launch; the kernel leaves them zero.
+//
+// Sizes: hd a multiple of 16 bytes' worth of elements (8 for bfloat16, 4 for float32) and at most
+// 256; any number of heads and groups; any page size that is a multiple of that vector width is
+// NOT required: rows are [page][k|v][kv head][slot][hd], so every row starts 16-byte aligned
+// when hd does.
+#include "common.cuh"
+
+namespace vk {
+
+constexpr int DEC_THREADS = 256;
+constexpr int DEC_SPLIT = 256;     // keys per block: one per thread in the score phase
+constexpr int DEC_G_TILE = 8;      // query heads of a group handled by one block
+constexpr int DEC_MAX_HD = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(
+    const T* __restrict__ q, const T* __restrict__ cache, const int32_t* __restrict__ block_tables,
+    const int32_t* __restrict__ token_seg, const int32_t* __restrict__ positions, const int32_t* __restrict__ tok_list,
+    T* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int nh, int nkv,
+    int hd, int page_size, int max_blocks, int max_splits, float scale, int window) {
+    constexpr int V = Vec16<T>::N;
+    extern __shared__ float smem[];
+    const int g = nh / nkv;
+    const int tiles_per_kv = (g + DEC_G_TILE - 1) / DEC_G_TILE;
+    const int split = blockIdx.x;
+    const int kvh = blockIdx.y / tiles_per_kv;
+    const int h0 = kvh * g + (blockIdx.y % tiles_per_kv) * DEC_G_TILE;       // first query head of this block
+    const int gt = min(DEC_G_TILE, kvh * g + g - h0);                         // query heads of this block
+    const int zi = blockIdx.z;                                                // index of the token in this launch: its scratch rows
+    const int t = tok_list ? tok_list[zi] : zi;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    const int pos = positions[t];
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int first_split = lo / DEC_SPLIT, last_split = pos / DEC_SPLIT;
+    if (split < first_split || split > last_split) return;
+    const int n_active = last_split - first_split + 1;
+    const int k0 = split * DEC_SPLIT;
+    const int nkeys = min(DEC_SPLIT, pos - k0 + 1);                           // keys k0 .. k0+nkeys-1 are not after pos
+
+    float* qs = smem;                                  // [G_TILE][hd]
+    float* ps = qs + DEC_G_TILE * hd;                  // [G_TILE][SPLIT]
+    float* red = ps + DEC_G_TILE * DEC_SPLIT;          // [groups][hd], groups * hd = 8 warps * 32 lanes * V
+    __shared__ float wred[DEC_THREADS / 32][DEC_G_TILE];
+    __shared__ float stat_m[DEC_G_TILE], stat_l[DEC_G_TILE];
+    __shared__ int is_last;
+
+    for (int i = tid; i < gt * hd; i += DEC_THREADS) qs[i] = to_f32<T>(q[((size_t)t * nh + h0) * hd + i]);
+    __syncthreads();
+
+    const int32_t* bt = block_tables + (size_t)token_seg[t] * max_blocks;
+    const size_t page_stride = (size_t)2 * nkv * page_size * hd;
+    const size_t v_off = (size_t)nkv * page_size * hd;
+
+    // ---- scores: one key per thread -------------------------------------------------------------
+    const int key = k0 + tid;
+    const bool valid = tid < nkeys && key >= lo;
+    float s[DEC_G_TILE];
+#pragma unroll
+    for (int h = 0; h < DEC_G_TILE; h++) s[h] = 0.0f;
+    if (valid) {
+        const T* kr = cache + (size_t)bt[key / page_size] * page_stride + ((size_t)kvh * page_size + key % page_size) * hd;
+#pragma unroll 4
+        for (int c = 0; c < hd; c += V) {
+            float kf[V];
+            load16<T>(kr + c, kf);
+#pragma unroll
+            for (int h = 0; h < DEC_G_TILE; h++) {
+                if (h < gt) {
+#pragma unroll
+                    for (int i = 0; i < V; i++) s[h] = fmaf(qs[h * hd + c + i], kf[i], s[h]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < DEC_G_TILE; h++) s[h] = valid ? s[h] * scale : -INFINITY;
+
+    // block maximum of each head
+#pragma unroll
+    for (int h = 0; h < DEC_G_TILE; h++) {
+        const float m = warp_max(s[h]);
+        if (lane == 0) wred[warp][h] = m;
+    }
+    __syncthreads();
+    if (tid < DEC_G_TILE) {
+        float m = -INFINITY;
+        for (int w = 0; w < DEC_THREADS / 32; w++) m = fmaxf(m, wred[w][tid]);
+        stat_m[tid] = m;
+    }
+    __syncthreads();
+    float p[DEC_G_TILE];
+#pragma unroll
+    for (int h = 0; h < DEC_G_TILE; h++) {
+        p[h] = (valid && h < gt) ? expf(s[h] - stat_m[h]) : 0.0f;
+        if (h < gt) ps[h * DEC_SPLIT + tid] = p[h];
+        const float sum = warp_sum(p[h]);
+        if (lane == 0) wred[warp][h] = sum;       // safe: every thread has read stat_m's inputs before the barrier above
+    }
+    __syncthreads();
+    if (tid < DEC_G_TILE) {
+        float l = 0.0f;
+        for (int w = 0; w < DEC_THREADS / 32; w++) l += wred[w][tid];
+        stat_l[tid] = l;
+    }
+
+    // ---- sum of p * v: a row of v is read by hd/V lanes, 16 bytes each --------------------------
+    const int lpr = hd / V;                        // lanes per row
+    const int rpw = 32 / lpr;                      // rows per warp per pass (lanes beyond rpw*lpr idle)
+    const int r = lane / lpr, c = (lane % lpr) * V;
+    const bool lane_on = r < rpw;
+    const int group = warp * rpw + r;              // which partial sum this thread adds to
+    const int groups = (DEC_THREADS / 32) * rpw;
+    float acc[DEC_G_TILE][V];
+#pragma unroll
+    for (int h = 0; h < DEC_G_TILE; h++)
+#pragma unroll
+        for (int i = 0; i < V; i++) acc[h][i] = 0.0f;
+    if (lane_on) {
+        const int row_lo = lo > k0 ? lo - k0 : 0;
+        for (int row = group; row < nkeys; row += groups) {
+            if (row < row_lo) continue;
+            const int kk = k0 + row;
+            const T* vr = cache + (size_t)bt[kk / page_size] * page_stride + v_off + ((size_t)kvh * page_size + kk % page_size) * hd;
+            float vf[V];
+            load16<T>(vr + c, vf);
+#pragma unroll
+            for (int h = 0; h < DEC_G_TILE; h++) {
+                if (h < gt) {
+                    const float pv = ps[h * DEC_SPLIT + row];
+#pragma unroll
+                    for (int i = 0; i < V; i++) acc[h][i] = fmaf(pv, vf[i], acc[h][i]);
+                }
+            }
+        }
+    }
+    // partial sums of the groups meet in shared memory, one head at a time, in group order
+    const bool single = n_active == 1;
+#pragma unroll
+    for (int h = 0; h < DEC_G_TILE; h++) {
+        if (h >= gt) break;                        // gt is the same for the whole block
+        __syncthreads();
+        if (lane_on) {
+#pragma unroll
+            for (int i = 0; i < V; i++) red[group * hd + c + i] = acc[h][i];
+        }
+        __syncthreads();
+        for (int d = tid; d < hd; d += DEC_THREADS) {
+            float o = 0.0f;
+            for (int gi = 0; gi < groups; gi++) o += red[gi * hd + d];
+            if (single) out[((size_t)t * nh + h0 + h) * hd + d] = from_f32<T>(o * (1.0f / stat_l[h]));
+            else part_o[(((size_t)zi * nh + h0 + h) * max_splits + split) * hd + d] = o;
+        }
+    }
+    if (single) return;
+    if (tid < gt) {
+        float* ml = part_ml + (((size_t)zi * nh + h0 + tid) * max_splits + split) * 2;
+        ml[0] = stat_m[tid];
+        ml[1] = stat_l[tid];
+    }
+
+    // ---- the last block of this (token, kv-head tile) combines ----------------------------------
+    __threadfence();
+    __syncthreads();
+    int* counter = counters + (size_t)zi * (nkv * tiles_per_kv) + blockIdx.y;
+    if (tid == 0) {
+        const int old = atomicAdd(counter, 1);
+        is_last = old == n_active - 1;
+        if (is_last) *counter = 0;                 // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int h = 0; h < gt; h++) {
+        const volatile float* ml = part_ml + ((size_t)zi * nh + h0 + h) * max_splits * 2;
+        float m = -INFINITY;
+        for (int sp = first_split; sp <= last_split; sp++) m = fmaxf(m, ml[sp * 2]);
+        float l = 0.0f;
+        for (int sp = first_split; sp <= last_split; sp++) l += ml[sp * 2 + 1] * expf(ml[sp * 2] - m);
+        const float inv = 1.0f / l;
+        const volatile float* po = part_o + ((size_t)zi * nh + h0 + h) * max_splits * hd;
+        for (int d = tid; d < hd; d += DEC_THREADS) {
+            float o = 0.0f;
+            for (int sp = first_split; sp <= last_split; sp++) o += po[(size_t)sp * hd + d] * expf(ml[sp * 2] - m);
+            out[((size_t)t * nh + h0 + h) * hd + d] = from_f32<T>(o * inv);
+        }
+    }
+}
+
+}  // namespace vk
+
+using namespace vk;
+
+// Bytes of scratch for `tokens` decoded tokens: part_o, part_ml and counters, in that order, each 256-byte aligned.
+VK_API size_t vk_attention_decode_scratch_bytes(int tokens, int nh, int nkv, int hd, int max_context) {
+    const size_t splits = (size_t)(max_context + DEC_SPLIT - 1) / DEC_SPLIT;
+    const size_t g = nh / nkv, tiles = nkv * ((g + DEC_G_TILE - 1) / DEC_G_TILE);
+    auto up = [](size_t b) { return (b + 255) / 256 * 256; };
+    return up((size_t)tokens * nh * splits * hd * 4) + up((size_t)tokens * nh * splits * 2 * 4) + up((size_t)tokens * tiles * 4);
+}
+
+// q, out [all tokens, nh*hd]; tok_list [n_tokens] names the tokens to run (null: tokens 0..n_tokens-1).
+// scratch: vk_attention_decode_scratch_bytes(scratch_tokens, ..., max_context) bytes whose counters part (the
+// last) was zero before the first launch.  max_context fixes the layout of the scratch; grid_context
+// (<= max_context) bounds every position + 1 of this launch and sizes the grid (a captured graph keeps it).
+VK_API int vk_attention_decode(const void* q, const void* cache, const int32_t* block_tables, const int32_t* token_seg,
+                               const int32_t* positions, const int32_t* tok_list, void* out, void* scratch, int scratch_tokens,
+                               int n_tokens, int nh, int nkv, int hd, int page_size, int max_blocks, int max_context,
+                               int grid_context, float scale, int window, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return VK_OK;
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || page_size <= 0 || max_blocks <= 0 || window < 0 || max_context <= 0 ||
+        grid_context <= 0 || grid_context > max_context)
+        return VK_BAD_SHAPE;
+    const int vec = dtype == 0 ? 4 : 8;
+    if (hd % vec != 0) return VK_BAD_SHAPE;
+    if (hd > DEC_MAX_HD || hd / vec > 32 || n_tokens > scratch_tokens || n_tokens > 65535) return VK_TOO_LARGE;
+    if (((uintptr_t)cache % 16) || ((uintptr_t)scratch % 16) || ((uintptr_t)q % 4)) return VK_BAD_ALIGNMENT;
+    const int splits = (max_context + DEC_SPLIT - 1) / DEC_SPLIT;
+    const int grid_splits = (grid_context + DEC_SPLIT - 1) / DEC_SPLIT;
+    const int g = nh / nkv, tiles = nkv * ((g + DEC_G_TILE - 1) / DEC_G_TILE);
+    auto up = [](size_t b) { return (b + 255) / 256 * 256; };
+    char* base = (char*)scratch;
+    float* part_o = (float*)base;
+    float* part_ml = (float*)(base + up((size_t)scratch_tokens * nh * splits * hd * 4));
+    int* counters = (int*)((char*)part_ml + up((size_t)scratch_tokens * nh * splits * 2 * 4));
+    const size_t smem = (size_t)(DEC_G_TILE * hd + DEC_G_TILE * DEC_SPLIT + DEC_THREADS * vec) * sizeof(float);
+    dim3 grid(grid_splits, tiles, n_tokens);
+    if (dtype == 0) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attention_decode_kernel<float><<<grid, DEC_THREADS, smem, stream>>>(
+            (const float*)q, (const float*)cache, block_tables, token_seg, positions, tok_list, (float*)out, part_o, part_ml,
+            counters, nh, nkv, hd, page_size, max_blocks, splits, scale, window);
+    } else {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attention_decode_kernel<__nv_bfloat16><<<grid, DEC_THREADS, smem, stream>>>(
+            (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_tables, token_seg, positions, tok_list, (__nv_bfloat16*)out,
+            part_o, part_ml, counters, nh, nkv, hd, page_size, max_blocks, splits, scale, window);
+    }
+    return launch_status();
+}

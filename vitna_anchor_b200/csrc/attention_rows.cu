@@ -24,15 +24,15 @@ constexpr int ATT_MAX_ACC = 4;  // head sizes up to 4 * 128
 template <typename T>
 __global__ void __launch_bounds__(ATT_THREADS) attention_rows_kernel(
     const T* __restrict__ q, const T* __restrict__ cache, const int32_t* __restrict__ block_tables,
-    const int32_t* __restrict__ token_seg, const int32_t* __restrict__ positions, T* __restrict__ out, int nh, int nkv,
-    int hd, int page_size, int max_blocks, float scale, int window) {
+    const int32_t* __restrict__ token_seg, const int32_t* __restrict__ positions, const int32_t* __restrict__ tok_list,
+    T* __restrict__ out, int nh, int nkv, int hd, int page_size, int max_blocks, float scale, int window) {
     extern __shared__ float smem[];
     float* qs = smem;                         // [hd]
     float* pr = qs + hd;                      // [128]
     float* scratch = pr + ATT_THREADS;        // [32]
     __shared__ size_t row_off[ATT_THREADS];   // element offset of each key's K row in the layer's cache
 
-    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int t = tok_list ? tok_list[blockIdx.x] : blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int kvh = h / (nh / nkv);
     const int pos = positions[t];
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
@@ -95,9 +95,10 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_rows_kernel(
 using namespace vk;
 
 // q, out [tokens, nh*hd]; cache: one layer [pages][2][nkv][page_size][hd];
-// block_tables [segments, max_blocks]; token_seg, positions [tokens].
+// block_tables [segments, max_blocks]; token_seg, positions [all tokens]; tok_list [tokens] names the
+// tokens to run (null: 0..tokens-1).
 VK_API int vk_attention_rows(const void* q, const void* cache, const int32_t* block_tables, const int32_t* token_seg,
-                             const int32_t* positions, void* out, int tokens, int nh, int nkv, int hd, int page_size,
+                             const int32_t* positions, const int32_t* tok_list, void* out, int tokens, int nh, int nkv, int hd, int page_size,
                              int max_blocks, float scale, int window, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return VK_OK;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || page_size <= 0 || max_blocks <= 0 || window < 0) return VK_BAD_SHAPE;
@@ -106,11 +107,11 @@ VK_API int vk_attention_rows(const void* q, const void* cache, const int32_t* bl
     dim3 grid(tokens, nh);
     if (dtype == 0)
         attention_rows_kernel<float><<<grid, ATT_THREADS, smem, stream>>>((const float*)q, (const float*)cache, block_tables,
-                                                                          token_seg, positions, (float*)out, nh, nkv, hd,
+                                                                          token_seg, positions, tok_list, (float*)out, nh, nkv, hd,
                                                                           page_size, max_blocks, scale, window);
     else
         attention_rows_kernel<__nv_bfloat16><<<grid, ATT_THREADS, smem, stream>>>(
-            (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_tables, token_seg, positions, (__nv_bfloat16*)out, nh,
+            (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_tables, token_seg, positions, tok_list, (__nv_bfloat16*)out, nh,
             nkv, hd, page_size, max_blocks, scale, window);
     return launch_status();
 }

@@ -65,6 +65,26 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return r;
 }
 
+// Sixteen bytes of T as floats: 4 float32 or 8 bfloat16 (widened exactly).  p must be 16-byte aligned.
+template <typename T> struct Vec16;
+template <> struct Vec16<float> { static constexpr int N = 4; };
+template <> struct Vec16<__nv_bfloat16> { static constexpr int N = 8; };
+
+template <typename T> __device__ __forceinline__ void load16(const T* p, float* f);
+template <> __device__ __forceinline__ void load16<float>(const float* p, float* f) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+template <> __device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* p, float* f) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        f[2 * i] = __uint_as_float(u[i] << 16);
+        f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+}
+
 inline int launch_status() { return (int)cudaGetLastError(); }
 
 }  // namespace vk

@@ -75,29 +75,10 @@ __global__ void __launch_bounds__(256) gemm_tile_kernel(const T* __restrict__ x,
 // row once, 16 bytes per lane per load, and keeps one sum per input row.
 // Each lane's partial sum runs over k = lane*VEC + 32*VEC*i (+0..VEC-1) in
 // increasing order; the 32 partial sums meet in a fixed shuffle tree.
-template <typename T> struct Vec;
-template <> struct Vec<float> { static constexpr int N = 4; };
-template <> struct Vec<__nv_bfloat16> { static constexpr int N = 8; };
-
-template <typename T> __device__ __forceinline__ void load_vec(const T* p, float* f);
-template <> __device__ __forceinline__ void load_vec<float>(const float* p, float* f) {
-    const float4 v = *reinterpret_cast<const float4*>(p);
-    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
-}
-template <> __device__ __forceinline__ void load_vec<__nv_bfloat16>(const __nv_bfloat16* p, float* f) {
-    const uint4 v = *reinterpret_cast<const uint4*>(p);
-    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        f[2 * i] = __uint_as_float(u[i] << 16);
-        f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
-    }
-}
-
 template <typename T, int MODE, int ROWS, bool VECTOR>
 __global__ void __launch_bounds__(256) gemv_rows_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restrict__ out,
                                                         int M, int N, int K, int ldx) {
-    constexpr int V = Vec<T>::N;
+    constexpr int V = Vec16<T>::N;
     const int lane = threadIdx.x & 31;
     const int warps_per_block = blockDim.x >> 5;
     for (int n = blockIdx.x * warps_per_block + (threadIdx.x >> 5); n < N; n += gridDim.x * warps_per_block) {
@@ -108,12 +89,12 @@ __global__ void __launch_bounds__(256) gemv_rows_kernel(const T* __restrict__ x,
         if (VECTOR) {
             for (int k = lane * V; k < K; k += 32 * V) {
                 float wf[V];
-                load_vec<T>(wr + k, wf);
+                load16<T>(wr + k, wf);
 #pragma unroll
                 for (int m = 0; m < ROWS; m++) {
                     if (m < M) {
                         float xf[V];
-                        load_vec<T>(x + (size_t)m * ldx + k, xf);
+                        load16<T>(x + (size_t)m * ldx + k, xf);
 #pragma unroll
                         for (int i = 0; i < V; i++) acc[m] = fmaf(xf[i], wf[i], acc[m]);
                     }
@@ -138,7 +119,7 @@ __global__ void __launch_bounds__(256) gemv_rows_kernel(const T* __restrict__ x,
 template <typename T, int MODE>
 static int launch_linear(const T* x, const T* w, void* out, int M, int N, int K, int ldx, int few_rows, cudaStream_t stream) {
     if (M <= few_rows) {
-        constexpr int V = Vec<T>::N;
+        constexpr int V = Vec16<T>::N;
         const bool vec = (K % V == 0) && (ldx % V == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0);
         const int blocks = (N + 7) / 8 < 148 * 8 ? (N + 7) / 8 : 148 * 8;
         if (M <= 4) {

@@ -70,11 +70,11 @@ class ModelRunner:
         self.cache = CacheManager(model.cache_specs(), page_size=page_size, num_pages=num_pages, max_requests=max_requests,
                                   dtype=model.dtype, device=self.device)
         self.max_blocks = -(-self.max_model_len // page_size)
-        self.workspace = Workspace(self.device, max_batch_tokens)
+        self.workspace = Workspace(self.device, max_batch_tokens, max_requests, self.max_model_len)
         self.max_segments = max_requests
         n_groups = len(self.cache.groups)
         most = max(max_batch_tokens, self.max_segments)
-        self._meta_len = 4 * most + 3 * self.max_segments + 1 + n_groups * (most + self.max_segments * self.max_blocks)
+        self._meta_len = 5 * most + 3 * self.max_segments + 1 + n_groups * (most + self.max_segments * self.max_blocks)
         self._staging = [_Staging(self._meta_len, True) for _ in range(4)]
         self._stage_i = 0
         self._meta_dev = torch.zeros(self._meta_len, dtype=torch.int32, device=self.device)
@@ -168,6 +168,10 @@ class ModelRunner:
         s_slots = put(np.asarray(slots, dtype=np.int32), S)
         rows = [int(seg_starts[i]) + int(w) for i, e in enumerate(entries) for w in e.want]
         s_rows = put(np.asarray(rows, dtype=np.int32), R) if R else slice(off, off)
+        dec = [int(seg_starts[i]) for i in range(S) if lens[i] == 1]
+        pre = [t for i in range(S) if lens[i] > 1 for t in range(int(seg_starts[i]), int(seg_starts[i + 1]))]
+        s_dec = put(np.asarray(dec, dtype=np.int32), len(dec)) if dec else None
+        s_pre = put(np.asarray(pre, dtype=np.int32), len(pre)) if pre and dec else None
         group_slices = []
         for g in range(len(self.cache.groups)):
             bt = np.zeros((S, maxb), dtype=np.int32)
@@ -191,7 +195,9 @@ class ModelRunner:
             num_tokens=T, num_segments=S, dtype=self.model.dtype, tokens=dev[s_tokens], positions=dev[s_pos],
             token_seg=dev[s_seg], seg_starts=dev[s_starts], seg_context=dev[s_ctx], seg_slots=dev[s_slots], groups=groups,
             caches=self.cache.views, workspace=self.workspace, host_seg_lens=lens, host_seg_first_pos=first,
-            host_seg_slots=slots, max_seg_len=max(lens), max_context=max(context), decode_only=all(n == 1 for n in lens))
+            host_seg_slots=slots, max_seg_len=max(lens), max_context=max(context), decode_only=all(n == 1 for n in lens),
+            num_dec=len(dec), dec_tokens=None if (s_dec is None or not pre) else dev[s_dec],
+            num_pre=len(pre), pre_tokens=None if s_pre is None else dev[s_pre])
         return ctx, (dev[s_rows] if R else None)
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
@@ -272,7 +278,7 @@ class ModelRunner:
             token_seg=dev[o_seg:o_seg + B], seg_starts=dev[o_starts:o_starts + B + 1], seg_context=dev[o_ctx:o_ctx + B],
             seg_slots=dev[o_slots:o_slots + B], groups=groups, caches=self.cache.views, workspace=self.workspace,
             host_seg_lens=[1] * B, host_seg_first_pos=first + [0] * (B - S), host_seg_slots=[rc.slot for rc in rcs] + [0] * (B - S),
-            max_seg_len=1, max_context=self.max_model_len, decode_only=True)
+            max_seg_len=1, max_context=self.max_model_len, decode_only=True, num_dec=B)
         return ctx, dev[o_rows:o_rows + B]
 
     def _decode_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:

@@ -160,8 +160,9 @@ def rope_store(qkv: torch.Tensor, positions: torch.Tensor, cos: Optional[torch.T
 
 def attention_rows(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: torch.Tensor, token_seg: torch.Tensor,
                    positions: torch.Tensor, out: torch.Tensor, nh: int, nkv: int, hd: int, scale: float,
-                   window: int = 0) -> torch.Tensor:
-    """Causal attention of every token over its request's pages (any sizes, float32 arithmetic)."""
+                   window: int = 0, tok_list: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of every token (or of those in tok_list) over its request's pages (any sizes,
+    float32 arithmetic)."""
     _req(q, "q", dims=2); _req(cache_layer, "cache_layer", q.dtype, 5); _req(block_tables, "block_tables", torch.int32, 2)
     _req(token_seg, "token_seg", torch.int32, 1); _req(positions, "positions", torch.int32, 1); _req(out, "out", q.dtype, 2)
     T = q.shape[0]
@@ -170,9 +171,53 @@ def attention_rows(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: tor
         raise KernelError("attention_rows: shapes do not fit the head counts")
     if token_seg.shape[0] != T or positions.shape[0] != T:
         raise KernelError("attention_rows: per-token arrays differ in length")
-    _check(lib().vk_attention_rows(_p(q), _p(cache_layer), _p(block_tables), _p(token_seg), _p(positions), _p(out), T, nh,
-                                   nkv, hd, page_size, block_tables.shape[1], ctypes.c_float(scale), window, _dt(q),
+    n = T
+    if tok_list is not None:
+        _req(tok_list, "tok_list", torch.int32, 1)
+        n = tok_list.shape[0]
+    _check(lib().vk_attention_rows(_p(q), _p(cache_layer), _p(block_tables), _p(token_seg), _p(positions), _p(tok_list), _p(out),
+                                   n, nh, nkv, hd, page_size, block_tables.shape[1], ctypes.c_float(scale), window, _dt(q),
                                    _stream()), "attention_rows")
+    return out
+
+
+def attention_decode_scratch_bytes(tokens: int, nh: int, nkv: int, hd: int, max_context: int) -> int:
+    fn = lib().vk_attention_decode_scratch_bytes
+    fn.restype = ctypes.c_size_t
+    return int(fn(tokens, nh, nkv, hd, max_context))
+
+
+def attention_decode_takes(dtype: torch.dtype, hd: int) -> bool:
+    """Whether the split-key decode kernel takes this head size (else attention_rows does the work)."""
+    vec = 4 if dtype == torch.float32 else 8
+    return hd % vec == 0 and hd <= 256 and hd // vec <= 32
+
+
+def attention_decode(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: torch.Tensor, token_seg: torch.Tensor,
+                     positions: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, scratch_tokens: int, nh: int, nkv: int,
+                     hd: int, scale: float, max_context: int, grid_context: int, window: int = 0,
+                     tok_list: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of single decoded tokens, split over the keys in runs of 256 absolute positions.
+    scratch: a byte buffer of attention_decode_scratch_bytes(scratch_tokens, ...) that was zero at first use
+    and is used by no other shape; max_context fixes its layout, grid_context (<= max_context) bounds the
+    positions of this launch."""
+    _req(q, "q", dims=2); _req(cache_layer, "cache_layer", q.dtype, 5); _req(block_tables, "block_tables", torch.int32, 2)
+    _req(token_seg, "token_seg", torch.int32, 1); _req(positions, "positions", torch.int32, 1); _req(out, "out", q.dtype, 2)
+    _req(scratch, "scratch", torch.uint8, 1)
+    T = q.shape[0]
+    page_size = cache_layer.shape[3]
+    if q.shape[1] != nh * hd or out.shape != q.shape or tuple(cache_layer.shape[1:]) != (2, nkv, page_size, hd):
+        raise KernelError("attention_decode: shapes do not fit the head counts")
+    n = T
+    if tok_list is not None:
+        _req(tok_list, "tok_list", torch.int32, 1)
+        n = tok_list.shape[0]
+    if scratch.numel() < attention_decode_scratch_bytes(scratch_tokens, nh, nkv, hd, max_context):
+        raise KernelError("attention_decode: the scratch is too small")
+    _check(lib().vk_attention_decode(_p(q), _p(cache_layer), _p(block_tables), _p(token_seg), _p(positions), _p(tok_list),
+                                     _p(out), _p(scratch), scratch_tokens, n, nh, nkv, hd, page_size, block_tables.shape[1],
+                                     max_context, grid_context, ctypes.c_float(scale), window, _dt(q), _stream()),
+           "attention_decode")
     return out
 
 
@@ -233,5 +278,17 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> to
 
 def attention(q: torch.Tensor, pages: torch.Tensor, meta, ctx, out: torch.Tensor, nh: int, nkv: int, hd: int,
               scale: float, window: int = 0) -> torch.Tensor:
-    """Causal attention of a mixed batch over the paged cache; `meta` is the page group's GroupMeta."""
+    """Causal attention of a mixed batch over the paged cache; `meta` is the page group's GroupMeta.
+    Single decoded tokens take the split-key kernel; tokens of prompt portions take attention_rows."""
+    if ctx.num_dec and attention_decode_takes(q.dtype, hd):
+        ws = ctx.workspace
+        cap, layout = ws.max_segments, ws.max_context
+        nbytes = attention_decode_scratch_bytes(cap, nh, nkv, hd, layout)
+        scratch = ws.flat(f"att.dec/{nh}/{nkv}/{hd}/{layout}", nbytes, torch.uint8, zero=True)
+        attention_decode(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, scratch, cap, nh, nkv, hd, scale,
+                         layout, min(layout, max(1, ctx.max_context)), window, ctx.dec_tokens)
+        if ctx.num_pre:
+            attention_rows(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, nh, nkv, hd, scale, window,
+                           ctx.pre_tokens)
+        return out
     return attention_rows(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, nh, nkv, hd, scale, window)

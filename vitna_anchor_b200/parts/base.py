@@ -22,9 +22,11 @@ class Workspace:
     Addresses never change after the first use, which is what replaying a
     captured CUDA graph needs."""
 
-    def __init__(self, device: torch.device, max_tokens: int):
+    def __init__(self, device: torch.device, max_tokens: int, max_segments: int = 0, max_context: int = 0):
         self.device = device
         self.max_tokens = max_tokens
+        self.max_segments = max_segments or max_tokens     # most requests in a step
+        self.max_context = max_context or 8192             # most positions a request may reach
         self._bufs: Dict[str, torch.Tensor] = {}
 
     def rows(self, name: str, rows: int, width: int, dtype: torch.dtype) -> torch.Tensor:
@@ -38,17 +40,16 @@ class Workspace:
             self._bufs[key] = buf
         return buf[:rows]
 
-    def flat(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+    def flat(self, name: str, numel: int, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """A flat buffer `name` of at least numel elements; it never moves or shrinks once made (zero: it starts as zeros)."""
         key = f"{name}/flat/{dtype}"
         buf = self._bufs.get(key)
-        if buf is None or buf.numel() < numel:
-            if buf is not None and self.frozen:
-                raise ValueError(f"workspace {name} would move after a graph was captured")
-            buf = torch.empty((numel,), dtype=dtype, device=self.device)
+        if buf is None:
+            buf = (torch.zeros if zero else torch.empty)((numel,), dtype=dtype, device=self.device)
             self._bufs[key] = buf
+        elif buf.numel() < numel:
+            raise ValueError(f"workspace {name} was made for {buf.numel()} elements and {numel} are asked for")
         return buf[:numel]
-
-    frozen = False
 
 
 @dataclass
@@ -81,6 +82,11 @@ class StepContext:
     max_seg_len: int = 0
     max_context: int = 0
     decode_only: bool = False                # every segment is a single token
+    # tokens of single-token segments and of longer segments, as flat token indices (None: all tokens, in order)
+    num_dec: int = 0
+    dec_tokens: Optional[torch.Tensor] = None
+    num_pre: int = 0
+    pre_tokens: Optional[torch.Tensor] = None
     extra: dict = field(default_factory=dict)
 
 
