@@ -333,3 +333,89 @@ def test_attention_decode_split_keys(ops, dtype, nh, nkv, hd, ps, window):
     rows = torch.empty_like(out)
     ops.attention_rows(*args, rows, nh, nkv, hd, 1.0 / math.sqrt(hd), window, tok)
     assert (rows.float()[0::2] - out.float()[0::2]).abs().max() <= (1e-5 if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("M,N,K", [(1, 50, 64), (3, 131, 576), (8, 960, 576), (9, 49, 128), (20, 200, 1536), (64, 96, 72), (5, 34, 8200)])
+def test_linear_skinny_plain_epilogues(ops, dtype, M, N, K):
+    x = torch.randn(M, K).to(dtype).cuda()
+    w = (torch.randn(N, K) / math.sqrt(K)).to(dtype).cuda()
+    want = x.double() @ w.double().T
+    scale = float(want.abs().max())
+    same = torch.empty(M, N, dtype=dtype, device="cuda")
+    ops.linear_skinny(x, w, same, ops.EPI_SAME)
+    assert (same.double() - want).abs().max() <= tol(dtype) * scale
+    f32 = torch.empty(M, N, device="cuda")
+    ops.linear_skinny(x, w, f32, ops.EPI_F32)
+    assert (f32.double() - want).abs().max() <= 2e-5 * scale
+    acc = torch.ones(M, N, device="cuda")
+    ops.linear_skinny(x, w, acc, ops.EPI_ACC)
+    assert (acc.double() - 1 - want).abs().max() <= 2e-5 * scale
+    one = torch.empty(1, N, device="cuda")                 # a row alone gives the same bits as in the batch
+    ops.linear_skinny(x[M - 1:M].contiguous(), w, one, ops.EPI_F32)
+    assert torch.equal(one[0], f32[M - 1])
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("M,K", [(1, 576), (8, 96), (13, 8200)])
+def test_linear_skinny_with_norm_and_rows(ops, dtype, M, K):
+    N, rows_total = 70, 30
+    x = (torch.randn(rows_total, K) * 2).cuda()
+    nw = (1 + 0.1 * torch.randn(K)).cuda()
+    w = (torch.randn(N, K) / math.sqrt(K)).to(dtype).cuda()
+    rows = torch.randperm(rows_total)[:M].to(torch.int32).cuda()
+    xn = torch.empty(M, K, dtype=dtype, device="cuda")
+    ops.rmsnorm_rows(x, nw, 1e-5, xn, rows)                 # the unfused path rounds the same way
+    want = xn.double() @ w.double().T
+    got = torch.empty(M, N, device="cuda")
+    ops.linear_skinny(x, w, got, ops.EPI_F32, norm_weight=nw, eps=1e-5, rows=rows)
+    assert (got.double() - want).abs().max() <= (2e-5 if dtype == torch.float32 else 6e-3) * float(want.abs().max())
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_linear_skinny_swiglu(ops, dtype):
+    M, I, K = 7, 93, 80
+    x = (torch.randn(M, K) * 2).cuda()
+    nw = torch.ones(K).cuda()
+    w = (torch.randn(2 * I, K) / math.sqrt(K) * 2).to(dtype).cuda()
+    xn = torch.empty(M, K, dtype=dtype, device="cuda")
+    ops.rmsnorm_rows(x, nw, 1e-6, xn)
+    gu = torch.empty(M, 2 * I, dtype=dtype, device="cuda")
+    ops.linear_simt(xn, w, gu, ops.LINEAR_SAME)
+    want = torch.empty(M, I, dtype=dtype, device="cuda")
+    ops.silu_mul(gu, want)
+    got = torch.empty(M, I, dtype=dtype, device="cuda")
+    ops.linear_skinny(x, w, got, ops.EPI_SWIGLU, norm_weight=nw, eps=1e-6)
+    assert (got.float() - want.float()).abs().max() <= tol(dtype) * float(want.float().abs().max())
+    got2 = torch.empty(M, I, dtype=dtype, device="cuda")
+    ops.linear_skinny(xn, w, got2, ops.EPI_SWIGLU)
+    assert (got2.float() - want.float()).abs().max() <= tol(dtype) * float(want.float().abs().max())
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(4, 2, 16, 4), (3, 1, 32, 8), (9, 3, 64, 16), (2, 2, 80, 3)])
+def test_linear_skinny_rope_store_matches_the_separate_kernels(ops, dtype, nh, nkv, hd, ps):
+    M, K, pages = 6, 96, 9
+    N = (nh + 2 * nkv) * hd
+    x = (torch.randn(M, K) * 2).cuda()
+    nw = (1 + 0.1 * torch.randn(K)).cuda()
+    w = (torch.randn(N, K) / math.sqrt(K) * 2).to(dtype).cuda()
+    positions = dev(np.array([0, 1, 77, 300, 5, 6], dtype=np.int32))
+    cos, sin = P.rope_tables(np.arange(400), hd, 50000.0)
+    slots = np.random.default_rng(1).permutation(pages * ps)[:M].astype(np.int32)
+    slots[2] = -1
+    xn = torch.empty(M, K, dtype=dtype, device="cuda")
+    ops.rmsnorm_rows(x, nw, 1e-5, xn)
+    qkv = torch.empty(M, N, dtype=dtype, device="cuda")
+    ops.linear_simt(xn, w, qkv, ops.LINEAR_SAME)
+    cache_a = torch.full((pages, 2, nkv, ps, hd), 7.0, dtype=dtype, device="cuda")
+    q_a = torch.empty(M, nh * hd, dtype=dtype, device="cuda")
+    ops.rope_store(qkv, positions, dev(cos), dev(sin), dev(slots), q_a, cache_a, nh, nkv, hd, hd, ps)
+    cache_b = torch.full((pages, 2, nkv, ps, hd), 7.0, dtype=dtype, device="cuda")
+    q_b = torch.empty(M, nh * hd, dtype=dtype, device="cuda")
+    ops.linear_skinny(x, w, q_b, ops.EPI_ROPE, norm_weight=nw, eps=1e-5,
+                      rope=(positions, dev(cos), dev(sin), dev(slots), cache_b, nh, nkv, hd))
+    t = tol(dtype) * 4 * float(q_a.float().abs().max())
+    assert (q_a.float() - q_b.float()).abs().max() <= t
+    assert (cache_a.float() - cache_b.float()).abs().max() <= t
+    assert torch.equal(cache_a == 7.0, cache_b == 7.0)        # the same slots were written, no others

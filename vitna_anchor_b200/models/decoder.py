@@ -69,5 +69,7 @@ class DecoderModel:
             self.blocks[run.block].forward(x, ctx, cache, run.write_cache)
         if logit_rows is None or logit_rows.shape[0] == 0:
             return None
+        if self.lm_head.fuses_norm(self.final_norm, ctx, logit_rows.shape[0]):
+            return self.lm_head.forward_normed(x, logit_rows, self.final_norm, ctx)
         xn = self.final_norm.forward(x, ctx, "head.xn", logit_rows)
         return self.lm_head.forward(xn, ctx)

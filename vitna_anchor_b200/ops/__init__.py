@@ -266,6 +266,61 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Te
     return out
 
 
+EPI_SAME, EPI_F32, EPI_ACC, EPI_SWIGLU, EPI_ROPE = 0, 1, 2, 3, 4
+SKINNY_MAX_ROWS = 64
+
+
+def skinny_takes(dtype: torch.dtype, M: int, K: int) -> bool:
+    """Whether the few-rows kernel takes this product (else the tile kernels do the work)."""
+    return 0 < M <= SKINNY_MAX_ROWS and K % (4 if dtype == torch.float32 else 8) == 0
+
+
+def linear_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, *, norm_weight: Optional[torch.Tensor] = None,
+                  eps: float = 0.0, rows: Optional[torch.Tensor] = None, rope: Optional[tuple] = None) -> torch.Tensor:
+    """out = epilogue(x' @ w.T) for at most 64 rows, where x' is x, or rmsnorm(x[rows]) * norm_weight when
+    norm_weight is given (x float32 then).  epi: EPI_SAME / EPI_F32 / EPI_ACC as LINEAR_*; EPI_SWIGLU: out [M, N/2] =
+    silu(first half) * second half; EPI_ROPE: out = rotated q [M, nh*hd], rotated k and v go into the cache;
+    rope = (positions, cos, sin, slot_mapping, cache_layer, nh, nkv, hd)."""
+    _req(w, "w", dims=2)
+    N, K = w.shape
+    if norm_weight is not None:
+        _req(x, "x", torch.float32, 2); _req(norm_weight, "norm_weight", torch.float32, 1)
+        if x.shape[1] != K or norm_weight.shape[0] != K:
+            raise KernelError("linear_skinny: widths differ")
+        M = x.shape[0]
+        if rows is not None:
+            _req(rows, "rows", torch.int32, 1)
+            M = rows.shape[0]
+        ldx = x.stride(0)
+    else:
+        if not x.is_cuda or x.dim() != 2 or x.stride(1) != 1 or x.dtype != w.dtype:
+            raise KernelError("linear_skinny: x must be a CUDA matrix of the weights' dtype with unit column stride")
+        if x.shape[1] != K or rows is not None:
+            raise KernelError("linear_skinny: widths differ, or rows given without a norm")
+        M = x.shape[0]
+        ldx = x.stride(0) if M > 1 else max(K, x.stride(0))
+    want = {EPI_SAME: ((M, N), w.dtype), EPI_F32: ((M, N), torch.float32), EPI_ACC: ((M, N), torch.float32),
+            EPI_SWIGLU: ((M, N // 2), w.dtype)}
+    pos = cos = sin = slot = cache = None
+    nh = nkv = hd = ps = 0
+    if epi == EPI_ROPE:
+        pos, cos, sin, slot, cache, nh, nkv, hd = rope
+        _req(pos, "positions", torch.int32, 1); _req(cos, "cos", torch.float32, 2); _req(sin, "sin", torch.float32, 2)
+        _req(slot, "slot_mapping", torch.int32, 1); _req(cache, "cache_layer", w.dtype, 5)
+        ps = cache.shape[3]
+        if (cos.shape[1] != hd // 2 or tuple(cache.shape[1:]) != (2, nkv, ps, hd) or pos.shape[0] < M or slot.shape[0] < M
+                or N != (nh + 2 * nkv) * hd):
+            raise KernelError("linear_skinny: the rotary epilogue's arrays do not fit the head counts")
+        want[EPI_ROPE] = ((M, nh * hd), w.dtype)
+    _req(out, "out", want[epi][1], 2)
+    if tuple(out.shape) != want[epi][0]:
+        raise KernelError(f"linear_skinny: out is {tuple(out.shape)}, expected {want[epi][0]}")
+    _check(lib().vk_linear_skinny(_p(x), _p(rows), _p(norm_weight), ctypes.c_float(eps), _p(w), _p(out), M, N, K, ldx, epi,
+                                  _p(pos), _p(cos), _p(sin), _p(slot), _p(cache), nh, nkv, hd, ps, _dt(w), _stream()),
+           "linear_skinny")
+    return out
+
+
 # ---------------------------------------------------------------------------
 # Dispatch: which kernel a part's call runs, by dtype and size.
 # ---------------------------------------------------------------------------
@@ -273,6 +328,8 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Te
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> torch.Tensor:
     """out (=, or += in mode LINEAR_ACC_F32) x @ w.T.  float32 runs on CUDA cores in float32 arithmetic
     (no reduced-precision matrix mode); bfloat16 runs the tensor-core kernel where it takes the sizes."""
+    if skinny_takes(x.dtype, x.shape[0], x.shape[1]) and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
+        return linear_skinny(x, w, out, mode)
     return linear_simt(x, w, out, mode)
 
 

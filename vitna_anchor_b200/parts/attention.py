@@ -41,16 +41,30 @@ class PagedAttention(Mixer):
     def cache_spec(self):
         return KVSpec(self.nkv, self.hd, self.window)
 
+    def fuses_norm(self, norm, ctx: StepContext) -> bool:
+        from .norms import RMSNorm
+        return isinstance(norm, RMSNorm) and ops.skinny_takes(ctx.dtype, ctx.num_tokens, self.hidden)
+
     def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCacheView, residual: torch.Tensor,
-                write_cache: bool = True) -> None:
+                write_cache: bool = True, norm=None) -> None:
         T = ctx.num_tokens
         ws = ctx.workspace
-        qkv = ops.linear(xn, self.wqkv, ws.rows("att.qkv", T, self.qd + 2 * self.kvd, ctx.dtype), ops.LINEAR_SAME)
         meta = ctx.groups[cache.group]
         tables = self.position.rotary_tables()
         cos, sin, rot = tables if tables is not None else (None, None, 0)
-        q = ops.rope_store(qkv, ctx.positions, cos, sin, meta.slot_mapping, ws.rows("att.q", T, self.qd, ctx.dtype),
-                           cache.pages if write_cache else None, self.nh, self.nkv, self.hd, rot, cache.pages.shape[3])
+        q_buf = ws.rows("att.q", T, self.qd, ctx.dtype)
+        if norm is not None and rot == self.hd and write_cache:
+            # few rows: norm, the three projections, the rotation and the cache write in one launch
+            q = ops.linear_skinny(xn, self.wqkv, q_buf, ops.EPI_ROPE, norm_weight=norm.weight, eps=norm.eps,
+                                  rope=(ctx.positions, cos, sin, meta.slot_mapping, cache.pages, self.nh, self.nkv, self.hd))
+        else:
+            qkv_buf = ws.rows("att.qkv", T, self.qd + 2 * self.kvd, ctx.dtype)
+            if norm is not None:
+                qkv = ops.linear_skinny(xn, self.wqkv, qkv_buf, ops.EPI_SAME, norm_weight=norm.weight, eps=norm.eps)
+            else:
+                qkv = ops.linear(xn, self.wqkv, qkv_buf, ops.LINEAR_SAME)
+            q = ops.rope_store(qkv, ctx.positions, cos, sin, meta.slot_mapping, q_buf, cache.pages if write_cache else None,
+                               self.nh, self.nkv, self.hd, rot, cache.pages.shape[3])
         att = ops.attention(q, cache.pages, meta, ctx, ws.rows("att.out", T, self.qd, ctx.dtype), self.nh, self.nkv,
                             self.hd, self.scale, self.window)
         ops.linear(att, self.wo, residual, ops.LINEAR_ACC_F32)

@@ -124,14 +124,23 @@ class Mixer(Part):
         return None
 
     def forward(self, xn: torch.Tensor, ctx: StepContext, cache: Optional[LayerCacheView], residual: torch.Tensor,
-                write_cache: bool = True) -> None:
-        """xn [T, hidden] in the compute dtype; adds the result into residual (float32 [T, hidden])."""
+                write_cache: bool = True, norm: Optional["Norm"] = None) -> None:
+        """xn [T, hidden] in the compute dtype; adds the result into residual (float32 [T, hidden]).
+        With `norm` (only ever passed when fuses_norm said yes) xn is the float32 residual stream itself and
+        the part applies the norm in its first kernel."""
         raise NotImplementedError
+
+    def fuses_norm(self, norm: "Norm", ctx: StepContext) -> bool:
+        """Whether this part can apply `norm` itself for this batch (saves a launch and a round trip)."""
+        return False
 
 
 class FeedForward(Part):
-    def forward(self, xn: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
+    def forward(self, xn: torch.Tensor, ctx: StepContext, residual: torch.Tensor, norm: Optional["Norm"] = None) -> None:
         raise NotImplementedError
+
+    def fuses_norm(self, norm: "Norm", ctx: StepContext) -> bool:
+        return False
 
 
 class Block(Part):

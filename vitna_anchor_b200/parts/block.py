@@ -18,7 +18,11 @@ class PreNormBlock(Block):
         return self.mixer_norm.tensors() + self.mixer.tensors() + self.ffn_norm.tensors() + self.ffn.tensors()
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCacheView], write_cache: bool = True) -> None:
-        xn = self.mixer_norm.forward(x, ctx, "block.xn")
-        self.mixer.forward(xn, ctx, cache, x, write_cache)
-        xn = self.ffn_norm.forward(x, ctx, "block.xn")
-        self.ffn.forward(xn, ctx, x)
+        if self.mixer.fuses_norm(self.mixer_norm, ctx):
+            self.mixer.forward(x, ctx, cache, x, write_cache, norm=self.mixer_norm)
+        else:
+            self.mixer.forward(self.mixer_norm.forward(x, ctx, "block.xn"), ctx, cache, x, write_cache)
+        if self.ffn.fuses_norm(self.ffn_norm, ctx):
+            self.ffn.forward(x, ctx, x, norm=self.ffn_norm)
+        else:
+            self.ffn.forward(self.ffn_norm.forward(x, ctx, "block.xn"), ctx, x)

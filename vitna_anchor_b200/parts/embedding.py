@@ -39,3 +39,12 @@ class LMHead(Part):
         """xn [R, hidden] in the compute dtype -> float32 logits [R, vocab] (a new tensor each call)."""
         out = torch.empty((xn.shape[0], self.vocab), dtype=torch.float32, device=xn.device)
         return ops.linear(xn, self.weight, out, ops.LINEAR_F32)
+
+    def fuses_norm(self, norm, ctx: StepContext, rows: int) -> bool:
+        from .norms import RMSNorm
+        return isinstance(norm, RMSNorm) and ops.skinny_takes(ctx.dtype, rows, self.hidden)
+
+    def forward_normed(self, x: torch.Tensor, rows: torch.Tensor, norm, ctx: StepContext) -> torch.Tensor:
+        """logits of rmsnorm(x[rows]) in one launch (few rows); x is the float32 residual stream."""
+        out = torch.empty((rows.shape[0], self.vocab), dtype=torch.float32, device=x.device)
+        return ops.linear_skinny(x, self.weight, out, ops.EPI_F32, norm_weight=norm.weight, eps=norm.eps, rows=rows)

@@ -19,9 +19,18 @@ class SwiGLU(FeedForward):
     def tensors(self):
         return [self.w_gate_up, self.w_down]
 
-    def forward(self, xn: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
+    def fuses_norm(self, norm, ctx: StepContext) -> bool:
+        from .norms import RMSNorm
+        return isinstance(norm, RMSNorm) and ops.skinny_takes(ctx.dtype, ctx.num_tokens, self.hidden)
+
+    def forward(self, xn: torch.Tensor, ctx: StepContext, residual: torch.Tensor, norm=None) -> None:
         T = ctx.num_tokens
         ws = ctx.workspace
-        gu = ops.linear(xn, self.w_gate_up, ws.rows("ffn.gu", T, 2 * self.intermediate, ctx.dtype), ops.LINEAR_SAME)
-        act = ops.silu_mul(gu, ws.rows("ffn.act", T, self.intermediate, ctx.dtype))
+        act_buf = ws.rows("ffn.act", T, self.intermediate, ctx.dtype)
+        if norm is not None:
+            # few rows: norm, gate and up, and silu(gate) * up in one launch
+            act = ops.linear_skinny(xn, self.w_gate_up, act_buf, ops.EPI_SWIGLU, norm_weight=norm.weight, eps=norm.eps)
+        else:
+            gu = ops.linear(xn, self.w_gate_up, ws.rows("ffn.gu", T, 2 * self.intermediate, ctx.dtype), ops.LINEAR_SAME)
+            act = ops.silu_mul(gu, act_buf)
         ops.linear(act, self.w_down, residual, ops.LINEAR_ACC_F32)
