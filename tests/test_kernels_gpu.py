@@ -335,31 +335,35 @@ def test_attention_decode_split_keys(ops, dtype, nh, nkv, hd, ps, window):
     assert (rows.float()[0::2] - out.float()[0::2]).abs().max() <= (1e-5 if dtype == torch.float32 else 2e-2)
 
 
+@pytest.mark.parametrize("simt", [False, True])
 @pytest.mark.parametrize("dtype", DT)
-@pytest.mark.parametrize("M,N,K", [(1, 50, 64), (3, 131, 576), (8, 960, 576), (9, 49, 128), (20, 200, 1536), (64, 96, 72), (5, 34, 8200)])
-def test_linear_skinny_plain_epilogues(ops, dtype, M, N, K):
+@pytest.mark.parametrize("M,N,K", [(1, 50, 64), (3, 131, 576), (8, 960, 576), (9, 49, 128), (20, 200, 1536), (64, 96, 72),
+                                   (5, 34, 8200), (33, 77, 960), (64, 130, 2048), (7, 40, 544), (2, 18, 12288)])
+def test_linear_skinny_plain_epilogues(ops, dtype, M, N, K, simt):
+    """Both few-rows kernels: CUDA cores (float32, and bfloat16 at sizes the other refuses) and tensor cores
+    (bfloat16, K a multiple of 32)."""
     x = torch.randn(M, K).to(dtype).cuda()
     w = (torch.randn(N, K) / math.sqrt(K)).to(dtype).cuda()
     want = x.double() @ w.double().T
     scale = float(want.abs().max())
     same = torch.empty(M, N, dtype=dtype, device="cuda")
-    ops.linear_skinny(x, w, same, ops.EPI_SAME)
+    ops.linear_skinny(x, w, same, ops.EPI_SAME, force_simt=simt)
     assert (same.double() - want).abs().max() <= tol(dtype) * scale
     f32 = torch.empty(M, N, device="cuda")
-    ops.linear_skinny(x, w, f32, ops.EPI_F32)
+    ops.linear_skinny(x, w, f32, ops.EPI_F32, force_simt=simt)
     assert (f32.double() - want).abs().max() <= 2e-5 * scale
     acc = torch.ones(M, N, device="cuda")
-    ops.linear_skinny(x, w, acc, ops.EPI_ACC)
+    ops.linear_skinny(x, w, acc, ops.EPI_ACC, force_simt=simt)
     assert (acc.double() - 1 - want).abs().max() <= 2e-5 * scale
     one = torch.empty(1, N, device="cuda")                 # a row alone gives the same bits as in the batch
-    ops.linear_skinny(x[M - 1:M].contiguous(), w, one, ops.EPI_F32)
+    ops.linear_skinny(x[M - 1:M].contiguous(), w, one, ops.EPI_F32, force_simt=simt)
     assert torch.equal(one[0], f32[M - 1])
 
 
 @pytest.mark.parametrize("dtype", DT)
-@pytest.mark.parametrize("M,K", [(1, 576), (8, 96), (13, 8200)])
+@pytest.mark.parametrize("M,K", [(1, 576), (8, 96), (13, 8200), (40, 1536), (3, 88)])
 def test_linear_skinny_with_norm_and_rows(ops, dtype, M, K):
-    N, rows_total = 70, 30
+    N, rows_total = 70, 90
     x = (torch.randn(rows_total, K) * 2).cuda()
     nw = (1 + 0.1 * torch.randn(K)).cuda()
     w = (torch.randn(N, K) / math.sqrt(K)).to(dtype).cuda()
@@ -373,8 +377,9 @@ def test_linear_skinny_with_norm_and_rows(ops, dtype, M, K):
 
 
 @pytest.mark.parametrize("dtype", DT)
-def test_linear_skinny_swiglu(ops, dtype):
-    M, I, K = 7, 93, 80
+@pytest.mark.parametrize("K", [80, 576])
+def test_linear_skinny_swiglu(ops, dtype, K):
+    M, I = 7, 93
     x = (torch.randn(M, K) * 2).cuda()
     nw = torch.ones(K).cuda()
     w = (torch.randn(2 * I, K) / math.sqrt(K) * 2).to(dtype).cuda()
@@ -394,8 +399,9 @@ def test_linear_skinny_swiglu(ops, dtype):
 
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("nh,nkv,hd,ps", [(4, 2, 16, 4), (3, 1, 32, 8), (9, 3, 64, 16), (2, 2, 80, 3)])
-def test_linear_skinny_rope_store_matches_the_separate_kernels(ops, dtype, nh, nkv, hd, ps):
-    M, K, pages = 6, 96, 9
+@pytest.mark.parametrize("K", [96, 72])
+def test_linear_skinny_rope_store_matches_the_separate_kernels(ops, dtype, nh, nkv, hd, ps, K):
+    M, pages = 6, 9
     N = (nh + 2 * nkv) * hd
     x = (torch.randn(M, K) * 2).cuda()
     nw = (1 + 0.1 * torch.randn(K)).cuda()

@@ -31,7 +31,7 @@ constexpr int DEC_G_TILE = 8;      // query heads of a group handled by one bloc
 constexpr int DEC_MAX_HD = 256;
 
 template <typename T>
-__global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(
+__global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
     const T* __restrict__ q, const T* __restrict__ cache, const int32_t* __restrict__ block_tables,
     const int32_t* __restrict__ token_seg, const int32_t* __restrict__ positions, const int32_t* __restrict__ tok_list,
     T* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int nh, int nkv,
@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(
     for (int h = 0; h < DEC_G_TILE; h++) s[h] = 0.0f;
     if (valid) {
         const T* kr = cache + (size_t)bt[key / page_size] * page_stride + ((size_t)kvh * page_size + key % page_size) * hd;
-#pragma unroll 4
+#pragma unroll 8
         for (int c = 0; c < hd; c += V) {
             float kf[V];
             load16<T>(kr + c, kf);
@@ -136,36 +136,70 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(
         for (int i = 0; i < V; i++) acc[h][i] = 0.0f;
     if (lane_on) {
         const int row_lo = lo > k0 ? lo - k0 : 0;
-        for (int row = group; row < nkeys; row += groups) {
-            if (row < row_lo) continue;
-            const int kk = k0 + row;
-            const T* vr = cache + (size_t)bt[kk / page_size] * page_stride + v_off + ((size_t)kvh * page_size + kk % page_size) * hd;
-            float vf[V];
-            load16<T>(vr + c, vf);
+        constexpr int B = 8;                       // rows in flight per thread: all their loads are issued before any is used
+        for (int base = group; base < nkeys; base += B * groups) {
+            float vf[B][V];
 #pragma unroll
-            for (int h = 0; h < DEC_G_TILE; h++) {
-                if (h < gt) {
-                    const float pv = ps[h * DEC_SPLIT + row];
+            for (int i = 0; i < B; i++) {
+                const int row = base + i * groups;
+                if (row < nkeys && row >= row_lo) {
+                    const int kk = k0 + row;
+                    const T* vr = cache + (size_t)bt[kk / page_size] * page_stride + v_off + ((size_t)kvh * page_size + kk % page_size) * hd;
+                    load16<T>(vr + c, vf[i]);
+                } else {
 #pragma unroll
-                    for (int i = 0; i < V; i++) acc[h][i] = fmaf(pv, vf[i], acc[h][i]);
+                    for (int e = 0; e < V; e++) vf[i][e] = 0.0f;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < B; i++) {
+                const int row = base + i * groups;
+                if (row < nkeys) {
+#pragma unroll
+                    for (int h = 0; h < DEC_G_TILE; h++) {
+                        if (h < gt) {
+                            const float pv = ps[h * DEC_SPLIT + row];
+#pragma unroll
+                            for (int e = 0; e < V; e++) acc[h][e] = fmaf(pv, vf[i][e], acc[h][e]);
+                        }
+                    }
                 }
             }
         }
     }
-    // partial sums of the groups meet in shared memory, one head at a time, in group order
+    // The partial sums of the groups meet: inside a warp by shuffles when the lanes of a row are a power
+    // of two (then lanes r = 0 hold the warp's sum), and across warps (or across all groups otherwise) in
+    // shared memory, one head at a time, in a fixed order.
+    const bool pow2 = (lpr & (lpr - 1)) == 0;
+    if (pow2) {
+#pragma unroll
+        for (int h = 0; h < DEC_G_TILE; h++) {
+            if (h < gt) {
+#pragma unroll
+                for (int e = 0; e < V; e++) {
+                    float v = acc[h][e];
+                    for (int o = lpr; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                    acc[h][e] = v;
+                }
+            }
+        }
+    }
+    const int parts = pow2 ? DEC_THREADS / 32 : groups;       // partial sums per output element
+    const int my_part = pow2 ? warp : group;
+    const bool writer = pow2 ? (r == 0) : lane_on;
     const bool single = n_active == 1;
 #pragma unroll
     for (int h = 0; h < DEC_G_TILE; h++) {
         if (h >= gt) break;                        // gt is the same for the whole block
         __syncthreads();
-        if (lane_on) {
+        if (writer) {
 #pragma unroll
-            for (int i = 0; i < V; i++) red[group * hd + c + i] = acc[h][i];
+            for (int e = 0; e < V; e++) red[my_part * hd + c + e] = acc[h][e];
         }
         __syncthreads();
         for (int d = tid; d < hd; d += DEC_THREADS) {
             float o = 0.0f;
-            for (int gi = 0; gi < groups; gi++) o += red[gi * hd + d];
+            for (int gi = 0; gi < parts; gi++) o += red[gi * hd + d];
             if (single) out[((size_t)t * nh + h0 + h) * hd + d] = from_f32<T>(o * (1.0f / stat_l[h]));
             else part_o[(((size_t)zi * nh + h0 + h) * max_splits + split) * hd + d] = o;
         }
@@ -189,19 +223,43 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int h = 0; h < gt; h++) {
-        const volatile float* ml = part_ml + ((size_t)zi * nh + h0 + h) * max_splits * 2;
+    // weights of the splits: w[h][sp] = exp(m_sp - m) / sum_sp(l_sp * exp(m_sp - m)); all loads of a stage
+    // are issued together (the partials come from L2: __ldcg), then the sums run in split order
+    float* wsp = ps;                               // [G_TILE][n_active], the scores are no longer needed
+    for (int i = tid; i < gt * n_active; i += DEC_THREADS) {
+        const int h = i / n_active, sp = first_split + i % n_active;
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (((size_t)zi * nh + h0 + h) * max_splits + sp) * 2));
+        red[i] = ml.x;                             // maxima
+        wsp[h * DEC_SPLIT + (sp - first_split)] = ml.y;     // sums, for now
+    }
+    __syncthreads();
+    if (tid < gt) {
         float m = -INFINITY;
-        for (int sp = first_split; sp <= last_split; sp++) m = fmaxf(m, ml[sp * 2]);
+        for (int j = 0; j < n_active; j++) m = fmaxf(m, red[tid * n_active + j]);
         float l = 0.0f;
-        for (int sp = first_split; sp <= last_split; sp++) l += ml[sp * 2 + 1] * expf(ml[sp * 2] - m);
-        const float inv = 1.0f / l;
-        const volatile float* po = part_o + ((size_t)zi * nh + h0 + h) * max_splits * hd;
-        for (int d = tid; d < hd; d += DEC_THREADS) {
-            float o = 0.0f;
-            for (int sp = first_split; sp <= last_split; sp++) o += po[(size_t)sp * hd + d] * expf(ml[sp * 2] - m);
-            out[((size_t)t * nh + h0 + h) * hd + d] = from_f32<T>(o * inv);
+        for (int j = 0; j < n_active; j++) {
+            const float e = expf(red[tid * n_active + j] - m);
+            l += wsp[tid * DEC_SPLIT + j] * e;
+            wsp[tid * DEC_SPLIT + j] = e;
         }
+        stat_l[tid] = 1.0f / l;
+    }
+    __syncthreads();
+    for (int i = tid; i < gt * hd; i += DEC_THREADS) {
+        const int h = i / hd, d = i % hd;
+        const float* po = part_o + (((size_t)zi * nh + h0 + h) * max_splits + first_split) * hd + d;
+        float o = 0.0f;
+        int j = 0;
+        for (; j + 4 <= n_active; j += 4) {
+            const float a0 = __ldcg(po + (size_t)j * hd), a1 = __ldcg(po + (size_t)(j + 1) * hd);
+            const float a2 = __ldcg(po + (size_t)(j + 2) * hd), a3 = __ldcg(po + (size_t)(j + 3) * hd);
+            o += a0 * wsp[h * DEC_SPLIT + j];
+            o += a1 * wsp[h * DEC_SPLIT + j + 1];
+            o += a2 * wsp[h * DEC_SPLIT + j + 2];
+            o += a3 * wsp[h * DEC_SPLIT + j + 3];
+        }
+        for (; j < n_active; j++) o += __ldcg(po + (size_t)j * hd) * wsp[h * DEC_SPLIT + j];
+        out[((size_t)t * nh + h0 + h) * hd + d] = from_f32<T>(o * stat_l[h]);
     }
 }
 
@@ -231,7 +289,8 @@ VK_API int vk_attention_decode(const void* q, const void* cache, const int32_t* 
         return VK_BAD_SHAPE;
     const int vec = dtype == 0 ? 4 : 8;
     if (hd % vec != 0) return VK_BAD_SHAPE;
-    if (hd > DEC_MAX_HD || hd / vec > 32 || n_tokens > scratch_tokens || n_tokens > 65535) return VK_TOO_LARGE;
+    if (hd > DEC_MAX_HD || hd / vec > 32 || n_tokens > scratch_tokens || n_tokens > 65535 || max_context > 128 * DEC_SPLIT)
+        return VK_TOO_LARGE;
     if (((uintptr_t)cache % 16) || ((uintptr_t)scratch % 16) || ((uintptr_t)q % 4)) return VK_BAD_ALIGNMENT;
     const int splits = (max_context + DEC_SPLIT - 1) / DEC_SPLIT;
     const int grid_splits = (grid_context + DEC_SPLIT - 1) / DEC_SPLIT;

@@ -57,18 +57,51 @@ __device__ __forceinline__ void unit_rows(const SkinnyParams& p, int u, int& r0,
 }
 
 // Stage rows m0 .. m0+mrows of x, columns kb .. kb+kn, into xs [SK_ROWS][kc].  Called by the whole block.
+// Warp w copies rows w, w+8, ...: 16-byte loads, several in flight, so that staging costs about one
+// trip to memory.  With NORM the row is float32, scaled by inv_rms[row] * norm_w and rounded to T.
+template <typename T> __device__ __forceinline__ void store4(T* dst, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* dst, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* dst, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 v;
+    v.x = *reinterpret_cast<uint32_t*>(&lo);
+    v.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = v;
+}
+
 template <typename T, bool NORM>
-__device__ __forceinline__ void stage_rows(const SkinnyParams& p, T* xs, const float* inv_rms, int m0, int mrows, int kb, int kn) {
+__device__ __forceinline__ void stage_rows(const SkinnyParams& p, T* xs, const float* inv_rms, int m0, int mrows, int kb, int kn,
+                                           bool vec_ok) {
+    constexpr int V = Vec16<T>::N;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     __syncthreads();
-    for (int m = 0; m < mrows; m++) {
+    for (int m = warp; m < mrows; m += (int)(blockDim.x >> 5)) {
+        T* dst = xs + m * p.kc;
         if (NORM) {
             const int src = p.rows ? p.rows[m0 + m] : m0 + m;
             const float* xr = reinterpret_cast<const float*>(p.x) + (size_t)src * p.ldx + kb;
+            const float* nw = p.norm_w + kb;
             const float inv = inv_rms[m];
-            for (int k = threadIdx.x; k < kn; k += SK_THREADS) xs[m * p.kc + k] = from_f32<T>((xr[k] * inv) * p.norm_w[kb + k]);
+            if (vec_ok) {
+#pragma unroll 4
+                for (int k = lane * 4; k < kn; k += 128) {
+                    const float4 xv = *reinterpret_cast<const float4*>(xr + k);
+                    const float4 wv = *reinterpret_cast<const float4*>(nw + k);
+                    store4<T>(dst + k, (xv.x * inv) * wv.x, (xv.y * inv) * wv.y, (xv.z * inv) * wv.z, (xv.w * inv) * wv.w);
+                }
+            } else {
+                for (int k = lane; k < kn; k += 32) dst[k] = from_f32<T>((xr[k] * inv) * nw[k]);
+            }
         } else {
             const T* xr = reinterpret_cast<const T*>(p.x) + (size_t)(m0 + m) * p.ldx + kb;
-            for (int k = threadIdx.x; k < kn; k += SK_THREADS) xs[m * p.kc + k] = xr[k];
+            if (vec_ok) {
+#pragma unroll 4
+                for (int k = lane * V; k < kn; k += 32 * V) *reinterpret_cast<uint4*>(dst + k) = *reinterpret_cast<const uint4*>(xr + k);
+            } else {
+                for (int k = lane; k < kn; k += 32) dst[k] = xr[k];
+            }
         }
     }
     __syncthreads();
@@ -78,6 +111,7 @@ template <typename T>
 __device__ __forceinline__ void accumulate(const T* xs, int kc, const T* w0, const T* w1, int kn, int mrows, float* acc0, float* acc1) {
     constexpr int V = Vec16<T>::N;
     const int lane = threadIdx.x & 31;
+#pragma unroll 2
     for (int k = lane * V; k < kn; k += 32 * V) {
         float wf0[V], wf1[V];
         load16<T>(w0 + k, wf0);
@@ -159,27 +193,39 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_linear_kernel(const SkinnyP
     T* xs = reinterpret_cast<T*>(smem_raw);                 // [SK_ROWS][kc]
     __shared__ float inv_rms[SK_ROWS];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    constexpr int WARPS = SK_THREADS / 32;
+    const int WARPS = blockDim.x >> 5;
     const T* __restrict__ W = reinterpret_cast<const T*>(p.w);
     const int K = p.K;
     const int units = (EPI == EPI_SWIGLU) ? p.N / 2 : (p.N + 1) / 2;
+    // 16-byte loads of x need aligned rows (the launcher has checked the weights and K)
+    const bool vec_ok = NORM ? ((reinterpret_cast<uintptr_t>(p.x) % 16 == 0) && (p.ldx % 4 == 0) && (K % 4 == 0) && (p.kc % 4 == 0) &&
+                                (reinterpret_cast<uintptr_t>(p.norm_w) % 16 == 0))
+                             : ((reinterpret_cast<uintptr_t>(p.x) % 16 == 0) && (p.ldx % Vec16<T>::N == 0));
 
     for (int m0 = 0; m0 < p.M; m0 += SK_ROWS) {
         const int mrows = min(SK_ROWS, p.M - m0);
         if (NORM) {
             __syncthreads();             // the previous pass has read inv_rms
-            if (warp < mrows) {          // one warp per row: the sum of squares over the whole row
-                const int src = p.rows ? p.rows[m0 + warp] : m0 + warp;
+            for (int mr = warp; mr < mrows; mr += WARPS) {          // a warp per row: the sum of squares over the whole row
+                const int src = p.rows ? p.rows[m0 + mr] : m0 + mr;
                 const float* xr = reinterpret_cast<const float*>(p.x) + (size_t)src * p.ldx;
                 float ss = 0.0f;
-                for (int k = lane; k < K; k += 32) { const float v = xr[k]; ss = fmaf(v, v, ss); }
+                if (vec_ok) {
+#pragma unroll 4
+                    for (int k = lane * 4; k < K; k += 128) {
+                        const float4 v = *reinterpret_cast<const float4*>(xr + k);
+                        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+                    }
+                } else {
+                    for (int k = lane; k < K; k += 32) { const float v = xr[k]; ss = fmaf(v, v, ss); }
+                }
                 ss = warp_sum(ss);
-                if (lane == 0) inv_rms[warp] = 1.0f / sqrtf(ss / (float)K + p.eps);
+                if (lane == 0) inv_rms[mr] = 1.0f / sqrtf(ss / (float)K + p.eps);
             }
         }
         if (p.kc >= K) {
             // K fits: stage once, then each warp walks over units
-            stage_rows<T, NORM>(p, xs, inv_rms, m0, mrows, 0, K);
+            stage_rows<T, NORM>(p, xs, inv_rms, m0, mrows, 0, K, vec_ok);
             for (int u = blockIdx.x * WARPS + warp; u < units; u += gridDim.x * WARPS) {
                 int r0, r1;
                 unit_rows<EPI>(p, u, r0, r1);
@@ -202,7 +248,7 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_linear_kernel(const SkinnyP
             for (int m = 0; m < SK_ROWS; m++) { acc0[m] = 0.0f; acc1[m] = 0.0f; }
             for (int kb = 0; kb < K; kb += p.kc) {
                 const int kn = min(p.kc, K - kb);
-                stage_rows<T, NORM>(p, xs, inv_rms, m0, mrows, kb, kn);
+                stage_rows<T, NORM>(p, xs, inv_rms, m0, mrows, kb, kn, vec_ok);
                 if (on) accumulate<T>(xs, p.kc, W + (size_t)r0 * K + kb, W + (size_t)(has1 ? r1 : r0) * K + kb, kn, mrows, acc0, acc1);
             }
             if (on) finish_unit<T, EPI>(p, u, r0, r1, has1, m0, mrows, acc0, acc1);
@@ -216,7 +262,9 @@ static int launch_skinny(SkinnyParams p, cudaStream_t stream) {
     const int kc_max = 65536 / (SK_ROWS * (int)sizeof(T));           // 64 KB of shared memory for the staged rows
     p.kc = p.K <= kc_max ? p.K : kc_max;
     const int units = (EPI == EPI_SWIGLU) ? p.N / 2 : (p.N + 1) / 2;
-    const int warps = SK_THREADS / 32;
+    // few units: fewer warps a block, so that the work spreads over the SMs (a block stages x for itself)
+    int warps = (units + 147) / 148;
+    warps = warps < 1 ? 1 : (warps > SK_THREADS / 32 ? SK_THREADS / 32 : warps);
     int blocks = (units + warps - 1) / warps;
     if (p.kc >= p.K && blocks > 148 * 4) blocks = 148 * 4;
     const size_t smem = (size_t)SK_ROWS * p.kc * sizeof(T);
@@ -226,7 +274,7 @@ static int launch_skinny(SkinnyParams p, cudaStream_t stream) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    kern<<<blocks, SK_THREADS, smem, stream>>>(p);
+    kern<<<blocks, 32 * warps, smem, stream>>>(p);
     return launch_status();
 }
 

@@ -1,0 +1,303 @@
+// The few-rows matrix product in bfloat16 on the tensor cores: out[M, N] = x[M, K] * W[N, K]^T, M <= 64,
+// fused with RMSNorm before and with the rotation and cache write, SwiGLU or the residual sum after.
+//
+// Decoding streams every weight once and has almost no arithmetic, so what counts is how few
+// instructions and how few dependent trips to memory a block needs.  One m16n8k16 instruction
+// (weights as the 16-row operand, eight batch rows as the 8-column operand) replaces 64 float32
+// multiply-adds.  A block owns eight "units" (pairs of weight rows, see below) and splits K over its
+// warps; each warp issues all of its 16-byte weight loads before it uses any, the warps' partial sums
+// meet in shared memory in a fixed order, and warp 0 (and others, for more than eight rows) finishes.
+//
+// Within a run of 32 columns lane (g, q) = (lane / 4, lane % 4) loads columns 8q .. 8q+7 of weight
+// rows g and g+8 of the tile, and of batch row g: 16 contiguous bytes each.  The instruction's k index
+// is a permutation of the memory column, the same for both operands, so the dot products are unchanged.
+//
+// Units, as in linear_skinny.cu: SAME / F32 / ACC rows (2u, 2u+1); SWIGLU rows (u, N/2 + u);
+// ROPE the half-split pair (h*hd + j, h*hd + j + hd/2) of a q or k head, or two adjacent rows of v.
+// A tile's rows 0..7 are the first rows of eight units and rows 8..15 their second rows, so a lane
+// holds both values of a pair for two batch rows.
+//
+// Rounding points equal those of the separate kernels (values that would be stored in bfloat16 between
+// two kernels are rounded to it here), and an output does not depend on M or on the other batch rows:
+// the split of K over warps depends on K alone.
+#include "common.cuh"
+
+namespace vk {
+
+enum { ME_SAME = 0, ME_F32 = 1, ME_ACC = 2, ME_SWIGLU = 3, ME_ROPE = 4 };
+constexpr int MM_XPAD = 8;           // elements of padding per staged row (keeps 16-byte loads free of bank conflicts)
+
+struct MmaParams {
+    const void* x;               // NORM: float32 [*, K] rows of stride ldx; else bfloat16 [M, K] rows of stride ldx
+    const int32_t* rows;         // NORM only, optional: input row of each of the M rows
+    const float* norm_w;
+    float eps;
+    const __nv_bfloat16* w;      // [N, K]
+    void* out;
+    int M, N, K, ldx, kc, ks;    // kc: columns staged at a time (a multiple of 32 * ks); ks: warps = splits of K
+    const int32_t* positions;
+    const float* cos_t;
+    const float* sin_t;
+    const int32_t* slot;
+    __nv_bfloat16* cache;
+    int nh, nkv, hd, page_size;
+};
+
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+__device__ __forceinline__ void mma_bf16(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int EPI>
+__device__ __forceinline__ void mma_unit_rows(const MmaParams& p, int u, int& r0, int& r1) {
+    if (EPI == ME_SWIGLU) { r0 = u; r1 = p.N / 2 + u; }
+    else if (EPI == ME_ROPE) {
+        const int half = p.hd / 2, rot_units = (p.nh + p.nkv) * half;
+        if (u < rot_units) { r0 = (u / half) * p.hd + u % half; r1 = r0 + half; }
+        else { r0 = (p.nh + p.nkv) * p.hd + 2 * (u - rot_units); r1 = r0 + 1; }
+    } else { r0 = 2 * u; r1 = 2 * u + 1; }
+}
+
+// One (unit, batch row) pair of sums -> its place.
+template <int EPI>
+__device__ __forceinline__ void mma_finish(const MmaParams& p, int u, int r0, int r1, bool has1, int m, float a0, float a1) {
+    typedef __nv_bfloat16 T;
+    if (EPI == ME_SAME) {
+        T* o = reinterpret_cast<T*>(p.out) + (size_t)m * p.N;
+        o[r0] = __float2bfloat16_rn(a0);
+        if (has1) o[r1] = __float2bfloat16_rn(a1);
+    } else if (EPI == ME_F32) {
+        float* o = reinterpret_cast<float*>(p.out) + (size_t)m * p.N;
+        o[r0] = a0;
+        if (has1) o[r1] = a1;
+    } else if (EPI == ME_ACC) {
+        float* o = reinterpret_cast<float*>(p.out) + (size_t)m * p.N;
+        o[r0] += a0;
+        if (has1) o[r1] += a1;
+    } else if (EPI == ME_SWIGLU) {
+        const float g = bf16_round(a0), up = bf16_round(a1);
+        reinterpret_cast<T*>(p.out)[(size_t)m * (p.N / 2) + u] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * up);
+    } else {
+        const int half = p.hd / 2, rot_units = (p.nh + p.nkv) * half;
+        const int s = p.slot[m];
+        const size_t page = s >= 0 ? (size_t)(s / p.page_size) : 0;
+        const int off = s >= 0 ? s % p.page_size : 0;
+        T* kbase = p.cache + page * 2 * p.nkv * p.page_size * p.hd;
+        if (u < rot_units) {
+            const int h = u / half, j = u % half, pos = p.positions[m];
+            const float c = p.cos_t[(size_t)pos * half + j], sn = p.sin_t[(size_t)pos * half + j];
+            const float a = bf16_round(a0), b = bf16_round(a1);
+            const float ra = a * c - b * sn, rb = b * c + a * sn;
+            if (h < p.nh) {
+                T* qo = reinterpret_cast<T*>(p.out) + (size_t)m * p.nh * p.hd + h * p.hd;
+                qo[j] = __float2bfloat16_rn(ra);
+                qo[j + half] = __float2bfloat16_rn(rb);
+            } else if (s >= 0) {
+                T* dst = kbase + ((size_t)(h - p.nh) * p.page_size + off) * p.hd;
+                dst[j] = __float2bfloat16_rn(ra);
+                dst[j + half] = __float2bfloat16_rn(rb);
+            }
+        } else if (s >= 0) {
+            const int col = 2 * (u - rot_units);
+            T* vbase = kbase + (size_t)p.nkv * p.page_size * p.hd;
+            T* dst = vbase + ((size_t)(col / p.hd) * p.page_size + off) * p.hd + col % p.hd;
+            dst[0] = __float2bfloat16_rn(a0);
+            dst[1] = __float2bfloat16_rn(a1);
+        }
+    }
+}
+
+// MG: groups of eight batch rows (1, 2, 4 or 8).  blockDim.x = 32 * ks.  grid.x = ceil(units / 8).
+template <int EPI, bool NORM, int MG>
+__global__ void __launch_bounds__(256) skinny_mma_kernel(const MmaParams p) {
+    typedef __nv_bfloat16 T;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int xstride = p.kc + MM_XPAD;
+    T* xs = reinterpret_cast<T*>(smem_raw);                                   // [MG*8][kc + pad]
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)MG * 8 * xstride * sizeof(T));   // [ks][MG][32][4]
+    __shared__ float inv_rms[MG * 8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, q = lane & 3;
+    const int K = p.K, ks = p.ks;
+    const int units = (EPI == ME_SWIGLU) ? p.N / 2 : (p.N + 1) / 2;
+
+    // this lane's two weight rows: the first and second row of unit (tile*8 + g)
+    const int u = blockIdx.x * 8 + g;
+    const bool on = u < units;
+    int r0 = 0, r1 = 0;
+    if (on) mma_unit_rows<EPI>(p, u, r0, r1);
+    const bool has1 = on && r1 < p.N;
+    const T* w0 = p.w + (size_t)r0 * K;
+    const T* w1 = p.w + (size_t)(has1 ? r1 : r0) * K;
+
+    if (NORM) {
+        for (int m = warp; m < p.M; m += ks) {          // a warp per row: the sum of squares over the whole row
+            const int src = p.rows ? p.rows[m] : m;
+            const float* xr = reinterpret_cast<const float*>(p.x) + (size_t)src * p.ldx;
+            float ss = 0.0f;
+#pragma unroll 4
+            for (int k = lane * 4; k < K; k += 128) {
+                const float4 v = *reinterpret_cast<const float4*>(xr + k);
+                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) inv_rms[m] = 1.0f / sqrtf(ss / (float)K + p.eps);
+        }
+    }
+
+    float d[MG][4];
+#pragma unroll
+    for (int mg = 0; mg < MG; mg++) { d[mg][0] = d[mg][1] = d[mg][2] = d[mg][3] = 0.0f; }
+
+    for (int kb = 0; kb < K; kb += p.kc) {
+        const int kn = min(p.kc, K - kb);               // a multiple of 32
+        __syncthreads();                                // inv_rms is written; the previous chunk has been read
+        // stage rows 0..M-1 (rows up to MG*8 are zero) of columns kb .. kb+kn
+        for (int m = warp; m < MG * 8; m += ks) {
+            T* dst = xs + m * xstride;
+            if (m >= p.M) {
+                for (int k = lane * 8; k < kn; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
+            } else if (NORM) {
+                const int src = p.rows ? p.rows[m] : m;
+                const float* xr = reinterpret_cast<const float*>(p.x) + (size_t)src * p.ldx + kb;
+                const float* nw = p.norm_w + kb;
+                const float inv = inv_rms[m];
+#pragma unroll 4
+                for (int k = lane * 4; k < kn; k += 128) {
+                    const float4 xv = *reinterpret_cast<const float4*>(xr + k);
+                    const float4 wv = *reinterpret_cast<const float4*>(nw + k);
+                    __nv_bfloat162 lo = __floats2bfloat162_rn((xv.x * inv) * wv.x, (xv.y * inv) * wv.y);
+                    __nv_bfloat162 hi = __floats2bfloat162_rn((xv.z * inv) * wv.z, (xv.w * inv) * wv.w);
+                    uint2 v;
+                    v.x = *reinterpret_cast<uint32_t*>(&lo);
+                    v.y = *reinterpret_cast<uint32_t*>(&hi);
+                    *reinterpret_cast<uint2*>(dst + k) = v;
+                }
+            } else {
+                const T* xr = reinterpret_cast<const T*>(p.x) + (size_t)m * p.ldx + kb;
+#pragma unroll 4
+                for (int k = lane * 8; k < kn; k += 256) *reinterpret_cast<uint4*>(dst + k) = *reinterpret_cast<const uint4*>(xr + k);
+            }
+        }
+        __syncthreads();
+        // this warp's share of the chunk: the runs of 32 columns whose index is warp modulo ks.  A chunk starts
+        // at a multiple of 32 * ks, so which warp adds a run, and in which order, depends on K alone.
+        const int nblk = kn / 32;
+        constexpr int UN = 4;                           // runs in flight: 8 weight loads of 16 bytes per lane
+        for (int b = warp; b < nblk; b += UN * ks) {
+            uint4 wr[UN], ws[UN];
+#pragma unroll
+            for (int i = 0; i < UN; i++) {
+                if (b + i * ks < nblk) {
+                    const int col = kb + (b + i * ks) * 32 + q * 8;
+                    wr[i] = __ldg(reinterpret_cast<const uint4*>(w0 + col));
+                    ws[i] = __ldg(reinterpret_cast<const uint4*>(w1 + col));
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < UN; i++) {
+                if (b + i * ks < nblk) {
+#pragma unroll
+                    for (int mg = 0; mg < MG; mg++) {
+                        const uint4 xv = *reinterpret_cast<const uint4*>(xs + (mg * 8 + g) * xstride + (b + i * ks) * 32 + q * 8);
+                        mma_bf16(d[mg], wr[i].x, ws[i].x, wr[i].y, ws[i].y, xv.x, xv.y);
+                        mma_bf16(d[mg], wr[i].z, ws[i].z, wr[i].w, ws[i].w, xv.z, xv.w);
+                    }
+                }
+            }
+        }
+    }
+    // partial sums of the warps meet in shared memory; warp w then finishes the row groups w, w+ks, ...
+#pragma unroll
+    for (int mg = 0; mg < MG; mg++)
+        *reinterpret_cast<float4*>(red + (((size_t)warp * MG + mg) * 32 + lane) * 4) = make_float4(d[mg][0], d[mg][1], d[mg][2], d[mg][3]);
+    __syncthreads();
+    for (int mg = warp; mg < MG; mg += ks) {
+        float4 s = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int w = 0; w < ks; w++) {
+            const float4 v = *reinterpret_cast<const float4*>(red + (((size_t)w * MG + mg) * 32 + lane) * 4);
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        if (!on) continue;
+        // lane (g, q): unit u; batch rows mg*8 + 2q and + 1; s.x, s.y are row r0's sums, s.z, s.w row r1's
+        const int m = mg * 8 + 2 * q;
+        if (m < p.M) mma_finish<EPI>(p, u, r0, r1, has1, m, s.x, s.z);
+        if (m + 1 < p.M) mma_finish<EPI>(p, u, r0, r1, has1, m + 1, s.y, s.w);
+    }
+}
+
+template <int EPI, bool NORM>
+static int launch_mma(MmaParams p, cudaStream_t stream) {
+    const int mg = p.M <= 8 ? 1 : p.M <= 16 ? 2 : p.M <= 32 ? 4 : 8;
+    const int nblk = p.K / 32;
+    // warps that split K (K alone decides): between 4 and 8 if that divides the runs of 32 columns evenly,
+    // else as many as leave a warp at least two runs
+    int ks = 0;
+    for (int cand = 8; cand >= 4 && !ks; cand--)
+        if (nblk % cand == 0) ks = cand;
+    if (!ks) { ks = 8; while (ks > 1 && nblk / ks < 2) ks--; }
+    p.ks = ks;
+    // columns staged at a time: all of K if the rows fit in 160 KB, else the largest multiple of 32*ks that does
+    const int rows = mg * 8;
+    int kc = p.K;
+    const int fit = (163840 / (rows * 2) - MM_XPAD) / (32 * ks) * (32 * ks);
+    if (kc > fit) kc = fit;
+    if (kc <= 0) return VK_TOO_LARGE;
+    p.kc = kc;
+    const int units = (EPI == ME_SWIGLU) ? p.N / 2 : (p.N + 1) / 2;
+    const int blocks = (units + 7) / 8;
+    const size_t smem = (size_t)rows * (kc + MM_XPAD) * 2 + (size_t)ks * mg * 32 * 4 * sizeof(float);
+#define LAUNCH(MGV)                                                                                                         \
+    {                                                                                                                       \
+        auto kern = skinny_mma_kernel<EPI, NORM, MGV>;                                                                      \
+        if (smem > 48 * 1024) {                                                                                             \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);             \
+            if (e != cudaSuccess) return (int)e;                                                                            \
+        }                                                                                                                   \
+        kern<<<blocks, 32 * ks, smem, stream>>>(p);                                                                         \
+    }
+    if (mg == 1) LAUNCH(1) else if (mg == 2) LAUNCH(2) else if (mg == 4) LAUNCH(4) else LAUNCH(8)
+#undef LAUNCH
+    return launch_status();
+}
+
+template <bool NORM>
+static int mma_dispatch(int epi, const MmaParams& p, cudaStream_t stream) {
+    switch (epi) {
+        case ME_SAME: return launch_mma<ME_SAME, NORM>(p, stream);
+        case ME_F32: return launch_mma<ME_F32, NORM>(p, stream);
+        case ME_ACC: return launch_mma<ME_ACC, NORM>(p, stream);
+        case ME_SWIGLU: return launch_mma<ME_SWIGLU, NORM>(p, stream);
+        case ME_ROPE: return launch_mma<ME_ROPE, NORM>(p, stream);
+    }
+    return VK_BAD_SHAPE;
+}
+
+}  // namespace vk
+
+using namespace vk;
+
+// The bfloat16 few-rows product on tensor cores.  Arguments as vk_linear_skinny; in addition K must be a
+// multiple of 32, and with the fused norm x's rows must be 16-byte aligned (ldx a multiple of 4).
+VK_API int vk_linear_skinny_mma(const void* x, const int32_t* rows, const float* norm_w, float eps, const void* w, void* out,
+                                int M, int N, int K, int ldx, int epi, const int32_t* positions, const float* cos_t,
+                                const float* sin_t, const int32_t* slot, void* cache, int nh, int nkv, int hd, int page_size,
+                                cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return VK_OK;
+    if (K <= 0 || ldx < K || epi < 0 || epi > 4 || K % 32 != 0) return VK_BAD_SHAPE;
+    if (M > 64) return VK_TOO_LARGE;
+    if (((uintptr_t)w % 16) || ((uintptr_t)x % 16)) return VK_BAD_ALIGNMENT;
+    if (norm_w ? (ldx % 4 != 0 || ((uintptr_t)norm_w % 16)) : (ldx % 8 != 0)) return VK_BAD_ALIGNMENT;
+    if (epi == ME_SWIGLU && (N % 2)) return VK_BAD_SHAPE;
+    if (epi == ME_ROPE) {
+        if (nh <= 0 || nkv <= 0 || hd <= 0 || (hd % 2) || page_size <= 0 || N != (nh + 2 * nkv) * hd || !positions || !cos_t || !sin_t ||
+            !slot || !cache)
+            return VK_BAD_SHAPE;
+    }
+    MmaParams p{x, rows, norm_w, eps, (const __nv_bfloat16*)w, out, M, N, K, ldx, 0, 0, positions, cos_t, sin_t, slot,
+                (__nv_bfloat16*)cache, nh, nkv, hd, page_size};
+    return norm_w ? mma_dispatch<true>(epi, p, stream) : mma_dispatch<false>(epi, p, stream);
+}

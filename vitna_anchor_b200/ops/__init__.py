@@ -187,10 +187,10 @@ def attention_decode_scratch_bytes(tokens: int, nh: int, nkv: int, hd: int, max_
     return int(fn(tokens, nh, nkv, hd, max_context))
 
 
-def attention_decode_takes(dtype: torch.dtype, hd: int) -> bool:
-    """Whether the split-key decode kernel takes this head size (else attention_rows does the work)."""
+def attention_decode_takes(dtype: torch.dtype, hd: int, max_context: int = 0) -> bool:
+    """Whether the split-key decode kernel takes this head size and context (else attention_rows does the work)."""
     vec = 4 if dtype == torch.float32 else 8
-    return hd % vec == 0 and hd <= 256 and hd // vec <= 32
+    return hd % vec == 0 and hd <= 256 and hd // vec <= 32 and max_context <= 128 * 256
 
 
 def attention_decode(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: torch.Tensor, token_seg: torch.Tensor,
@@ -276,7 +276,8 @@ def skinny_takes(dtype: torch.dtype, M: int, K: int) -> bool:
 
 
 def linear_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, *, norm_weight: Optional[torch.Tensor] = None,
-                  eps: float = 0.0, rows: Optional[torch.Tensor] = None, rope: Optional[tuple] = None) -> torch.Tensor:
+                  eps: float = 0.0, rows: Optional[torch.Tensor] = None, rope: Optional[tuple] = None,
+                  force_simt: bool = False) -> torch.Tensor:
     """out = epilogue(x' @ w.T) for at most 64 rows, where x' is x, or rmsnorm(x[rows]) * norm_weight when
     norm_weight is given (x float32 then).  epi: EPI_SAME / EPI_F32 / EPI_ACC as LINEAR_*; EPI_SWIGLU: out [M, N/2] =
     silu(first half) * second half; EPI_ROPE: out = rotated q [M, nh*hd], rotated k and v go into the cache;
@@ -315,6 +316,13 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int,
     _req(out, "out", want[epi][1], 2)
     if tuple(out.shape) != want[epi][0]:
         raise KernelError(f"linear_skinny: out is {tuple(out.shape)}, expected {want[epi][0]}")
+    if (w.dtype == torch.bfloat16 and K % 32 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and not force_simt
+            and (ldx % 4 == 0 and norm_weight.data_ptr() % 16 == 0 if norm_weight is not None else ldx % 8 == 0)):
+        # bfloat16: the tensor-core kernel
+        _check(lib().vk_linear_skinny_mma(_p(x), _p(rows), _p(norm_weight), ctypes.c_float(eps), _p(w), _p(out), M, N, K, ldx,
+                                          epi, _p(pos), _p(cos), _p(sin), _p(slot), _p(cache), nh, nkv, hd, ps, _stream()),
+               "linear_skinny_mma")
+        return out
     _check(lib().vk_linear_skinny(_p(x), _p(rows), _p(norm_weight), ctypes.c_float(eps), _p(w), _p(out), M, N, K, ldx, epi,
                                   _p(pos), _p(cos), _p(sin), _p(slot), _p(cache), nh, nkv, hd, ps, _dt(w), _stream()),
            "linear_skinny")
@@ -337,7 +345,7 @@ def attention(q: torch.Tensor, pages: torch.Tensor, meta, ctx, out: torch.Tensor
               scale: float, window: int = 0) -> torch.Tensor:
     """Causal attention of a mixed batch over the paged cache; `meta` is the page group's GroupMeta.
     Single decoded tokens take the split-key kernel; tokens of prompt portions take attention_rows."""
-    if ctx.num_dec and attention_decode_takes(q.dtype, hd):
+    if ctx.num_dec and attention_decode_takes(q.dtype, hd, ctx.workspace.max_context):
         ws = ctx.workspace
         cap, layout = ws.max_segments, ws.max_context
         nbytes = attention_decode_scratch_bytes(cap, nh, nkv, hd, layout)
