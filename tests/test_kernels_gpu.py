@@ -425,3 +425,33 @@ def test_linear_skinny_rope_store_matches_the_separate_kernels(ops, dtype, nh, n
     assert (q_a.float() - q_b.float()).abs().max() <= t
     assert (cache_a.float() - cache_b.float()).abs().max() <= t
     assert torch.equal(cache_a == 7.0, cache_b == 7.0)        # the same slots were written, no others
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 64, 64), (128, 128, 576), (2048, 960, 576), (300, 576, 1536), (65, 200, 72), (1000, 3072, 576),
+                                   (257, 49152, 576), (130, 72, 200)])
+def test_linear_tcgen05(ops, M, N, K):
+    """The tcgen05 product against float64, and against the CUDA-core kernel (same exact products, float32 sums)."""
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K) / math.sqrt(K)).to(torch.bfloat16).cuda()
+    want = x.double() @ w.double().T
+    scale = float(want.abs().max())
+    f32 = torch.full((M, N), 7.0, device="cuda")
+    ops.linear_tcgen05(x, w, f32, ops.LINEAR_F32)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    assert (f32.double() - want).abs().max() <= 2e-5 * scale
+    same = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ops.linear_tcgen05(x, w, same, ops.LINEAR_SAME)
+    assert (same.double() - want).abs().max() <= 1e-2 * scale
+    acc = torch.ones(M, N, device="cuda")
+    ops.linear_tcgen05(x, w, acc, ops.LINEAR_ACC_F32)
+    assert (acc.double() - 1 - want).abs().max() <= 2e-5 * scale
+    part = torch.empty(3, N, device="cuda")                  # rows alone (another tile position) give the same bits
+    xs = torch.zeros(131, K, dtype=torch.bfloat16, device="cuda")
+    xs[128:131] = x[M - 3:M]
+    big = torch.empty(131, N, device="cuda")
+    ops.linear_tcgen05(xs, w, big, ops.LINEAR_F32)
+    assert torch.equal(big[128:131], f32[M - 3:M])
+    torch.cuda.synchronize()
+    ops.check_device_errors()

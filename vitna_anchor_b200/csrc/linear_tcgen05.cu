@@ -1,0 +1,296 @@
+// Prompt-sized matrix products in bfloat16 on the fifth-generation tensor cores:
+// out[M, N] = x[M, K] * W[N, K]^T, float32 accumulation in tensor memory.
+//
+// One block computes a 128 x BN tile of the output.  Warp 0 (one lane) feeds a ring of shared-memory
+// stages with TMA (cp.async.bulk.tensor, 128-byte swizzle, out-of-range rows and columns read as zero);
+// warp 1 (one lane) issues tcgen05.mma (M = 128, N = BN, K = 16 per instruction, both operands K-major)
+// into a BN-column accumulator in tensor memory and releases stages with tcgen05.commit; warps 2-5 read
+// the accumulator with tcgen05.ld, each its own 32 lanes, and store it: as bfloat16, as float32, or
+// added into a float32 output (the residual sum).  No cluster, no multicast: every block loads its own
+// tiles.  Each output element's sum runs over K in the same order whatever M is, so a row's result does
+// not depend on the batch.
+//
+// Every wait on an mbarrier is bounded: after about a second a waiter sets *error (a word the host can
+// read), the block stops issuing work, lets its copies land, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace vk {
+
+constexpr int TC_BM = 128, TC_BK = 64, TC_STAGES = 4, TC_THREADS = 192;
+constexpr unsigned long long TC_WAIT_CYCLES = 2000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity.  False: gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    const long long start = clock64();
+    for (;;) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((unsigned long long)(clock64() - start) > TC_WAIT_CYCLES) return false;
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // start address
+    d |= (uint64_t)1 << 16;                               // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset: 8 rows * 128 bytes
+    d |= (uint64_t)1 << 46;                               // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                               // 128-byte swizzle
+    return d;
+}
+
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M x N.
+__device__ __forceinline__ uint32_t umma_idesc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
+        "%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+enum { TC_SAME = 0, TC_F32 = 1, TC_ACC = 2 };
+
+// A bounded wait ran out: tell the block and the host (error may be a mapped host word: a plain store).
+__device__ __forceinline__ void give_up(int* error, int* failed, int code) {
+    *reinterpret_cast<volatile int*>(failed) = 1;
+    *reinterpret_cast<volatile int*>(error) = code;
+    __threadfence_system();
+}
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                                    const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
+                                                                    int M, int N, int K, int* error) {
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + TC_STAGES * STAGE_BYTES);
+    uint64_t* empty = full + TC_STAGES;
+    uint64_t* acc_full = empty + TC_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+
+    __shared__ int failed;                // set when a bounded wait of this block ran out
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        failed = 0;
+        for (int s = 0; s < TC_STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // producer: fill a stage as soon as the tensor core has released it
+            for (int kb = 0; kb < num_kb; kb++) {
+                const int s = kb % TC_STAGES;
+                if (kb >= TC_STAGES && !mbar_wait(&empty[s], ((kb / TC_STAGES) & 1) ^ 1)) { give_up(error, &failed, 1); break; }
+                mbar_expect_tx(&full[s], STAGE_BYTES);
+                tma_load_2d(smem + s * STAGE_BYTES, &map_x, kb * TC_BK, m0, &full[s]);
+                tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &map_w, kb * TC_BK, n0, &full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < num_kb && ok; kb++) {
+                const int s = kb % TC_STAGES;
+                if (!mbar_wait(&full[s], (kb / TC_STAGES) & 1)) { give_up(error, &failed, 2); ok = false; break; }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; k++) {
+                    umma_bf16(tmem_base, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32), idesc, (kb | k) != 0);
+                }
+                umma_commit(&empty[s]);           // arrives when the instructions above have read the stage
+            }
+            umma_commit(acc_full);                // arrives when every instruction has written the accumulator
+        }
+    } else {
+        // epilogue: warp w reads lanes 32*(w%4) .. +31 of the accumulator, one output row per thread
+        const int quarter = warp & 3;
+        const int row = m0 + quarter * 32 + lane;
+        if (!mbar_wait(acc_full, 0)) {
+            if (lane == 0) give_up(error, &failed, 3);
+        } else {
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                __syncwarp();
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + c, r);
+                const int col = n0 + c;
+                const bool whole = col + 32 <= N;
+                if (row >= M || col >= N) {
+                    // nothing of this thread's to store
+                } else if (EPI == TC_SAME) {
+                    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + col;
+                    if (whole && (N % 8 == 0)) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint4 v;
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                            v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
+                            v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
+                            *reinterpret_cast<uint4*>(o + j) = v;
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && col + j < N; j++) o[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                    }
+                } else {
+                    float* o = reinterpret_cast<float*>(out) + (size_t)row * N + col;
+                    if (whole && (N % 4 == 0)) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                                   __uint_as_float(r[j + 3]));
+                            if (EPI == TC_ACC) {
+                                const float4 old = *reinterpret_cast<const float4*>(o + j);
+                                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                            }
+                            *reinterpret_cast<float4*>(o + j) = v;
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && col + j < N; j++) {
+                            if (EPI == TC_ACC) o[j] += __uint_as_float(r[j]);
+                            else o[j] = __uint_as_float(r[j]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (failed) __nanosleep(200000);      // after a failed wait: let copies in flight land
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// A [rows, cols] bfloat16 matrix with row stride ld (elements), read in boxes of box_rows x 64 columns.
+static bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int EPI>
+static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int M, int N, int K, int* error, cudaStream_t stream) {
+    const size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + 128;
+    auto kern = linear_tcgen05_kernel<BN, EPI>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
+    kern<<<grid, TC_THREADS, smem, stream>>>(mx, mw, out, M, N, K, error);
+    return launch_status();
+}
+
+}  // namespace vk
+
+using namespace vk;
+
+// x [M, K] bfloat16 with row stride ldx, w [N, K] bfloat16, out [M, N]: mode 0 bfloat16, 1 float32, 2 float32 +=.
+// K and ldx multiples of 8, pointers 16-byte aligned.  error: a word the kernel sets (non-zero) if a bounded wait ran out.
+VK_API int vk_linear_tcgen05(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int mode, int* error,
+                             cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return VK_OK;
+    if (K <= 0 || ldx < K || mode < 0 || mode > 2 || !error) return VK_BAD_SHAPE;
+    if (K % 8 != 0 || ldx % 8 != 0) return VK_BAD_SHAPE;
+    if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)out % 16)) return VK_BAD_ALIGNMENT;
+    const int bn = N >= 2048 ? 128 : 64;
+    if ((M + TC_BM - 1) / TC_BM > 65535) return VK_TOO_LARGE;
+    CUtensorMap mx, mw;
+    if (!make_map(&mx, x, M, K, ldx, TC_BM) || !make_map(&mw, w, N, K, K, bn)) return VK_BAD_SHAPE;
+#define GO(BN, EPI) return launch_tc<BN, EPI>(mx, mw, out, M, N, K, error, stream)
+    if (bn == 128) {
+        if (mode == 0) GO(128, TC_SAME);
+        if (mode == 1) GO(128, TC_F32);
+        GO(128, TC_ACC);
+    }
+    if (mode == 0) GO(64, TC_SAME);
+    if (mode == 1) GO(64, TC_F32);
+    GO(64, TC_ACC);
+#undef GO
+}

@@ -266,6 +266,45 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Te
     return out
 
 
+_error_word = None
+
+
+def error_word() -> torch.Tensor:
+    """A pinned host word that kernels with bounded waits set when a wait runs out (the device writes it
+    through the mapped address; the host reads it for free after any synchronisation)."""
+    global _error_word
+    if _error_word is None:
+        _error_word = torch.zeros(1, dtype=torch.int32).pin_memory()
+    return _error_word
+
+
+def check_device_errors() -> None:
+    """Raise if a kernel gave up a bounded wait since the last check (call after a synchronisation)."""
+    if _error_word is not None and int(_error_word[0]) != 0:
+        code = int(_error_word[0])
+        _error_word[0] = 0
+        raise KernelError(f"a kernel gave up waiting on an mbarrier (code {code}); its results are not valid")
+
+
+def tcgen05_takes(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tcgen05 product takes these operands (bfloat16, K and the row stride multiples of 8, aligned)."""
+    return (x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def linear_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> torch.Tensor:
+    """out (=, or += in mode 2) x @ w.T in bfloat16 on the tcgen05 tensor cores, float32 accumulation in tensor memory."""
+    if not tcgen05_takes(x, w):
+        raise KernelError("linear_tcgen05: operands must be bfloat16, 16-byte aligned, with K and the row stride multiples of 8")
+    _req(w, "w", torch.bfloat16, 2); _req(out, "out", torch.bfloat16 if mode == LINEAR_SAME else torch.float32, 2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"linear: shapes x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
+    _check(lib().vk_linear_tcgen05(_p(x), _p(w), _p(out), M, N, K, x.stride(0), mode, _p(error_word()), _stream()), "linear_tcgen05")
+    return out
+
+
 EPI_SAME, EPI_F32, EPI_ACC, EPI_SWIGLU, EPI_ROPE = 0, 1, 2, 3, 4
 SKINNY_MAX_ROWS = 64
 
@@ -338,6 +377,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> to
     (no reduced-precision matrix mode); bfloat16 runs the tensor-core kernel where it takes the sizes."""
     if skinny_takes(x.dtype, x.shape[0], x.shape[1]) and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
         return linear_skinny(x, w, out, mode)
+    if tcgen05_takes(x, w) and out.data_ptr() % 16 == 0:
+        return linear_tcgen05(x, w, out, mode)
     return linear_simt(x, w, out, mode)
 
 
