@@ -455,3 +455,51 @@ def test_linear_tcgen05(ops, M, N, K):
     assert torch.equal(big[128:131], f32[M - 3:M])
     torch.cuda.synchronize()
     ops.check_device_errors()
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(4, 2, 16, 4, 0), (3, 1, 32, 8, 0), (9, 3, 64, 16, 0), (6, 2, 96, 16, 0), (4, 1, 128, 16, 0),
+                                                 (4, 2, 16, 4, 5), (3, 3, 64, 16, 70), (2, 1, 64, 8, 200)])
+def test_attention_prefill_tiles(ops, nh, nkv, hd, ps, window):
+    """Prompt portions on the tensor cores: a whole prompt of 150 tokens, a portion of 37 tokens in mid-request
+    (positions 103..139, across a boundary of 64), a portion of 2 tokens far into a context, and a portion that
+    starts exactly at a multiple of 64.  Sharp scores; against the plain attention and against attention_rows."""
+    rng = np.random.default_rng(6)
+    lens = [150, 140, 601, 128 + 70]         # context after the step
+    news = [150, 37, 2, 70]                  # tokens of this step
+    dtype = torch.bfloat16
+    pages = sum(-(-n // ps) for n in lens) + 7
+    pool = torch.zeros(pages, 2, nkv, ps, hd, dtype=dtype) + 1000.0
+    free = list(rng.permutation(pages))
+    maxb = max(-(-n // ps) for n in lens)
+    bt = np.zeros((len(lens), maxb), dtype=np.int32)
+    q_all, seg, pos, want, tiles = [], [], [], [], []
+    g = nh // nkv
+    for s, (n, new) in enumerate(zip(lens, news)):
+        k = (rng.standard_normal((n, nkv, hd)) * 1.5).astype(np.float32)
+        v = rng.standard_normal((n, nkv, hd)).astype(np.float32)
+        q = (rng.standard_normal((n, nh, hd)) * 1.5).astype(np.float32)
+        k[3] = q[n - 1, ::g][:nkv] * 2.0               # a far key stands out for the last query
+        k, v, q = (torch.from_numpy(a).to(dtype).float().numpy() for a in (k, v, q))
+        for b in range(-(-n // ps)):
+            bt[s, b] = free.pop()
+        kk = torch.from_numpy(k).to(dtype); vv = torch.from_numpy(v).to(dtype)
+        for p in range(n):
+            pool[bt[s, p // ps], 0, :, p % ps] = kk[p]
+            pool[bt[s, p // ps], 1, :, p % ps] = vv[p]
+        ref = P.causal_attention(q, k, v, window=window or None).reshape(n, nh * hd)
+        start = len(q_all)
+        for o in range(0, new, 64):
+            tiles.append((start + o, min(64, new - o), n - new + o, s))
+        for p in range(n - new, n):
+            q_all.append(q[p].reshape(-1)); seg.append(s); pos.append(p); want.append(ref[p])
+    q_dev = torch.from_numpy(np.stack(q_all)).to(dtype).cuda()
+    out = torch.empty_like(q_dev)
+    ops.attention_prefill(q_dev, pool.cuda(), dev(bt), dev(np.asarray(tiles, np.int32)), out, nh, nkv, hd, 1.0 / math.sqrt(hd), window)
+    want = np.stack(want)
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= 3e-2 * max(1.0, np.abs(want).max())
+    rows = torch.empty_like(q_dev)
+    ops.attention_rows(q_dev, pool.cuda(), dev(bt), dev(np.array(seg, np.int32)), dev(np.array(pos, np.int32)), rows, nh, nkv, hd,
+                       1.0 / math.sqrt(hd), window)
+    assert (rows.float() - out.float()).abs().max() <= 3e-2 * max(1.0, np.abs(want).max())

@@ -74,7 +74,7 @@ class ModelRunner:
         self.max_segments = max_requests
         n_groups = len(self.cache.groups)
         most = max(max_batch_tokens, self.max_segments)
-        self._meta_len = 5 * most + 3 * self.max_segments + 1 + n_groups * (most + self.max_segments * self.max_blocks)
+        self._meta_len = 6 * most + 64 + 3 * self.max_segments + 1 + n_groups * (most + self.max_segments * self.max_blocks)
         self._staging = [_Staging(self._meta_len, True) for _ in range(4)]
         self._stage_i = 0
         self._meta_dev = torch.zeros(self._meta_len, dtype=torch.int32, device=self.device)
@@ -172,6 +172,10 @@ class ModelRunner:
         pre = [t for i in range(S) if lens[i] > 1 for t in range(int(seg_starts[i]), int(seg_starts[i + 1]))]
         s_dec = put(np.asarray(dec, dtype=np.int32), len(dec)) if dec else None
         s_pre = put(np.asarray(pre, dtype=np.int32), len(pre)) if pre and dec else None
+        tiles = [(int(seg_starts[i]) + o, min(64, lens[i] - o), first[i] + o, i)
+                 for i in range(S) if lens[i] > 1 for o in range(0, lens[i], 64)]
+        off = (off + 3) & ~3                                   # 16-byte alignment for what follows
+        s_tiles = put(np.asarray(tiles, dtype=np.int32).reshape(-1), 4 * len(tiles)) if tiles else None
         group_slices = []
         for g in range(len(self.cache.groups)):
             bt = np.zeros((S, maxb), dtype=np.int32)
@@ -197,7 +201,8 @@ class ModelRunner:
             caches=self.cache.views, workspace=self.workspace, host_seg_lens=lens, host_seg_first_pos=first,
             host_seg_slots=slots, max_seg_len=max(lens), max_context=max(context), decode_only=all(n == 1 for n in lens),
             num_dec=len(dec), dec_tokens=None if (s_dec is None or not pre) else dev[s_dec],
-            num_pre=len(pre), pre_tokens=None if s_pre is None else dev[s_pre])
+            num_pre=len(pre), pre_tokens=None if s_pre is None else dev[s_pre],
+            pre_tiles=None if s_tiles is None else dev[s_tiles].view(-1, 4))
         return ctx, (dev[s_rows] if R else None)
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:

@@ -382,19 +382,47 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> to
     return linear_simt(x, w, out, mode)
 
 
+PREFILL_HEAD_SIZES = (16, 32, 64, 96, 128)
+
+
+def attention_prefill(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: torch.Tensor, tiles: torch.Tensor,
+                      out: torch.Tensor, nh: int, nkv: int, hd: int, scale: float, window: int = 0) -> torch.Tensor:
+    """Causal attention of prompt portions in bfloat16 on the tensor cores.  tiles int32 [n, 4]: first token,
+    rows (1..64), position of the first token, segment."""
+    _req(q, "q", torch.bfloat16, 2); _req(cache_layer, "cache_layer", torch.bfloat16, 5)
+    _req(block_tables, "block_tables", torch.int32, 2); _req(tiles, "tiles", torch.int32, 2); _req(out, "out", torch.bfloat16, 2)
+    page_size = cache_layer.shape[3]
+    if q.shape[1] != nh * hd or out.shape != q.shape or tuple(cache_layer.shape[1:]) != (2, nkv, page_size, hd) or tiles.shape[1] != 4:
+        raise KernelError("attention_prefill: shapes do not fit the head counts")
+    if hd not in PREFILL_HEAD_SIZES:
+        raise KernelError(f"attention_prefill: head size {hd} is not one of {PREFILL_HEAD_SIZES}")
+    _check(lib().vk_attention_prefill(_p(q), _p(cache_layer), _p(block_tables), _p(tiles), _p(out), tiles.shape[0], nh, nkv, hd,
+                                      page_size, block_tables.shape[1], ctypes.c_float(scale), window, _stream()),
+           "attention_prefill")
+    return out
+
+
 def attention(q: torch.Tensor, pages: torch.Tensor, meta, ctx, out: torch.Tensor, nh: int, nkv: int, hd: int,
               scale: float, window: int = 0) -> torch.Tensor:
     """Causal attention of a mixed batch over the paged cache; `meta` is the page group's GroupMeta.
-    Single decoded tokens take the split-key kernel; tokens of prompt portions take attention_rows."""
-    if ctx.num_dec and attention_decode_takes(q.dtype, hd, ctx.workspace.max_context):
+    Single decoded tokens take the split-key kernel; tokens of prompt portions take the tensor-core kernel
+    (bfloat16, head sizes it is built for); whatever is left takes attention_rows, which takes every size."""
+    dec_ok = bool(ctx.num_dec) and attention_decode_takes(q.dtype, hd, ctx.workspace.max_context)
+    pre_ok = (bool(ctx.num_pre) and q.dtype == torch.bfloat16 and hd in PREFILL_HEAD_SIZES and ctx.pre_tiles is not None
+              and q.data_ptr() % 16 == 0)
+    if dec_ok:
         ws = ctx.workspace
         cap, layout = ws.max_segments, ws.max_context
         nbytes = attention_decode_scratch_bytes(cap, nh, nkv, hd, layout)
         scratch = ws.flat(f"att.dec/{nh}/{nkv}/{hd}/{layout}", nbytes, torch.uint8, zero=True)
         attention_decode(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, scratch, cap, nh, nkv, hd, scale,
                          layout, min(layout, max(1, ctx.max_context)), window, ctx.dec_tokens)
-        if ctx.num_pre:
-            attention_rows(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, nh, nkv, hd, scale, window,
-                           ctx.pre_tokens)
-        return out
-    return attention_rows(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, nh, nkv, hd, scale, window)
+    if pre_ok:
+        attention_prefill(q, pages, meta.block_tables, ctx.pre_tiles, out, nh, nkv, hd, scale, window)
+    if not dec_ok and not pre_ok:
+        return attention_rows(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, nh, nkv, hd, scale, window)
+    if ctx.num_pre and not pre_ok:
+        attention_rows(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, nh, nkv, hd, scale, window, ctx.pre_tokens)
+    if ctx.num_dec and not dec_ok:
+        attention_rows(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, nh, nkv, hd, scale, window, ctx.dec_tokens)
+    return out

@@ -87,6 +87,9 @@ class StepContext:
     dec_tokens: Optional[torch.Tensor] = None
     num_pre: int = 0
     pre_tokens: Optional[torch.Tensor] = None
+    # segments longer than one token cut into tiles of up to 64 tokens: int32 [n, 4] = first token, rows,
+    # position of the first token, segment
+    pre_tiles: Optional[torch.Tensor] = None
     extra: dict = field(default_factory=dict)
 
 
