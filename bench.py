@@ -209,6 +209,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the prefill")
+    ap.add_argument("--only-prefill", action="store_true", help="run the prefill measurement alone (for profiling)")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "pip cannot install the reference offline: it is a C program with a "
@@ -225,6 +226,12 @@ def main():
     model_dir = model_folder()
     clocks = ClockSampler()
     clocks.start()
+    if a.only_prefill:
+        pf = prefill_run(model_dir, clocks, repeats=3)
+        clocks.stop()
+        print(json.dumps({"prefill": {"value": pf["value"], "tokens": pf["tokens"], "ms": pf["ms"],
+                                      "frac": pf["flops"] / (pf["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12)}}))
+        return 0
     main_run = decode_run(model_dir, a.batch, a.steps, a.warmup, clocks, with_e2e=True)
     points, prefill = {}, None
     if not a.no_points:

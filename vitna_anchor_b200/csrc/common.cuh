@@ -87,4 +87,27 @@ template <> __device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfl
 
 inline int launch_status() { return (int)cudaGetLastError(); }
 
+// Programmatic dependent launch.  A kernel launched with launch_dependent() may start while the kernel before it
+// in the stream is still running; what it does before dependency_wait() must touch only memory that no kernel
+// of the step writes (weights, tables, the step's metadata).  dependency_wait() returns when the kernel before
+// it has finished and its writes are visible; let_dependents_start() allows the kernel after this one to begin
+// its own prologue.  Calling them in a kernel launched the ordinary way does nothing.
+__device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void let_dependents_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline int launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 }  // namespace vk

@@ -63,7 +63,8 @@ __device__ __forceinline__ void mma_unit_rows(const MmaParams& p, int u, int& r0
 
 // One (unit, batch row) pair of sums -> its place.
 template <int EPI>
-__device__ __forceinline__ void mma_finish(const MmaParams& p, int u, int r0, int r1, bool has1, int m, float a0, float a1) {
+__device__ __forceinline__ void mma_finish(const MmaParams& p, int u, int r0, int r1, bool has1, int m, float a0, float a1,
+                                           bool pre, int pre_slot, float pre_cos, float pre_sin, const float* old) {
     typedef __nv_bfloat16 T;
     if (EPI == ME_SAME) {
         T* o = reinterpret_cast<T*>(p.out) + (size_t)m * p.N;
@@ -75,20 +76,25 @@ __device__ __forceinline__ void mma_finish(const MmaParams& p, int u, int r0, in
         if (has1) o[r1] = a1;
     } else if (EPI == ME_ACC) {
         float* o = reinterpret_cast<float*>(p.out) + (size_t)m * p.N;
-        o[r0] += a0;
-        if (has1) o[r1] += a1;
+        o[r0] = (pre ? old[0] : o[r0]) + a0;
+        if (has1) o[r1] = (pre ? old[1] : o[r1]) + a1;
     } else if (EPI == ME_SWIGLU) {
         const float g = bf16_round(a0), up = bf16_round(a1);
         reinterpret_cast<T*>(p.out)[(size_t)m * (p.N / 2) + u] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * up);
     } else {
         const int half = p.hd / 2, rot_units = (p.nh + p.nkv) * half;
-        const int s = p.slot[m];
+        const int s = pre ? pre_slot : p.slot[m];
         const size_t page = s >= 0 ? (size_t)(s / p.page_size) : 0;
         const int off = s >= 0 ? s % p.page_size : 0;
         T* kbase = p.cache + page * 2 * p.nkv * p.page_size * p.hd;
         if (u < rot_units) {
-            const int h = u / half, j = u % half, pos = p.positions[m];
-            const float c = p.cos_t[(size_t)pos * half + j], sn = p.sin_t[(size_t)pos * half + j];
+            const int h = u / half, j = u % half;
+            float c = pre_cos, sn = pre_sin;
+            if (!pre) {
+                const int pos = p.positions[m];
+                c = p.cos_t[(size_t)pos * half + j];
+                sn = p.sin_t[(size_t)pos * half + j];
+            }
             const float a = bf16_round(a0), b = bf16_round(a1);
             const float ra = a * c - b * sn, rb = b * c + a * sn;
             if (h < p.nh) {
@@ -132,6 +138,60 @@ __global__ void __launch_bounds__(256) skinny_mma_kernel(const MmaParams p) {
     const bool has1 = on && r1 < p.N;
     const T* w0 = p.w + (size_t)r0 * K;
     const T* w1 = p.w + (size_t)(has1 ? r1 : r0) * K;
+
+    // The first weights of this warp are asked for before anything that depends on the kernel before this one:
+    // they are most of the wait of a decode layer, and they are nobody's output.
+    constexpr int UN = 4;                               // runs of 32 columns in flight: 8 loads of 16 bytes per lane
+    uint4 wr[UN], ws[UN];
+    {
+        const int nblk0 = min(p.kc, K) / 32;
+#pragma unroll
+        for (int i = 0; i < UN; i++) {
+            if (warp + i * ks < nblk0) {
+                const int col = (warp + i * ks) * 32 + q * 8;
+                wr[i] = __ldg(reinterpret_cast<const uint4*>(w0 + col));
+                ws[i] = __ldg(reinterpret_cast<const uint4*>(w1 + col));
+            }
+        }
+    }
+    // what the first finishing pass of this lane needs besides the sums, also nobody's output
+    const int m_first = warp * 8 + 2 * q;               // rows m_first, m_first + 1 of row group `warp`
+    int pre_slot[2] = {-1, -1}, pre_pos[2] = {0, 0};
+    float pre_cos[2] = {1.0f, 1.0f}, pre_sin[2] = {0.0f, 0.0f};
+    if (EPI == ME_ROPE && on && warp < MG) {
+        const int half = p.hd / 2, rot_units = (p.nh + p.nkv) * half;
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            if (m_first + e < p.M) {
+                pre_slot[e] = p.slot[m_first + e];
+                pre_pos[e] = p.positions[m_first + e];
+            }
+        }
+        if (u < rot_units) {
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                if (m_first + e < p.M) {
+                    pre_cos[e] = p.cos_t[(size_t)pre_pos[e] * half + u % half];
+                    pre_sin[e] = p.sin_t[(size_t)pre_pos[e] * half + u % half];
+                }
+            }
+        }
+    }
+    dependency_wait();
+    let_dependents_start();
+
+    // the values the residual sum adds to (read now, used at the end)
+    float old[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};
+    if (EPI == ME_ACC && on && warp < MG) {
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            if (m_first + e < p.M) {
+                const float* o = reinterpret_cast<const float*>(p.out) + (size_t)(m_first + e) * p.N;
+                old[e][0] = o[r0];
+                if (has1) old[e][1] = o[r1];
+            }
+        }
+    }
 
     if (NORM) {
         for (int m = warp; m < p.M; m += ks) {          // a warp per row: the sum of squares over the whole row
@@ -186,15 +246,15 @@ __global__ void __launch_bounds__(256) skinny_mma_kernel(const MmaParams p) {
         // this warp's share of the chunk: the runs of 32 columns whose index is warp modulo ks.  A chunk starts
         // at a multiple of 32 * ks, so which warp adds a run, and in which order, depends on K alone.
         const int nblk = kn / 32;
-        constexpr int UN = 4;                           // runs in flight: 8 weight loads of 16 bytes per lane
         for (int b = warp; b < nblk; b += UN * ks) {
-            uint4 wr[UN], ws[UN];
+            if (kb != 0 || b != warp) {                 // the first batch of the first chunk is already on its way
 #pragma unroll
-            for (int i = 0; i < UN; i++) {
-                if (b + i * ks < nblk) {
-                    const int col = kb + (b + i * ks) * 32 + q * 8;
-                    wr[i] = __ldg(reinterpret_cast<const uint4*>(w0 + col));
-                    ws[i] = __ldg(reinterpret_cast<const uint4*>(w1 + col));
+                for (int i = 0; i < UN; i++) {
+                    if (b + i * ks < nblk) {
+                        const int col = kb + (b + i * ks) * 32 + q * 8;
+                        wr[i] = __ldg(reinterpret_cast<const uint4*>(w0 + col));
+                        ws[i] = __ldg(reinterpret_cast<const uint4*>(w1 + col));
+                    }
                 }
             }
 #pragma unroll
@@ -224,8 +284,9 @@ __global__ void __launch_bounds__(256) skinny_mma_kernel(const MmaParams p) {
         if (!on) continue;
         // lane (g, q): unit u; batch rows mg*8 + 2q and + 1; s.x, s.y are row r0's sums, s.z, s.w row r1's
         const int m = mg * 8 + 2 * q;
-        if (m < p.M) mma_finish<EPI>(p, u, r0, r1, has1, m, s.x, s.z);
-        if (m + 1 < p.M) mma_finish<EPI>(p, u, r0, r1, has1, m + 1, s.y, s.w);
+        const bool first = mg == warp;                  // this pass has its extras in registers already
+        if (m < p.M) mma_finish<EPI>(p, u, r0, r1, has1, m, s.x, s.z, first, pre_slot[0], pre_cos[0], pre_sin[0], old[0]);
+        if (m + 1 < p.M) mma_finish<EPI>(p, u, r0, r1, has1, m + 1, s.y, s.w, first, pre_slot[1], pre_cos[1], pre_sin[1], old[1]);
     }
 }
 
@@ -257,7 +318,8 @@ static int launch_mma(MmaParams p, cudaStream_t stream) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);             \
             if (e != cudaSuccess) return (int)e;                                                                            \
         }                                                                                                                   \
-        kern<<<blocks, 32 * ks, smem, stream>>>(p);                                                                         \
+        const int rc = launch_dependent(kern, dim3(blocks), dim3(32 * ks), smem, stream, p);                                \
+        if (rc != 0) return rc;                                                                                             \
     }
     if (mg == 1) LAUNCH(1) else if (mg == 2) LAUNCH(2) else if (mg == 4) LAUNCH(4) else LAUNCH(8)
 #undef LAUNCH
