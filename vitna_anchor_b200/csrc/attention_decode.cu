@@ -30,7 +30,13 @@ constexpr int DEC_SPLIT = 256;     // keys per block: one per thread in the scor
 constexpr int DEC_G_TILE = 8;      // query heads of a group handled by one block
 constexpr int DEC_MAX_HD = 256;
 
-template <typename T>
+__device__ __forceinline__ void dec_cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+// ASYNC: the split's keys and values are first copied into shared memory with cp.async, all of them at once
+// (one trip to memory for both), and the two phases read them there; otherwise the phases read global memory.
+template <typename T, bool ASYNC>
 __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
     const T* __restrict__ q, const T* __restrict__ cache, const int32_t* __restrict__ block_tables,
     const int32_t* __restrict__ token_seg, const int32_t* __restrict__ positions, const int32_t* __restrict__ tok_list,
@@ -59,25 +65,44 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
     float* qs = smem;                                  // [G_TILE][hd]
     float* ps = qs + DEC_G_TILE * hd;                  // [G_TILE][SPLIT]
     float* red = ps + DEC_G_TILE * DEC_SPLIT;          // [groups][hd], groups * hd = 8 warps * 32 lanes * V
+    const int lds = hd + V;                            // a staged row and 16 bytes: 16-byte reads stay free of bank conflicts
+    T* sk = reinterpret_cast<T*>(red + DEC_THREADS * V);   // [SPLIT][lds]   (ASYNC only)
+    T* sv = sk + DEC_SPLIT * lds;                      // [SPLIT][lds]
     __shared__ float wred[DEC_THREADS / 32][DEC_G_TILE];
     __shared__ float stat_m[DEC_G_TILE], stat_l[DEC_G_TILE];
     __shared__ int is_last;
 
-    for (int i = tid; i < gt * hd; i += DEC_THREADS) qs[i] = to_f32<T>(q[((size_t)t * nh + h0) * hd + i]);
-    __syncthreads();
-
     const int32_t* bt = block_tables + (size_t)token_seg[t] * max_blocks;
     const size_t page_stride = (size_t)2 * nkv * page_size * hd;
     const size_t v_off = (size_t)nkv * page_size * hd;
-
-    // ---- scores: one key per thread -------------------------------------------------------------
     const int key = k0 + tid;
     const bool valid = tid < nkeys && key >= lo;
+    // the page of this thread's key: from the step's metadata, which no kernel writes
+    const size_t my_row = valid ? (size_t)bt[key / page_size] * page_stride + ((size_t)kvh * page_size + key % page_size) * hd : 0;
+
+    dependency_wait();                                 // q and the cache come from the kernels before this one
+    let_dependents_start();
+
+    if (ASYNC && valid) {
+        const T* kr = cache + my_row;
+        T* dk = sk + tid * lds;
+        T* dv = sv + tid * lds;
+        for (int c = 0; c < hd; c += V) {
+            dec_cp_async16(dk + c, kr + c);
+            dec_cp_async16(dv + c, kr + v_off + c);
+        }
+    }
+    if (ASYNC) asm volatile("cp.async.commit_group;" ::: "memory");
+    for (int i = tid; i < gt * hd; i += DEC_THREADS) qs[i] = to_f32<T>(q[((size_t)t * nh + h0) * hd + i]);
+    if (ASYNC) asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+
+    // ---- scores: one key per thread -------------------------------------------------------------
     float s[DEC_G_TILE];
 #pragma unroll
     for (int h = 0; h < DEC_G_TILE; h++) s[h] = 0.0f;
     if (valid) {
-        const T* kr = cache + (size_t)bt[key / page_size] * page_stride + ((size_t)kvh * page_size + key % page_size) * hd;
+        const T* kr = ASYNC ? sk + tid * lds : cache + my_row;
 #pragma unroll 8
         for (int c = 0; c < hd; c += V) {
             float kf[V];
@@ -136,7 +161,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
         for (int i = 0; i < V; i++) acc[h][i] = 0.0f;
     if (lane_on) {
         const int row_lo = lo > k0 ? lo - k0 : 0;
-        constexpr int B = 8;                       // rows in flight per thread: all their loads are issued before any is used
+        constexpr int B = ASYNC ? 2 : 8;           // rows in flight per thread: from global memory all loads are issued before any is used
         for (int base = group; base < nkeys; base += B * groups) {
             float vf[B][V];
 #pragma unroll
@@ -144,7 +169,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
                 const int row = base + i * groups;
                 if (row < nkeys && row >= row_lo) {
                     const int kk = k0 + row;
-                    const T* vr = cache + (size_t)bt[kk / page_size] * page_stride + v_off + ((size_t)kvh * page_size + kk % page_size) * hd;
+                    const T* vr = ASYNC ? sv + row * lds
+                                        : cache + (size_t)bt[kk / page_size] * page_stride + v_off + ((size_t)kvh * page_size + kk % page_size) * hd;
                     load16<T>(vr + c, vf[i]);
                 } else {
 #pragma unroll
@@ -300,18 +326,27 @@ VK_API int vk_attention_decode(const void* q, const void* cache, const int32_t* 
     float* part_o = (float*)base;
     float* part_ml = (float*)(base + up((size_t)scratch_tokens * nh * splits * hd * 4));
     int* counters = (int*)((char*)part_ml + up((size_t)scratch_tokens * nh * splits * 2 * 4));
-    const size_t smem = (size_t)(DEC_G_TILE * hd + DEC_G_TILE * DEC_SPLIT + DEC_THREADS * vec) * sizeof(float);
+    const size_t smem_base = (size_t)(DEC_G_TILE * hd + DEC_G_TILE * DEC_SPLIT + DEC_THREADS * vec) * sizeof(float);
+    const size_t smem_async = smem_base + (size_t)2 * DEC_SPLIT * (hd + vec) * (dtype == 0 ? 4 : 2);
+    const bool async = smem_async <= 100 * 1024;        // two blocks a multiprocessor
+    const size_t smem = async ? smem_async : smem_base;
     dim3 grid(grid_splits, tiles, n_tokens);
-    if (dtype == 0) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attention_decode_kernel<float><<<grid, DEC_THREADS, smem, stream>>>(
-            (const float*)q, (const float*)cache, block_tables, token_seg, positions, tok_list, (float*)out, part_o, part_ml,
-            counters, nh, nkv, hd, page_size, max_blocks, splits, scale, window);
-    } else {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attention_decode_kernel<__nv_bfloat16><<<grid, DEC_THREADS, smem, stream>>>(
-            (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_tables, token_seg, positions, tok_list, (__nv_bfloat16*)out,
-            part_o, part_ml, counters, nh, nkv, hd, page_size, max_blocks, splits, scale, window);
+#define GO(T, A)                                                                                                                     \
+    {                                                                                                                                \
+        auto kern = attention_decode_kernel<T, A>;                                                                                   \
+        if (smem > 48 * 1024) {                                                                                                      \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                      \
+            if (e != cudaSuccess) return (int)e;                                                                                     \
+        }                                                                                                                            \
+        return launch_dependent(kern, grid, dim3(DEC_THREADS), smem, stream, (const T*)q, (const T*)cache, block_tables, token_seg, \
+                                positions, tok_list, (T*)out, part_o, part_ml, counters, nh, nkv, hd, page_size, max_blocks, splits, \
+                                scale, window);                                                                                      \
     }
+    if (dtype == 0) {
+        if (async) GO(float, true) else GO(float, false)
+    } else {
+        if (async) GO(__nv_bfloat16, true) else GO(__nv_bfloat16, false)
+    }
+#undef GO
     return launch_status();
 }
