@@ -350,3 +350,82 @@ VK_API int vk_attention_decode(const void* q, const void* cache, const int32_t* 
 #undef GO
     return launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// The variant that allocates nothing (see attention_decode_static.h).
+// ---------------------------------------------------------------------------------------------------------
+#include <mutex>
+
+#include "attention_decode_static.h"
+
+// The library's own scratch.  In host code this name is only a handle for cudaGetSymbolAddress: it is not a
+// device pointer, and a kernel given it directly would read the wrong memory.
+static __device__ __align__(256) unsigned char vk_decode_static_scratch[VK_DECODE_STATIC_SCRATCH_BYTES];
+
+static void* decode_static_scratch_address(int* status) {
+    static std::mutex lock;
+    static void* address[64] = {};                 // per device
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { *status = (int)e; return nullptr; }
+    if (dev < 0 || dev >= 64) { *status = VK_TOO_LARGE; return nullptr; }
+    std::lock_guard<std::mutex> guard(lock);
+    if (!address[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, vk_decode_static_scratch);      // with device `dev` current: its copy of the array
+        if (e != cudaSuccess) { *status = (int)e; return nullptr; }
+        address[dev] = p;
+    }
+    *status = VK_OK;
+    return address[dev];
+}
+
+VK_API int vk_attention_decode_static(const void* q, const void* cache, const int32_t* block_tables, const int32_t* token_seg,
+                                      const int32_t* positions, const int32_t* tok_list, void* out, int n_tokens, int nh, int nkv,
+                                      int hd, int page_size, int max_blocks, int max_context, float scale, int window, int dtype,
+                                      cudaStream_t stream) {
+    if (n_tokens <= 0) return VK_OK;
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || page_size <= 0 || max_blocks <= 0 || window < 0 || max_context <= 0)
+        return VK_BAD_SHAPE;
+    const int vec = dtype == 0 ? 4 : 8;
+    if (hd % vec != 0) return VK_BAD_SHAPE;
+    if (hd > DEC_MAX_HD || hd / vec > 32 || n_tokens > 65535 || max_context > 128 * DEC_SPLIT) return VK_TOO_LARGE;
+    if (((uintptr_t)cache % 16) || ((uintptr_t)q % 4)) return VK_BAD_ALIGNMENT;
+    // the partial results of this launch must fit the array: refuse before anything runs
+    if (vk_attention_decode_scratch_bytes(n_tokens, nh, nkv, hd, max_context) > VK_DECODE_STATIC_SCRATCH_BYTES) return VK_TOO_LARGE;
+    int status = VK_OK;
+    char* base = (char*)decode_static_scratch_address(&status);
+    if (!base) return status;
+    const int splits = (max_context + DEC_SPLIT - 1) / DEC_SPLIT;
+    const int g = nh / nkv, tiles = nkv * ((g + DEC_G_TILE - 1) / DEC_G_TILE);
+    auto up = [](size_t b) { return (b + 255) / 256 * 256; };
+    float* part_o = (float*)base;
+    float* part_ml = (float*)(base + up((size_t)n_tokens * nh * splits * hd * 4));
+    int* counters = (int*)((char*)part_ml + up((size_t)n_tokens * nh * splits * 2 * 4));
+    // the array keeps the last call's bytes, laid out for that call's sizes: the counters start at zero
+    cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)n_tokens * tiles * sizeof(int), stream);
+    if (e != cudaSuccess) return (int)e;
+    const size_t smem_base = (size_t)(DEC_G_TILE * hd + DEC_G_TILE * DEC_SPLIT + DEC_THREADS * vec) * sizeof(float);
+    const size_t smem_async = smem_base + (size_t)2 * DEC_SPLIT * (hd + vec) * (dtype == 0 ? 4 : 2);
+    const bool async = smem_async <= 100 * 1024;
+    const size_t smem = async ? smem_async : smem_base;
+    dim3 grid(splits, tiles, n_tokens);
+#define GO(T, A)                                                                                                              \
+    {                                                                                                                         \
+        auto kern = attention_decode_kernel<T, A>;                                                                            \
+        if (smem > 48 * 1024) {                                                                                               \
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                           \
+            if (e != cudaSuccess) return (int)e;                                                                              \
+        }                                                                                                                     \
+        kern<<<grid, DEC_THREADS, smem, stream>>>((const T*)q, (const T*)cache, block_tables, token_seg, positions, tok_list, \
+                                                  (T*)out, part_o, part_ml, counters, nh, nkv, hd, page_size, max_blocks,     \
+                                                  splits, scale, window);                                                     \
+    }
+    if (dtype == 0) {
+        if (async) GO(float, true) else GO(float, false)
+    } else {
+        if (async) GO(__nv_bfloat16, true) else GO(__nv_bfloat16, false)
+    }
+#undef GO
+    return launch_status();
+}
