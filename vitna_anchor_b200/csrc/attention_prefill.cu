@@ -66,6 +66,7 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
     const size_t page_stride = (size_t)2 * nkv * page_size * HD;
     const size_t v_off = (size_t)nkv * page_size * HD;
 
+    const float scale_log2 = scale * 1.4426950408889634f;
     const int last_pos = pos0 + rows - 1;
     const int lo_first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;     // lowest key any row needs
     const int kt0 = lo_first / PF_BN, kt1 = last_pos / PF_BN;                               // key tiles kt0 .. kt1
@@ -149,8 +150,11 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
                     mma16816(s[nb2 * 2 + 1], qf[ks], b2, b3);
                 }
             }
-            // ---- scale, mask, running softmax --------------------------------------------------------------
+            // ---- scale, mask, running softmax (in base 2: exp(x) = exp2(x * log2 e), folded into the scale) ----------
             float mx[2] = {-INFINITY, -INFINITY};
+            // every key of the tile visible to every row of this warp: no mask to apply
+            const int warp_lo_last = (window > 0 && pos0 + warp * 16 + 15 - window + 1 > 0) ? pos0 + warp * 16 + 15 - window + 1 : 0;
+            const bool all_visible = kt * PF_BN + PF_BN - 1 <= pos0 + warp * 16 && kt * PF_BN >= warp_lo_last;
 #pragma unroll
             for (int nb = 0; nb < 8; nb++) {
 #pragma unroll
@@ -158,7 +162,7 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
                     const int key = kt * PF_BN + nb * 8 + qd * 2 + (e & 1);
                     const bool second = e >= 2;
                     const int pos = second ? pos_b : pos_a, lo = second ? lo_b : lo_a;
-                    const float v = (key <= pos && key >= lo) ? s[nb][e] * scale : -INFINITY;
+                    const float v = (all_visible || (key <= pos && key >= lo)) ? s[nb][e] * scale_log2 : -INFINITY;
                     s[nb][e] = v;
                     mx[second] = fmaxf(mx[second], v);
                 }
@@ -174,7 +178,7 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
                 m_new[r] = fmaxf(m_run[r], mx[r]);
                 // a row with no key yet (all masked so far) keeps m = -inf: use 0 as the reference so that exp gives 0
                 const float ref = m_new[r] == -INFINITY ? 0.0f : m_new[r];
-                corr[r] = expf(m_run[r] - ref);          // exp(-inf) = 0 on the first tile with keys
+                corr[r] = exp2f(m_run[r] - ref);         // exp2(-inf) = 0 on the first tile with keys
                 m_run[r] = m_new[r];
                 m_new[r] = ref;
             }
@@ -182,8 +186,8 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
             uint32_t pf[4][4], pl[4][4];                 // P as A fragments, high and low parts: 4 k-steps of 16 keys
 #pragma unroll
             for (int nb = 0; nb < 8; nb++) {
-                const float p0 = expf(s[nb][0] - m_new[0]), p1 = expf(s[nb][1] - m_new[0]);
-                const float p2 = expf(s[nb][2] - m_new[1]), p3 = expf(s[nb][3] - m_new[1]);
+                const float p0 = exp2f(s[nb][0] - m_new[0]), p1 = exp2f(s[nb][1] - m_new[0]);
+                const float p2 = exp2f(s[nb][2] - m_new[1]), p3 = exp2f(s[nb][3] - m_new[1]);
                 rs[0] += p0 + p1;
                 rs[1] += p2 + p3;
                 const uint32_t h01 = pack_bf16(p0, p1), h23 = pack_bf16(p2, p3);

@@ -167,11 +167,24 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
         // epilogue: warp w reads lanes 32*(w%4) .. +31 of the accumulator, one output row per thread
         const int quarter = warp & 3;
         const int row = m0 + quarter * 32 + lane;
+        // the residual sum's old values for the first 64 columns are read while the tensor core works
+        float4 pre[2][8];
+        if (EPI == TC_ACC && row < M && (N % 4 == 0)) {
+#pragma unroll
+            for (int c2 = 0; c2 < 2; c2++) {
+                const int col = n0 + c2 * 32;
+                if (c2 * 32 < BN && col + 32 <= N) {
+                    const float* o = reinterpret_cast<const float*>(out) + (size_t)row * N + col;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) pre[c2][j] = *reinterpret_cast<const float4*>(o + 4 * j);
+                }
+            }
+        }
         if (!mbar_wait(acc_full, 0)) {
             if (lane == 0) give_up(error, &failed, 3);
         } else {
             tc_fence_after();
-#pragma unroll 1
+#pragma unroll
             for (int c = 0; c < BN; c += 32) {
                 uint32_t r[32];
                 __syncwarp();
@@ -200,15 +213,22 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
                 } else {
                     float* o = reinterpret_cast<float*>(out) + (size_t)row * N + col;
                     if (whole && (N % 4 == 0)) {
+                        float4 prev[8];
+                        if (EPI == TC_ACC) {
+                            if (c < 64) {                  // read before the wait
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                                                   __uint_as_float(r[j + 3]));
-                            if (EPI == TC_ACC) {
-                                const float4 old = *reinterpret_cast<const float4*>(o + j);
-                                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                                for (int j = 0; j < 8; j++) prev[j] = pre[c / 32][j];
+                            } else {                       // all eight reads are issued before any is used
+#pragma unroll
+                                for (int j = 0; j < 8; j++) prev[j] = *reinterpret_cast<const float4*>(o + 4 * j);
                             }
-                            *reinterpret_cast<float4*>(o + j) = v;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                                                   __uint_as_float(r[4 * j + 3]));
+                            if (EPI == TC_ACC) { v.x += prev[j].x; v.y += prev[j].y; v.z += prev[j].z; v.w += prev[j].w; }
+                            *reinterpret_cast<float4*>(o + 4 * j) = v;
                         }
                     } else {
                         for (int j = 0; j < 32 && col + j < N; j++) {
