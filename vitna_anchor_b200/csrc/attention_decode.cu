@@ -289,6 +289,12 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
     }
 }
 
+// attention_decode_mma.cu: the bfloat16 tensor-core form for head sizes 16, 32, 64, 96, 128 (same scratch, same combine).
+int launch_decode_mma(const void* q, const void* cache, const int32_t* bt, const int32_t* token_seg, const int32_t* positions,
+                      const int32_t* tok_list, void* out, float* part_o, float* part_ml, int* counters, int n_tokens, int nh, int nkv,
+                      int hd, int page_size, int max_blocks, int splits, int grid_splits, int counter_tiles, float scale, int window,
+                      cudaStream_t stream);
+
 }  // namespace vk
 
 using namespace vk;
@@ -326,6 +332,9 @@ VK_API int vk_attention_decode(const void* q, const void* cache, const int32_t* 
     float* part_o = (float*)base;
     float* part_ml = (float*)(base + up((size_t)scratch_tokens * nh * splits * hd * 4));
     int* counters = (int*)((char*)part_ml + up((size_t)scratch_tokens * nh * splits * 2 * 4));
+    if (dtype == 1 && (hd == 16 || hd == 32 || hd == 64 || hd == 96 || hd == 128) && ((uintptr_t)q % 16 == 0))
+        return launch_decode_mma(q, cache, block_tables, token_seg, positions, tok_list, out, part_o, part_ml, counters, n_tokens, nh,
+                                 nkv, hd, page_size, max_blocks, splits, grid_splits, tiles, scale, window, stream);
     const size_t smem_base = (size_t)(DEC_G_TILE * hd + DEC_G_TILE * DEC_SPLIT + DEC_THREADS * vec) * sizeof(float);
     const size_t smem_async = smem_base + (size_t)2 * DEC_SPLIT * (hd + vec) * (dtype == 0 ? 4 : 2);
     const bool async = smem_async <= 100 * 1024;        // two blocks a multiprocessor
