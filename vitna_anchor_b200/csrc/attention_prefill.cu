@@ -1,9 +1,12 @@
 // Causal attention of prompt portions over the paged cache, in bfloat16 on the tensor cores.
 //
-// A block takes 64 consecutive tokens of one request (a "query tile") and one query head; its four
-// warps own 16 query rows each.  Keys and values of the request are read from its pages in tiles of
-// 64 positions whose boundaries are multiples of 64 in absolute position, so the order of a row's
-// sums does not depend on how the prompt was cut into steps.  Scores S = Q K^T (mma m16n8k16,
+// A block takes 64 consecutive tokens of one request (a "query tile") and one query head.  It has two
+// groups of four warps; a warp owns 16 query rows, and the two groups share the key tiles between them
+// (group 0 the even ones counted from the first, group 1 the odd ones), which halves the longest chain
+// of the causal triangle; their running (maximum, sum, output) meet once at the end, group 0 first.
+// Keys and values of the request are read from its pages in tiles of 64 positions whose boundaries are
+// multiples of 64 in absolute position, so the order of a row's sums does not depend on how the prompt
+// was cut into steps.  Scores S = Q K^T (mma m16n8k16,
 // float32 accumulation) are scaled after the sum, masked (a query at position p sees keys
 // max(0, p - window + 1) .. p), and folded into a running maximum, sum and output in float32
 // (the softmax of engine/src/model.c:932-956, computed tile by tile).  The tensor cores take P in
@@ -16,7 +19,7 @@
 
 namespace vk {
 
-constexpr int PF_BM = 64, PF_BN = 64, PF_THREADS = 128;
+constexpr int PF_BM = 64, PF_BN = 64, PF_THREADS = 256, PF_GROUP = 128;
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
@@ -43,7 +46,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
+__global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_tables,
     const int32_t* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int max_blocks, float scale,
     int window) {
@@ -53,14 +56,15 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
     constexpr int DBLK = HD / 8;                    // 8-wide blocks of the output
     extern __shared__ __align__(16) unsigned char smem_raw[];
     T* sq = reinterpret_cast<T*>(smem_raw);         // [64][LD]
-    T* sk = sq + PF_BM * LD;                        // [2][64][LD]
-    T* sv = sk + 2 * PF_BN * LD;                    // [2][64][LD]
+    const int grp = threadIdx.x / PF_GROUP;         // which half of the key tiles
+    T* sk = sq + PF_BM * LD + grp * 4 * PF_BN * LD; // this group's [2][64][LD]
+    T* sv = sk + 2 * PF_BN * LD;                    // this group's [2][64][LD]
 
     const int tile = gridDim.x - 1 - blockIdx.x;    // later tiles of a prompt have more keys: start them first
     const int h = blockIdx.y;
     const int kvh = h / (nh / nkv);
     const int tok0 = tiles[tile * 4 + 0], rows = tiles[tile * 4 + 1], pos0 = tiles[tile * 4 + 2], seg = tiles[tile * 4 + 3];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x % PF_GROUP, warp = tid >> 5, lane = tid & 31;      // within the group
     const int g = lane >> 2, qd = lane & 3;
     const int32_t* bt = block_tables + (size_t)seg * max_blocks;
     const size_t page_stride = (size_t)2 * nkv * page_size * HD;
@@ -74,7 +78,7 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
     // ---- loads ------------------------------------------------------------------------------------
     constexpr int CHUNKS = HD / 8;                  // 16-byte chunks per row
     auto load_q = [&]() {
-        for (int i = tid; i < PF_BM * CHUNKS; i += PF_THREADS) {
+        for (int i = threadIdx.x; i < PF_BM * CHUNKS; i += PF_THREADS) {
             const int r = i / CHUNKS, c = i % CHUNKS;
             T* dst = sq + r * LD + c * 8;
             if (r < rows) cp_async16(dst, q + ((size_t)(tok0 + r) * nh + h) * HD + c * 8);
@@ -84,7 +88,7 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
     auto load_kv = [&](int kt, int buf) {
         T* dk = sk + buf * PF_BN * LD;
         T* dv = sv + buf * PF_BN * LD;
-        for (int i = tid; i < PF_BN * CHUNKS; i += PF_THREADS) {
+        for (int i = tid; i < PF_BN * CHUNKS; i += PF_GROUP) {
             const int r = i / CHUNKS, c = i % CHUNKS;
             const int key = kt * PF_BN + r;
             if (key <= last_pos && key >= lo_first) {
@@ -98,8 +102,10 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
         }
     };
 
+    auto group_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "n"(PF_GROUP) : "memory"); };
+    const int kfirst = kt0 + grp;                   // this group's key tiles: kfirst, kfirst + 2, ...
     load_q();
-    load_kv(kt0, 0);
+    if (kfirst <= kt1) load_kv(kfirst, 0);
     cp_async_commit();
 
     // per-thread state: rows g and g+8 of this warp's 16 query rows
@@ -113,13 +119,17 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
     const int lo_a = (window > 0 && pos_a - window + 1 > 0) ? pos_a - window + 1 : 0;
     const int lo_b = (window > 0 && pos_b - window + 1 > 0) ? pos_b - window + 1 : 0;
 
-    for (int kt = kt0; kt <= kt1; kt++) {
-        const int buf = (kt - kt0) & 1;
-        if (kt < kt1) load_kv(kt + 1, buf ^ 1);
+    cp_async_wait<0>();
+    __syncthreads();                                // q (loaded by both groups) and each group's first tile
+    for (int kt = kfirst; kt <= kt1; kt += 2) {
+        const int buf = ((kt - kfirst) >> 1) & 1;
+        if (kt + 2 <= kt1) load_kv(kt + 2, buf ^ 1);
         cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
-        if (kt == kt0) {
+        if (kt != kfirst) {
+            cp_async_wait<1>();
+            group_sync();
+        }
+        if (kt == kfirst) {
             // this warp's Q fragments, once
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ks++) {
@@ -219,9 +229,38 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
                 }
             }
         }
-        __syncthreads();        // the buffer is free for the load after next
+        group_sync();           // the buffer is free for the load after next
     }
     cp_async_wait<0>();
+
+    // ---- the two groups' running results meet: group 1 hands over, group 0 folds it in after its own -----------
+    __syncthreads();            // every key tile is consumed: the tile buffers are free
+    float* hand = reinterpret_cast<float*>(sq + PF_BM * LD + 4 * PF_BN * LD);     // group 1's buffers, [128][DBLK*4 + 4]
+    constexpr int HW = DBLK * 4 + 4;
+    if (grp == 1) {
+        float* mine = hand + tid * HW;
+        mine[0] = m_run[0]; mine[1] = m_run[1]; mine[2] = l_run[0]; mine[3] = l_run[1];
+#pragma unroll
+        for (int i = 0; i < DBLK; i++) { mine[4 + i * 4] = o[i][0]; mine[5 + i * 4] = o[i][1]; mine[6 + i * 4] = o[i][2]; mine[7 + i * 4] = o[i][3]; }
+    }
+    __syncthreads();
+    if (grp == 1) return;
+    {
+        const float* other = hand + tid * HW;
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const float m1 = other[r], l1 = other[2 + r];
+            const float mm = fmaxf(m_run[r], m1);
+            const float ref = mm == -INFINITY ? 0.0f : mm;
+            const float c0 = exp2f(m_run[r] - ref), c1 = exp2f(m1 - ref);
+            l_run[r] = l_run[r] * c0 + l1 * c1;
+#pragma unroll
+            for (int i = 0; i < DBLK; i++) {
+                o[i][2 * r] = o[i][2 * r] * c0 + other[4 + i * 4 + 2 * r] * c1;
+                o[i][2 * r + 1] = o[i][2 * r + 1] * c0 + other[4 + i * 4 + 2 * r + 1] * c1;
+            }
+        }
+    }
 
     // ---- normalise and store ---------------------------------------------------------------------------
     const float inv_a = l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f, inv_b = l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f;
@@ -239,7 +278,7 @@ template <int HD>
 static int launch_prefill(const void* q, const void* cache, const int32_t* bt, const int32_t* tiles, void* out, int n_tiles, int nh,
                           int nkv, int page_size, int max_blocks, float scale, int window, cudaStream_t stream) {
     constexpr int LD = HD + 8;
-    const size_t smem = (size_t)(PF_BM + 4 * PF_BN) * LD * 2;
+    const size_t smem = (size_t)(PF_BM + 8 * PF_BN) * LD * 2;
     auto kern = attention_prefill_kernel<HD>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -309,9 +309,12 @@ EPI_SAME, EPI_F32, EPI_ACC, EPI_SWIGLU, EPI_ROPE = 0, 1, 2, 3, 4
 SKINNY_MAX_ROWS = 64
 
 
-def skinny_takes(dtype: torch.dtype, M: int, K: int) -> bool:
-    """Whether the few-rows kernel takes this product (else the tile kernels do the work)."""
-    return 0 < M <= SKINNY_MAX_ROWS and K % (4 if dtype == torch.float32 else 8) == 0
+def skinny_takes(dtype: torch.dtype, M: int, K: int, N: int = 0) -> bool:
+    """Whether the few-rows kernel should take this product (else the tile kernels do the work).  Every block
+    stages all M rows for itself, so many rows times many blocks (a large N) is left to the tile kernels."""
+    if not (0 < M <= SKINNY_MAX_ROWS and K % (4 if dtype == torch.float32 else 8) == 0):
+        return False
+    return M <= 8 or N <= 8192 or dtype == torch.float32
 
 
 def linear_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, *, norm_weight: Optional[torch.Tensor] = None,
@@ -375,7 +378,7 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int,
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> torch.Tensor:
     """out (=, or += in mode LINEAR_ACC_F32) x @ w.T.  float32 runs on CUDA cores in float32 arithmetic
     (no reduced-precision matrix mode); bfloat16 runs the tensor-core kernel where it takes the sizes."""
-    if skinny_takes(x.dtype, x.shape[0], x.shape[1]) and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
+    if skinny_takes(x.dtype, x.shape[0], x.shape[1], w.shape[0]) and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
         return linear_skinny(x, w, out, mode)
     if tcgen05_takes(x, w) and out.data_ptr() % 16 == 0:
         return linear_tcgen05(x, w, out, mode)

@@ -43,7 +43,7 @@ class PagedAttention(Mixer):
 
     def fuses_norm(self, norm, ctx: StepContext) -> bool:
         from .norms import RMSNorm
-        return isinstance(norm, RMSNorm) and ops.skinny_takes(ctx.dtype, ctx.num_tokens, self.hidden)
+        return isinstance(norm, RMSNorm) and ops.skinny_takes(ctx.dtype, ctx.num_tokens, self.hidden, self.qd + 2 * self.kvd)
 
     def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCacheView, residual: torch.Tensor,
                 write_cache: bool = True, norm=None) -> None:
