@@ -84,7 +84,10 @@ class ModelRunner:
             self._fail_at = int(env) if env.strip() else 0
         self.steps_run = 0
         self.cuda_graphs = cuda_graphs
-        self._graphs: Dict[int, tuple] = {}      # decode batch bucket -> (graph, logits)
+        self._graphs: Dict[object, tuple] = {}   # decode batch bucket, or the counts of a mixed step -> (graph, logits, kernels)
+        self._seen_shapes: Dict[tuple, int] = {}
+        self.graph_mixed_steps = True            # steps with prompt portions are captured too, once their counts repeat
+        self.max_graphs = 48
         self.graph_replays = 0
 
     # -- requests ---------------------------------------------------------------------------
@@ -133,8 +136,11 @@ class ModelRunner:
             raise StepError(f"{T} tokens in a step; the limit is {self.max_batch_tokens}")
         return T, R
 
-    def _build_context(self, entries: Sequence[StepEntry], T: int, R: int,
-                       fixed_blocks: Optional[int] = None) -> Tuple[StepContext, Optional[torch.Tensor]]:
+    def _build_context(self, entries: Sequence[StepEntry], T: int, R: int, fixed_blocks: Optional[int] = None,
+                       for_graph: bool = False) -> Tuple[StepContext, Optional[torch.Tensor]]:
+        """The batch's arrays in one staging buffer and one copy.  Where each array lies depends only on the
+        counts (tokens, segments, wanted rows, single-token segments, prompt tiles, width of the block tables),
+        so a graph captured for one batch finds the arrays of any batch with the same counts."""
         S = len(entries)
         ps = self.page_size
         tables = self.cache.tables
@@ -199,7 +205,8 @@ class ModelRunner:
             num_tokens=T, num_segments=S, dtype=self.model.dtype, tokens=dev[s_tokens], positions=dev[s_pos],
             token_seg=dev[s_seg], seg_starts=dev[s_starts], seg_context=dev[s_ctx], seg_slots=dev[s_slots], groups=groups,
             caches=self.cache.views, workspace=self.workspace, host_seg_lens=lens, host_seg_first_pos=first,
-            host_seg_slots=slots, max_seg_len=max(lens), max_context=max(context), decode_only=all(n == 1 for n in lens),
+            host_seg_slots=slots, max_seg_len=max(lens), max_context=self.max_model_len if for_graph else max(context),
+            decode_only=all(n == 1 for n in lens),
             num_dec=len(dec), dec_tokens=None if (s_dec is None or not pre) else dev[s_dec],
             num_pre=len(pre), pre_tokens=None if s_pre is None else dev[s_pre],
             pre_tiles=None if s_tiles is None else dev[s_tiles].view(-1, 4))
@@ -220,6 +227,8 @@ class ModelRunner:
         try:
             if self.cuda_graphs and T == len(entries) == R and all(len(e.want) == 1 for e in entries):
                 logits = self._decode_step(entries)
+            elif self.cuda_graphs and self.graph_mixed_steps and 0 < R <= 64:
+                logits = self._graphed_step(entries, T, R)
             else:
                 ctx, rows = self._build_context(entries, T, R)
                 logits = self.model.forward(ctx, rows)
@@ -312,3 +321,34 @@ class ModelRunner:
         ops.add_launches(kernels)
         self.graph_replays += 1
         return static_logits[:S]
+
+    def _graphed_step(self, entries: Sequence[StepEntry], T: int, R: int) -> torch.Tensor:
+        """A step with prompt portions.  Issuing its few hundred launches from the host takes longer than the GPU
+        needs for them, so once the same counts come a second time the step's launches are captured and from then
+        on replayed.  Everything that differs between two such steps (tokens, positions, block tables, which rows
+        are wanted) is in the metadata buffer, at places that depend on the counts alone."""
+        lens = [len(e.tokens) for e in entries]
+        n_dec = sum(1 for n in lens if n == 1)
+        n_tiles = sum(-(-n // 64) for n in lens if n > 1)
+        key = ("mixed", T, len(entries), R, n_dec, n_tiles)
+        ctx, rows = self._build_context(entries, T, R, fixed_blocks=self.max_blocks, for_graph=True)
+        held = self._graphs.get(key)
+        if held is not None:
+            graph, static_logits, kernels = held
+            graph.replay()
+            ops.add_launches(kernels)
+            self.graph_replays += 1
+            return static_logits
+        logits = self.model.forward(ctx, rows)
+        seen = self._seen_shapes.get(key, 0) + 1
+        self._seen_shapes[key] = seen
+        if seen >= 2 and len(self._graphs) < self.max_graphs:
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count()
+            with torch.cuda.graph(graph):
+                static_logits = self.model.forward(ctx, rows)
+            kernels = ops.launch_count() - before
+            ops.add_launches(-kernels)            # capture does not run the kernels; `logits` above is this step's result
+            self._graphs[key] = (graph, static_logits, kernels)
+        return logits
