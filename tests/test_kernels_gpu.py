@@ -503,3 +503,49 @@ def test_attention_prefill_tiles(ops, nh, nkv, hd, ps, window):
     ops.attention_rows(q_dev, pool.cuda(), dev(bt), dev(np.array(seg, np.int32)), dev(np.array(pos, np.int32)), rows, nh, nkv, hd,
                        1.0 / math.sqrt(hd), window)
     assert (rows.float() - out.float()).abs().max() <= 3e-2 * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("M,I,K", [(128, 64, 64), (2048, 1536, 576), (300, 200, 72), (70, 8192, 2048)])
+def test_linear_tcgen05_swiglu_matches_the_separate_kernels(ops, M, I, K):
+    torch.manual_seed(M + I)
+    x = torch.randn(M, K).to(torch.bfloat16).cuda()
+    w = (torch.randn(2 * I, K) / math.sqrt(K) * 2).to(torch.bfloat16).cuda()
+    gu = torch.empty(M, 2 * I, dtype=torch.bfloat16, device="cuda")
+    ops.linear_tcgen05(x, w, gu, ops.LINEAR_SAME)
+    want = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
+    ops.silu_mul(gu, want)
+    got = torch.full((M, I), 9.0, dtype=torch.bfloat16, device="cuda")
+    ops.linear_tcgen05_swiglu(x, w, got)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    assert torch.equal(got, want)              # the same sums and the same rounding points
+    g = (x.double() @ w[:I].double().T); u = (x.double() @ w[I:].double().T)
+    ref = g / (1 + torch.exp(-g)) * u
+    assert (got.double() - ref).abs().max() <= 2e-2 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps,M,K", [(9, 3, 64, 16, 200, 576), (2, 1, 128, 8, 130, 96), (32, 32, 64, 16, 70, 2048)])
+def test_linear_tcgen05_rope_matches_the_separate_kernels(ops, nh, nkv, hd, ps, M, K):
+    torch.manual_seed(nh + M)
+    N = (nh + 2 * nkv) * hd
+    pages = -(-M // ps) + 3
+    x = torch.randn(M, K).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K) / math.sqrt(K) * 2).to(torch.bfloat16).cuda()
+    positions = dev(np.random.default_rng(1).integers(0, 900, M).astype(np.int32))
+    cos, sin = P.rope_tables(np.arange(1000), hd, 100000.0)
+    slots = np.random.default_rng(2).permutation(pages * ps)[:M].astype(np.int32)
+    slots[5] = -1
+    qkv = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ops.linear_tcgen05(x, w, qkv, ops.LINEAR_SAME)
+    cache_a = torch.full((pages, 2, nkv, ps, hd), 7.0, dtype=torch.bfloat16, device="cuda")
+    q_a = torch.empty(M, nh * hd, dtype=torch.bfloat16, device="cuda")
+    ops.rope_store(qkv, positions, dev(cos), dev(sin), dev(slots), q_a, cache_a, nh, nkv, hd, hd, ps)
+    cache_b = torch.full((pages, 2, nkv, ps, hd), 7.0, dtype=torch.bfloat16, device="cuda")
+    q_b = torch.empty(M, nh * hd, dtype=torch.bfloat16, device="cuda")
+    ops.linear_tcgen05_rope(x, w, q_b, positions, dev(cos), dev(sin), dev(slots), cache_b, nh, nkv, hd)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    t = 1e-2 * float(q_a.float().abs().max())      # the rotation's float32 arithmetic may contract differently: one bfloat16 step
+    assert (q_a.float() - q_b.float()).abs().max() <= t
+    assert (cache_a.float() - cache_b.float()).abs().max() <= t
+    assert torch.equal(cache_a == 7.0, cache_b == 7.0)

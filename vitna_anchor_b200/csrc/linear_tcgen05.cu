@@ -92,7 +92,24 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-enum { TC_SAME = 0, TC_F32 = 1, TC_ACC = 2 };
+enum { TC_SAME = 0, TC_F32 = 1, TC_ACC = 2, TC_SWIGLU = 3, TC_ROPE = 4 };
+
+// What the fused epilogues need besides the accumulator.
+//   TC_SWIGLU  the weight is [2*inter, K], gate rows then up rows; a block's tile is 64 gate rows and the 64 up rows
+//              of the same columns (two TMA loads a stage), out [M, inter] = silu(gate) * up
+//              (engine/src/ops.c:283-288; both rounded to bfloat16 first, as the separate kernels store them)
+//   TC_ROPE    the weight is [(nh + 2*nkv) * hd, K]; BN = hd, so a tile is one head: a q head is rotated by the
+//              token's position and written to out [M, nh*hd]; a k head is rotated and written into the token's
+//              cache slot; a v head is written there as it is (engine/src/ops.c:273-281, engine/src/model.c:927-930)
+struct TcExtra {
+    int inter;
+    const int32_t* positions;
+    const float* cos_t;
+    const float* sin_t;
+    const int32_t* slot;
+    __nv_bfloat16* cache;
+    int nh, nkv, hd, page_size;
+};
 
 // A bounded wait ran out: tell the block and the host (error may be a mapped host word: a plain store).
 __device__ __forceinline__ void give_up(int* error, int* failed, int code) {
@@ -104,7 +121,7 @@ __device__ __forceinline__ void give_up(int* error, int* failed, int code) {
 template <int BN, int EPI>
 __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                     const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
-                                                                    int M, int N, int K, int* error) {
+                                                                    int M, int N, int K, int* error, const TcExtra ex) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -116,7 +133,7 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
     __shared__ int failed;                // set when a bounded wait of this block ran out
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * (EPI == TC_SWIGLU ? BN / 2 : BN);     // first output column of the tile
     const int num_kb = (K + TC_BK - 1) / TC_BK;
 
     if (threadIdx.x == 0) {
@@ -143,7 +160,12 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
                 if (kb >= TC_STAGES && !mbar_wait(&empty[s], ((kb / TC_STAGES) & 1) ^ 1)) { give_up(error, &failed, 1); break; }
                 mbar_expect_tx(&full[s], STAGE_BYTES);
                 tma_load_2d(smem + s * STAGE_BYTES, &map_x, kb * TC_BK, m0, &full[s]);
-                tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &map_w, kb * TC_BK, n0, &full[s]);
+                if (EPI == TC_SWIGLU) {     // rows n0 .. n0+BN/2 of gate, then the same rows of up: the map's box is BN/2 rows
+                    tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &map_w, kb * TC_BK, n0, &full[s]);
+                    tma_load_2d(smem + s * STAGE_BYTES + A_BYTES + B_BYTES / 2, &map_w, kb * TC_BK, ex.inter + n0, &full[s]);
+                } else {
+                    tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &map_w, kb * TC_BK, n0, &full[s]);
+                }
             }
         }
     } else if (warp == 1) {
@@ -182,6 +204,91 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
         }
         if (!mbar_wait(acc_full, 0)) {
             if (lane == 0) give_up(error, &failed, 3);
+        } else if (EPI == TC_SWIGLU) {
+            tc_fence_after();
+            const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll
+            for (int c = 0; c < BN / 2; c += 32) {
+                uint32_t gr[32], ur[32];
+                __syncwarp();
+                tmem_ld32(lane_base + c, gr);
+                tmem_ld32(lane_base + BN / 2 + c, ur);
+                const int col = n0 + c;
+                if (row < M && col < ex.inter) {
+                    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * ex.inter + col;
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        float a[2];
+#pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            const float gte = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gr[j + e])));
+                            const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ur[j + e])));
+                            a[e] = (gte / (1.0f + expf(-gte))) * up;
+                        }
+                        __nv_bfloat162 v = __floats2bfloat162_rn(a[0], a[1]);
+                        packed[j / 2] = *reinterpret_cast<uint32_t*>(&v);
+                    }
+                    if (col + 32 <= ex.inter && (ex.inter % 8 == 0)) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                            *reinterpret_cast<uint4*>(o + 8 * j) = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                    } else {
+                        for (int j = 0; j < 32 && col + j < ex.inter; j++)
+                            o[j] = __ushort_as_bfloat16((unsigned short)((packed[j / 2] >> ((j & 1) * 16)) & 0xffffu));
+                    }
+                }
+            }
+        } else if (EPI == TC_ROPE) {
+            tc_fence_after();
+            // the tile is head number blockIdx.x: q heads, then k heads, then v heads; BN = hd
+            constexpr int HALF = BN / 2;
+            const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            const int head = blockIdx.x;
+            const bool is_q = head < ex.nh, is_k = !is_q && head < ex.nh + ex.nkv;
+            const int pos = row < M ? ex.positions[row] : 0;
+            const int sl = row < M ? ex.slot[row] : -1;
+            __nv_bfloat16* dst = nullptr;           // where this row's head goes (null: nowhere)
+            if (row < M) {
+                if (is_q) dst = reinterpret_cast<__nv_bfloat16*>(out) + ((size_t)row * ex.nh + head) * BN;
+                else if (sl >= 0) {
+                    const int kvh = is_k ? head - ex.nh : head - ex.nh - ex.nkv;
+                    dst = ex.cache + (size_t)(sl / ex.page_size) * 2 * ex.nkv * ex.page_size * BN + (is_k ? 0 : (size_t)ex.nkv * ex.page_size * BN) +
+                          ((size_t)kvh * ex.page_size + sl % ex.page_size) * BN;
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < HALF; c += 32) {
+                uint32_t ar[32], br[32];            // columns c .. c+31 and their partners HALF + c ..
+                __syncwarp();
+                tmem_ld32(lane_base + c, ar);
+                tmem_ld32(lane_base + HALF + c, br);
+                if (dst) {
+                    uint32_t pa[16], pb[16];
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        float ra[2], rb[2];
+#pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            const float a = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ar[j + e])));
+                            const float b = __bfloat162float(__float2bfloat16_rn(__uint_as_float(br[j + e])));
+                            if (is_q || is_k) {
+                                const float cs = ex.cos_t[(size_t)pos * HALF + c + j + e], sn = ex.sin_t[(size_t)pos * HALF + c + j + e];
+                                ra[e] = a * cs - b * sn;
+                                rb[e] = b * cs + a * sn;
+                            } else { ra[e] = a; rb[e] = b; }
+                        }
+                        __nv_bfloat162 va = __floats2bfloat162_rn(ra[0], ra[1]), vb = __floats2bfloat162_rn(rb[0], rb[1]);
+                        pa[j / 2] = *reinterpret_cast<uint32_t*>(&va);
+                        pb[j / 2] = *reinterpret_cast<uint32_t*>(&vb);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        *reinterpret_cast<uint4*>(dst + c + 8 * j) = make_uint4(pa[4 * j], pa[4 * j + 1], pa[4 * j + 2], pa[4 * j + 3]);
+                        *reinterpret_cast<uint4*>(dst + HALF + c + 8 * j) = make_uint4(pb[4 * j], pb[4 * j + 1], pb[4 * j + 2], pb[4 * j + 3]);
+                    }
+                }
+            }
         } else {
             tc_fence_after();
 #pragma unroll
@@ -277,13 +384,16 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int
 }
 
 template <int BN, int EPI>
-static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int M, int N, int K, int* error, cudaStream_t stream) {
+static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int M, int N, int K, int* error, cudaStream_t stream,
+                     const TcExtra& ex = TcExtra{}) {
     const size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + 128;
     auto kern = linear_tcgen05_kernel<BN, EPI>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
-    kern<<<grid, TC_THREADS, smem, stream>>>(mx, mw, out, M, N, K, error);
+    const int tile_cols = EPI == TC_SWIGLU ? BN / 2 : BN;
+    const int cols = EPI == TC_SWIGLU ? ex.inter : N;
+    dim3 grid((cols + tile_cols - 1) / tile_cols, (M + TC_BM - 1) / TC_BM);
+    kern<<<grid, TC_THREADS, smem, stream>>>(mx, mw, out, M, N, K, error, ex);
     return launch_status();
 }
 
@@ -313,4 +423,42 @@ VK_API int vk_linear_tcgen05(const void* x, const void* w, void* out, int M, int
     if (mode == 1) GO(64, TC_F32);
     GO(64, TC_ACC);
 #undef GO
+}
+
+// x [M, K] bfloat16 (row stride ldx), w [2*inter, K] bfloat16 with gate rows then up rows, out [M, inter] bfloat16 =
+// silu(x gate^T) * (x up^T).  inter a multiple of 8.
+VK_API int vk_linear_tcgen05_swiglu(const void* x, const void* w, void* out, int M, int inter, int K, int ldx, int* error,
+                                    cudaStream_t stream) {
+    if (M <= 0 || inter <= 0) return VK_OK;
+    if (K <= 0 || ldx < K || !error || K % 8 != 0 || ldx % 8 != 0 || inter % 8 != 0) return VK_BAD_SHAPE;
+    if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)out % 16)) return VK_BAD_ALIGNMENT;
+    if ((M + TC_BM - 1) / TC_BM > 65535) return VK_TOO_LARGE;
+    CUtensorMap mx, mw;
+    if (!make_map(&mx, x, M, K, ldx, TC_BM) || !make_map(&mw, w, 2 * inter, K, K, 64)) return VK_BAD_SHAPE;
+    TcExtra ex{};
+    ex.inter = inter;
+    return launch_tc<128, TC_SWIGLU>(mx, mw, out, M, 2 * inter, K, error, stream, ex);
+}
+
+// x [M, K] bfloat16, w [(nh + 2*nkv) * hd, K] bfloat16 (q heads, k heads, v heads); q_out [M, nh*hd] bfloat16 gets the
+// rotated q, the layer's cache ([pages][2][nkv][page_size][hd]) gets rotated k and v at slot[m] (-1: no write).
+// hd 64 or 128; cos, sin [positions, hd/2] float32.
+VK_API int vk_linear_tcgen05_rope(const void* x, const void* w, void* q_out, int M, int K, int ldx, const int32_t* positions,
+                                  const float* cos_t, const float* sin_t, const int32_t* slot, void* cache, int nh, int nkv, int hd,
+                                  int page_size, int* error, cudaStream_t stream) {
+    if (M <= 0) return VK_OK;
+    if (K <= 0 || ldx < K || !error || K % 8 != 0 || ldx % 8 != 0 || nh <= 0 || nkv <= 0 || page_size <= 0 || !positions || !cos_t ||
+        !sin_t || !slot || !cache)
+        return VK_BAD_SHAPE;
+    if (hd != 64 && hd != 128) return VK_BAD_SHAPE;
+    if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)q_out % 16) || ((uintptr_t)cache % 16)) return VK_BAD_ALIGNMENT;
+    if ((M + TC_BM - 1) / TC_BM > 65535) return VK_TOO_LARGE;
+    const int N = (nh + 2 * nkv) * hd;
+    CUtensorMap mx, mw;
+    if (!make_map(&mx, x, M, K, ldx, TC_BM) || !make_map(&mw, w, N, K, K, hd)) return VK_BAD_SHAPE;
+    TcExtra ex{};
+    ex.positions = positions; ex.cos_t = cos_t; ex.sin_t = sin_t; ex.slot = slot; ex.cache = (__nv_bfloat16*)cache;
+    ex.nh = nh; ex.nkv = nkv; ex.hd = hd; ex.page_size = page_size;
+    if (hd == 64) return launch_tc<64, TC_ROPE>(mx, mw, q_out, M, N, K, error, stream, ex);
+    return launch_tc<128, TC_ROPE>(mx, mw, q_out, M, N, K, error, stream, ex);
 }

@@ -305,6 +305,41 @@ def linear_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: in
     return out
 
 
+def linear_tcgen05_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out [M, I] = silu(x @ gate.T) * (x @ up.T) in one tcgen05 kernel; w_gate_up [2I, K], gate rows then up rows."""
+    if not tcgen05_takes(x, w_gate_up):
+        raise KernelError("linear_tcgen05_swiglu: operands must be bfloat16, 16-byte aligned, with K and the row stride multiples of 8")
+    _req(w_gate_up, "w_gate_up", torch.bfloat16, 2); _req(out, "out", torch.bfloat16, 2)
+    M, K = x.shape
+    inter = w_gate_up.shape[0] // 2
+    if w_gate_up.shape != (2 * inter, K) or out.shape != (M, inter) or inter % 8:
+        raise KernelError("linear_tcgen05_swiglu: shapes do not fit")
+    _check(lib().vk_linear_tcgen05_swiglu(_p(x), _p(w_gate_up), _p(out), M, inter, K, x.stride(0), _p(error_word()), _stream()),
+           "linear_tcgen05_swiglu")
+    return out
+
+
+def linear_tcgen05_rope(x: torch.Tensor, wqkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor,
+                        sin: torch.Tensor, slot_mapping: torch.Tensor, cache_layer: torch.Tensor, nh: int, nkv: int,
+                        hd: int) -> torch.Tensor:
+    """q, k, v projections with the rotation of q and k and the write of k and v into the pages in the product's
+    epilogue (head sizes 64 and 128; the whole head is rotated)."""
+    if not tcgen05_takes(x, wqkv):
+        raise KernelError("linear_tcgen05_rope: operands must be bfloat16, 16-byte aligned, with K and the row stride multiples of 8")
+    _req(wqkv, "wqkv", torch.bfloat16, 2); _req(q_out, "q_out", torch.bfloat16, 2); _req(positions, "positions", torch.int32, 1)
+    _req(cos, "cos", torch.float32, 2); _req(sin, "sin", torch.float32, 2); _req(slot_mapping, "slot_mapping", torch.int32, 1)
+    _req(cache_layer, "cache_layer", torch.bfloat16, 5)
+    M, K = x.shape
+    ps = cache_layer.shape[3]
+    if (wqkv.shape != ((nh + 2 * nkv) * hd, K) or q_out.shape != (M, nh * hd) or cos.shape[1] != hd // 2 or sin.shape != cos.shape
+            or tuple(cache_layer.shape[1:]) != (2, nkv, ps, hd) or positions.shape[0] < M or slot_mapping.shape[0] < M):
+        raise KernelError("linear_tcgen05_rope: shapes do not fit the head counts")
+    _check(lib().vk_linear_tcgen05_rope(_p(x), _p(wqkv), _p(q_out), M, K, x.stride(0), _p(positions), _p(cos), _p(sin),
+                                        _p(slot_mapping), _p(cache_layer), nh, nkv, hd, ps, _p(error_word()), _stream()),
+           "linear_tcgen05_rope")
+    return q_out
+
+
 EPI_SAME, EPI_F32, EPI_ACC, EPI_SWIGLU, EPI_ROPE = 0, 1, 2, 3, 4
 SKINNY_MAX_ROWS = 64
 

@@ -57,6 +57,11 @@ class PagedAttention(Mixer):
             # few rows: norm, the three projections, the rotation and the cache write in one launch
             q = ops.linear_skinny(xn, self.wqkv, q_buf, ops.EPI_ROPE, norm_weight=norm.weight, eps=norm.eps,
                                   rope=(ctx.positions, cos, sin, meta.slot_mapping, cache.pages, self.nh, self.nkv, self.hd))
+        elif (norm is None and T > ops.SKINNY_MAX_ROWS and rot == self.hd and self.hd in (64, 128) and write_cache
+              and ops.tcgen05_takes(xn, self.wqkv)):
+            # prompt-sized batch in bfloat16: the projections, the rotation and the cache write in one tcgen05 kernel
+            q = ops.linear_tcgen05_rope(xn, self.wqkv, q_buf, ctx.positions, cos, sin, meta.slot_mapping, cache.pages, self.nh,
+                                        self.nkv, self.hd)
         else:
             qkv_buf = ws.rows("att.qkv", T, self.qd + 2 * self.kvd, ctx.dtype)
             if norm is not None:

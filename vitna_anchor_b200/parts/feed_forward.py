@@ -30,6 +30,9 @@ class SwiGLU(FeedForward):
         if norm is not None:
             # few rows: norm, gate and up, and silu(gate) * up in one launch
             act = ops.linear_skinny(xn, self.w_gate_up, act_buf, ops.EPI_SWIGLU, norm_weight=norm.weight, eps=norm.eps)
+        elif T > ops.SKINNY_MAX_ROWS and self.intermediate % 8 == 0 and ops.tcgen05_takes(xn, self.w_gate_up):
+            # prompt-sized batch in bfloat16: gate, up and silu(gate) * up in one tcgen05 kernel
+            act = ops.linear_tcgen05_swiglu(xn, self.w_gate_up, act_buf)
         else:
             gu = ops.linear(xn, self.w_gate_up, ws.rows("ffn.gu", T, 2 * self.intermediate, ctx.dtype), ops.LINEAR_SAME)
             act = ops.silu_mul(gu, act_buf)
