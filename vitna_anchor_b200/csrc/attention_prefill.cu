@@ -104,6 +104,8 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
 
     auto group_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "n"(PF_GROUP) : "memory"); };
     const int kfirst = kt0 + grp;                   // this group's key tiles: kfirst, kfirst + 2, ...
+    dependency_wait();                              // q and the cache come from the kernels before this one
+    let_dependents_start();
     load_q();
     if (kfirst <= kt1) load_kv(kfirst, 0);
     cp_async_commit();
@@ -285,9 +287,8 @@ static int launch_prefill(const void* q, const void* cache, const int32_t* bt, c
         if (e != cudaSuccess) return (int)e;
     }
     dim3 grid(n_tiles, nh);
-    kern<<<grid, PF_THREADS, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bt, tiles, (__nv_bfloat16*)out, nh,
-                                             nkv, page_size, max_blocks, scale, window);
-    return launch_status();
+    return launch_plain(kern, grid, dim3(PF_THREADS), smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bt, tiles,
+                            (__nv_bfloat16*)out, nh, nkv, page_size, max_blocks, scale, window);
 }
 
 }  // namespace vk

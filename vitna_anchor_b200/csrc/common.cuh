@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define VK_API extern "C" __attribute__((visibility("default")))
 
@@ -95,6 +96,17 @@ inline int launch_status() { return (int)cudaGetLastError(); }
 __device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void let_dependents_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// An ordinary launch through the same interface (for kernels measured to run better without the overlap).
+template <typename... KArgs, typename... Args>
+inline int launch_plain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <typename... KArgs, typename... Args>
 inline int launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};
@@ -105,8 +117,9 @@ inline int launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    static const bool plain = getenv("VITNA_NO_DEPENDENT_LAUNCH") != nullptr;      // for measurements: ordinary launches
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = plain ? 0 : 1;
     return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 

@@ -20,22 +20,45 @@ __global__ void embed_rows_kernel(const T* __restrict__ table, const int32_t* __
 }
 
 // y_i = (x_i * (1 / sqrt(sum(x^2)/n + eps))) * w_i    (engine/src/kernels.c:94-111)
-// One block per output row; `rows` (optional) names the input row of each output row.
+// A warp per output row (eight rows a block): 16-byte loads when the rows allow, the 32 partial sums meet in a
+// fixed shuffle tree.  `rows` (optional) names the input row of each output row.
 template <typename T>
-__global__ void rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w,
-                                    const int32_t* __restrict__ rows, T* __restrict__ y, int n, float eps) {
-    __shared__ float scratch[32];
-    const int r = blockIdx.x;
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                           const int32_t* __restrict__ rows, T* __restrict__ y, int out_rows, int n, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+    dependency_wait();
+    let_dependents_start();
+    if (r >= out_rows) return;
     const float* in = x + (size_t)(rows ? rows[r] : r) * n;
-    float ss = 0.0f;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = in[i];
-        ss = fmaf(v, v, ss);
-    }
-    ss = block_sum(ss, scratch);
-    const float inv = 1.0f / sqrtf(ss / (float)n + eps);
     T* out = y + (size_t)r * n;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) out[i] = from_f32<T>((in[i] * inv) * w[i]);
+    const bool vec = (n % 4 == 0) && (reinterpret_cast<uintptr_t>(in) % 16 == 0) && (reinterpret_cast<uintptr_t>(w) % 16 == 0) &&
+                     (reinterpret_cast<uintptr_t>(out) % (4 * sizeof(T)) == 0);
+    float ss = 0.0f;
+    if (vec) {
+#pragma unroll 4
+        for (int i = lane * 4; i < n; i += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(in + i);
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) { const float v = in[i]; ss = fmaf(v, v, ss); }
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+    if (vec) {
+#pragma unroll 4
+        for (int i = lane * 4; i < n; i += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(in + i);
+            const float4 g = *reinterpret_cast<const float4*>(w + i);
+            out[i] = from_f32<T>((v.x * inv) * g.x);
+            out[i + 1] = from_f32<T>((v.y * inv) * g.y);
+            out[i + 2] = from_f32<T>((v.z * inv) * g.z);
+            out[i + 3] = from_f32<T>((v.w * inv) * g.w);
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) out[i] = from_f32<T>((in[i] * inv) * w[i]);
+    }
 }
 
 // Half-split rotation of every q head and k head of a token, and the write of
@@ -145,9 +168,9 @@ VK_API int vk_rmsnorm_rows(const float* x, const float* w, const int32_t* rows, 
                            int dtype, cudaStream_t stream) {
     if (out_rows <= 0) return VK_OK;
     if (n <= 0) return VK_BAD_SHAPE;
-    if (dtype == 0) rmsnorm_rows_kernel<float><<<out_rows, 256, 0, stream>>>(x, w, rows, (float*)y, n, eps);
-    else rmsnorm_rows_kernel<__nv_bfloat16><<<out_rows, 256, 0, stream>>>(x, w, rows, (__nv_bfloat16*)y, n, eps);
-    return launch_status();
+    const dim3 grid((out_rows + 7) / 8);
+    if (dtype == 0) return launch_plain(rmsnorm_rows_kernel<float>, grid, dim3(256), 0, stream, x, w, rows, (float*)y, out_rows, n, eps);
+    return launch_plain(rmsnorm_rows_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, x, w, rows, (__nv_bfloat16*)y, out_rows, n, eps);
 }
 
 VK_API int vk_rope_store(const void* qkv, const int32_t* positions, const float* cos_t, const float* sin_t,

@@ -18,7 +18,8 @@
 
 namespace vk {
 
-constexpr int TC_BM = 128, TC_BK = 64, TC_STAGES = 4, TC_THREADS = 192;
+constexpr int TC_BM = 128, TC_BK = 64, TC_THREADS = 192;
+template <int BN> struct TcStages { static constexpr int N = BN >= 128 ? 3 : 4; };   // 96 KB of stages either way: two blocks a multiprocessor
 constexpr unsigned long long TC_WAIT_CYCLES = 2000000000ull;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -122,6 +123,7 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                     const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
                                                                     int M, int N, int K, int* error, const TcExtra ex) {
+    constexpr int TC_STAGES = TcStages<BN>::N;
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -154,18 +156,30 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
 
     if (warp == 0) {
         if (lane == 0) {
-            // producer: fill a stage as soon as the tensor core has released it
-            for (int kb = 0; kb < num_kb; kb++) {
-                const int s = kb % TC_STAGES;
-                if (kb >= TC_STAGES && !mbar_wait(&empty[s], ((kb / TC_STAGES) & 1) ^ 1)) { give_up(error, &failed, 1); break; }
-                mbar_expect_tx(&full[s], STAGE_BYTES);
-                tma_load_2d(smem + s * STAGE_BYTES, &map_x, kb * TC_BK, m0, &full[s]);
+            // producer: fill a stage as soon as the tensor core has released it.  The weight tiles of the first
+            // stages are asked for before the wait on the kernel before this one (weights are nobody's output);
+            // the activation tiles follow the wait.
+            auto load_w = [&](int kb, int s) {
                 if (EPI == TC_SWIGLU) {     // rows n0 .. n0+BN/2 of gate, then the same rows of up: the map's box is BN/2 rows
                     tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &map_w, kb * TC_BK, n0, &full[s]);
                     tma_load_2d(smem + s * STAGE_BYTES + A_BYTES + B_BYTES / 2, &map_w, kb * TC_BK, ex.inter + n0, &full[s]);
                 } else {
                     tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &map_w, kb * TC_BK, n0, &full[s]);
                 }
+            };
+            const int early = num_kb < TC_STAGES ? num_kb : TC_STAGES;
+            for (int kb = 0; kb < early; kb++) {
+                mbar_expect_tx(&full[kb], STAGE_BYTES);
+                load_w(kb, kb);
+            }
+            dependency_wait();
+            for (int kb = 0; kb < early; kb++) tma_load_2d(smem + kb * STAGE_BYTES, &map_x, kb * TC_BK, m0, &full[kb]);
+            for (int kb = early; kb < num_kb; kb++) {
+                const int s = kb % TC_STAGES;
+                if (!mbar_wait(&empty[s], ((kb / TC_STAGES) & 1) ^ 1)) { give_up(error, &failed, 1); break; }
+                mbar_expect_tx(&full[s], STAGE_BYTES);
+                tma_load_2d(smem + s * STAGE_BYTES, &map_x, kb * TC_BK, m0, &full[s]);
+                load_w(kb, s);
             }
         }
     } else if (warp == 1) {
@@ -189,6 +203,8 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
         // epilogue: warp w reads lanes 32*(w%4) .. +31 of the accumulator, one output row per thread
         const int quarter = warp & 3;
         const int row = m0 + quarter * 32 + lane;
+        dependency_wait();                 // what this block reads besides weights, and everything it writes, is after the kernel before
+        let_dependents_start();
         // the residual sum's old values for the first 64 columns are read while the tensor core works
         float4 pre[2][8];
         if (EPI == TC_ACC && row < M && (N % 4 == 0)) {
@@ -201,6 +217,15 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
                     for (int j = 0; j < 8; j++) pre[c2][j] = *reinterpret_cast<const float4*>(o + 4 * j);
                 }
             }
+        }
+        // the rotation's cosines and sines of this row's position: read while the tensor core works
+        float4 rc[BN / 8], rs[BN / 8];
+        if (EPI == TC_ROPE && row < M && blockIdx.x < ex.nh + ex.nkv) {
+            const int p0 = ex.positions[row];
+            const float4* cp = reinterpret_cast<const float4*>(ex.cos_t + (size_t)p0 * (BN / 2));
+            const float4* sp = reinterpret_cast<const float4*>(ex.sin_t + (size_t)p0 * (BN / 2));
+#pragma unroll
+            for (int j = 0; j < BN / 8; j++) { rc[j] = cp[j]; rs[j] = sp[j]; }
         }
         if (!mbar_wait(acc_full, 0)) {
             if (lane == 0) give_up(error, &failed, 3);
@@ -246,7 +271,6 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
             const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
             const int head = blockIdx.x;
             const bool is_q = head < ex.nh, is_k = !is_q && head < ex.nh + ex.nkv;
-            const int pos = row < M ? ex.positions[row] : 0;
             const int sl = row < M ? ex.slot[row] : -1;
             __nv_bfloat16* dst = nullptr;           // where this row's head goes (null: nowhere)
             if (row < M) {
@@ -273,7 +297,10 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
                             const float a = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ar[j + e])));
                             const float b = __bfloat162float(__float2bfloat16_rn(__uint_as_float(br[j + e])));
                             if (is_q || is_k) {
-                                const float cs = ex.cos_t[(size_t)pos * HALF + c + j + e], sn = ex.sin_t[(size_t)pos * HALF + c + j + e];
+                                const int ti = c + j + e;                  // index into this row of the tables
+                                const float4 c4 = rc[ti / 4], s4 = rs[ti / 4];
+                                const float cs = (ti & 3) == 0 ? c4.x : (ti & 3) == 1 ? c4.y : (ti & 3) == 2 ? c4.z : c4.w;
+                                const float sn = (ti & 3) == 0 ? s4.x : (ti & 3) == 1 ? s4.y : (ti & 3) == 2 ? s4.z : s4.w;
                                 ra[e] = a * cs - b * sn;
                                 rb[e] = b * cs + a * sn;
                             } else { ra[e] = a; rb[e] = b; }
@@ -386,15 +413,14 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int
 template <int BN, int EPI>
 static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int M, int N, int K, int* error, cudaStream_t stream,
                      const TcExtra& ex = TcExtra{}) {
-    const size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + 128;
+    const size_t smem = (size_t)TcStages<BN>::N * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + 128;
     auto kern = linear_tcgen05_kernel<BN, EPI>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const int tile_cols = EPI == TC_SWIGLU ? BN / 2 : BN;
     const int cols = EPI == TC_SWIGLU ? ex.inter : N;
     dim3 grid((cols + tile_cols - 1) / tile_cols, (M + TC_BM - 1) / TC_BM);
-    kern<<<grid, TC_THREADS, smem, stream>>>(mx, mw, out, M, N, K, error, ex);
-    return launch_status();
+    return launch_plain(kern, grid, dim3(TC_THREADS), smem, stream, mx, mw, out, M, N, K, error, ex);
 }
 
 }  // namespace vk
