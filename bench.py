@@ -204,6 +204,37 @@ def prefill_run(model_dir, clocks, repeats=5):
     return {"value": T * 1e3 / ms, "tokens": T, "ms": ms, "flops": flops, "host_issue_ms": sorted(host)[len(host) // 2]}
 
 
+def gemm_run(pk, M=2048, reps=20):
+    """TFLOP/s of the tcgen05 product at the projection shapes of SmolLM2-135M / 360M / 1.7B, M rows of activations.
+    Operands are rotated through a set larger than L2 so that no launch finds its weights cached."""
+    import torch
+    from vitna_anchor_b200 import ops
+    shapes = {"135M qkv": (960, 576), "135M gate_up": (3072, 576), "135M down": (576, 1536),
+              "360M gate_up": (5120, 960), "360M down": (960, 2560),
+              "1.7B qkv": (6144, 2048), "1.7B o": (2048, 2048), "1.7B gate_up": (16384, 2048), "1.7B down": (2048, 8192)}
+    out = {}
+    for name, (N, K) in shapes.items():
+        copies = max(2, int(160e6 // (N * K * 2)) + 1)
+        ws = [(torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(copies)]
+        x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        for i in range(3):
+            ops.linear_tcgen05(x, ws[i % copies], y, ops.LINEAR_SAME)
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for i in range(reps):
+            ops.linear_tcgen05(x, ws[i % copies], y, ops.LINEAR_SAME)
+        ev1.record()
+        torch.cuda.synchronize()
+        ops.check_device_errors()
+        us = ev0.elapsed_time(ev1) * 1e3 / reps
+        tf = 2.0 * M * N * K / (us * 1e-6) / 1e12
+        out[name] = {"us": round(us, 1), "tflops": round(tf, 1), "frac": round(tf / pk["bf16_tflops"], 3)}
+        del ws
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -213,6 +244,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the prefill")
     ap.add_argument("--only-prefill", action="store_true", help="run the prefill measurement alone (for profiling)")
+    ap.add_argument("--only-gemm", action="store_true", help="time the tcgen05 product alone at the models' shapes, M = 2,048")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "pip cannot install the reference offline: it is a C program with a "
@@ -229,6 +261,9 @@ def main():
     model_dir = model_folder()
     clocks = ClockSampler()
     clocks.start()
+    if a.only_gemm:
+        print(json.dumps({"gemm_m2048": gemm_run(pk)}))
+        return 0
     if a.only_prefill:
         pf = prefill_run(model_dir, clocks, repeats=3)
         clocks.stop()

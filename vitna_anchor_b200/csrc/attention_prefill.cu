@@ -40,6 +40,12 @@ __device__ __forceinline__ void mma16816(float* d, const uint32_t* a, uint32_t b
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x by the special-function unit (about 2 units in the last place of float32; 2^-inf = 0).
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -167,16 +173,26 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
             // every key of the tile visible to every row of this warp: no mask to apply
             const int warp_lo_last = (window > 0 && pos0 + warp * 16 + 15 - window + 1 > 0) ? pos0 + warp * 16 + 15 - window + 1 : 0;
             const bool all_visible = kt * PF_BN + PF_BN - 1 <= pos0 + warp * 16 && kt * PF_BN >= warp_lo_last;
+            // the running maximum is kept of the raw scores (the scale is positive); the scale and log2 e go into
+            // the exponent's multiply-add.  Only tiles that touch the diagonal or a window's edge need the mask.
+            if (all_visible) {
 #pragma unroll
-            for (int nb = 0; nb < 8; nb++) {
+                for (int nb = 0; nb < 8; nb++) {
+                    mx[0] = fmaxf(mx[0], fmaxf(s[nb][0], s[nb][1]));
+                    mx[1] = fmaxf(mx[1], fmaxf(s[nb][2], s[nb][3]));
+                }
+            } else {
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const int key = kt * PF_BN + nb * 8 + qd * 2 + (e & 1);
-                    const bool second = e >= 2;
-                    const int pos = second ? pos_b : pos_a, lo = second ? lo_b : lo_a;
-                    const float v = (all_visible || (key <= pos && key >= lo)) ? s[nb][e] * scale_log2 : -INFINITY;
-                    s[nb][e] = v;
-                    mx[second] = fmaxf(mx[second], v);
+                for (int nb = 0; nb < 8; nb++) {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const int key = kt * PF_BN + nb * 8 + qd * 2 + (e & 1);
+                        const bool second = e >= 2;
+                        const int pos = second ? pos_b : pos_a, lo = second ? lo_b : lo_a;
+                        const float v = (key <= pos && key >= lo) ? s[nb][e] : -INFINITY;
+                        s[nb][e] = v;
+                        mx[second] = fmaxf(mx[second], v);
+                    }
                 }
             }
 #pragma unroll
@@ -184,22 +200,22 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
             }
-            float corr[2], m_new[2];
+            float corr[2], m_new[2];      // m_new: minus the reference maximum times scale * log2 e
 #pragma unroll
             for (int r = 0; r < 2; r++) {
-                m_new[r] = fmaxf(m_run[r], mx[r]);
+                const float mm = fmaxf(m_run[r], mx[r]);
                 // a row with no key yet (all masked so far) keeps m = -inf: use 0 as the reference so that exp gives 0
-                const float ref = m_new[r] == -INFINITY ? 0.0f : m_new[r];
-                corr[r] = exp2f(m_run[r] - ref);         // exp2(-inf) = 0 on the first tile with keys
-                m_run[r] = m_new[r];
-                m_new[r] = ref;
+                const float ref = mm == -INFINITY ? 0.0f : mm;
+                corr[r] = ex2_approx((m_run[r] - ref) * scale_log2);     // 2^(-inf) = 0 on the first tile with keys
+                m_run[r] = mm;
+                m_new[r] = -ref * scale_log2;
             }
             float rs[2] = {0.0f, 0.0f};
             uint32_t pf[4][4], pl[4][4];                 // P as A fragments, high and low parts: 4 k-steps of 16 keys
 #pragma unroll
             for (int nb = 0; nb < 8; nb++) {
-                const float p0 = exp2f(s[nb][0] - m_new[0]), p1 = exp2f(s[nb][1] - m_new[0]);
-                const float p2 = exp2f(s[nb][2] - m_new[1]), p3 = exp2f(s[nb][3] - m_new[1]);
+                const float p0 = ex2_approx(fmaf(s[nb][0], scale_log2, m_new[0])), p1 = ex2_approx(fmaf(s[nb][1], scale_log2, m_new[0]));
+                const float p2 = ex2_approx(fmaf(s[nb][2], scale_log2, m_new[1])), p3 = ex2_approx(fmaf(s[nb][3], scale_log2, m_new[1]));
                 rs[0] += p0 + p1;
                 rs[1] += p2 + p3;
                 const uint32_t h01 = pack_bf16(p0, p1), h23 = pack_bf16(p2, p3);
@@ -254,7 +270,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
             const float m1 = other[r], l1 = other[2 + r];
             const float mm = fmaxf(m_run[r], m1);
             const float ref = mm == -INFINITY ? 0.0f : mm;
-            const float c0 = exp2f(m_run[r] - ref), c1 = exp2f(m1 - ref);
+            const float c0 = ex2_approx((m_run[r] - ref) * scale_log2), c1 = ex2_approx((m1 - ref) * scale_log2);
             l_run[r] = l_run[r] * c0 + l1 * c1;
 #pragma unroll
             for (int i = 0; i < DBLK; i++) {
