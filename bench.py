@@ -30,10 +30,20 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: SmolLM2-135M
-SIZES = dict(num_hidden_layers=30, hidden_size=576, intermediate_size=1536, num_attention_heads=9, num_key_value_heads=3,
-             head_dim=64, vocab_size=49152, max_position_embeddings=8192, rms_norm_eps=1e-5, rope_theta=100000.0,
-             tie_word_embeddings=True)
+# BASELINE.json configs[2..4]: SmolLM2-135M (the default), 360M and 1.7B
+MODELS = {
+    "135M": dict(num_hidden_layers=30, hidden_size=576, intermediate_size=1536, num_attention_heads=9, num_key_value_heads=3,
+                 head_dim=64, vocab_size=49152, max_position_embeddings=8192, rms_norm_eps=1e-5, rope_theta=100000.0,
+                 tie_word_embeddings=True),
+    "360M": dict(num_hidden_layers=32, hidden_size=960, intermediate_size=2560, num_attention_heads=15, num_key_value_heads=5,
+                 head_dim=64, vocab_size=49152, max_position_embeddings=8192, rms_norm_eps=1e-5, rope_theta=100000.0,
+                 tie_word_embeddings=True),
+    "1.7B": dict(num_hidden_layers=24, hidden_size=2048, intermediate_size=8192, num_attention_heads=32, num_key_value_heads=32,
+                 head_dim=64, vocab_size=49152, max_position_embeddings=8192, rms_norm_eps=1e-5, rope_theta=130000.0,
+                 tie_word_embeddings=True),
+}
+MODEL_NAME = "135M"
+SIZES = dict(MODELS[MODEL_NAME])
 PROMPT_LEN, CONTEXT, KV_BLOCK, PREFILL_TOKENS = 2048, 4096, 16, 2048
 
 
@@ -102,7 +112,7 @@ def model_folder(seed=0):
         t0 = time.time()
         write_random_model(d, cfg, seed)
         open(os.path.join(d, "done"), "w").close()
-        print(f"[bench] wrote random SmolLM2-135M weights to {d} in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
+        print(f"[bench] wrote random SmolLM2-{MODEL_NAME} weights to {d} in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
     return d
 
 
@@ -242,6 +252,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="135M", choices=sorted(MODELS), help="layer sizes: SmolLM2-135M (the default), 360M or 1.7B")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the prefill")
     ap.add_argument("--only-prefill", action="store_true", help="run the prefill measurement alone (for profiling)")
     ap.add_argument("--only-gemm", action="store_true", help="time the tcgen05 product alone at the models' shapes, M = 2,048")
@@ -254,6 +265,10 @@ def main():
         print(f"bench.py measures one GPU; --gpus {a.gpus} is not supported by this engine")
         return 2
     a.warmup = max(a.warmup, 3)
+    global MODEL_NAME
+    MODEL_NAME = a.model
+    SIZES.clear()
+    SIZES.update(MODELS[a.model])
     import torch
     from vitna_anchor_b200 import ops
     ops.lib()
@@ -280,11 +295,12 @@ def main():
     clocks.stop()
     achieved = main_run["bytes"] / (main_run["ms_per_step"] * 1e-3) / 1e9
     line = {
-        "metric": "decode tokens/s, SmolLM2-135M random weights, batch 8 from 2,048-token prompts", "value": main_run["value"],
+        "metric": f"decode tokens/s, SmolLM2-{MODEL_NAME} random weights, batch {a.batch} from 2,048-token prompts", "value": main_run["value"],
         "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "ms_per_step": main_run["ms_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights and uniform-random token ids", "impl": "ours",
-        "config": {"model": "SmolLM2-135M", "layers": SIZES["num_hidden_layers"], "layers_of_model": 30, "hidden": SIZES["hidden_size"],
+        "config": {"model": f"SmolLM2-{MODEL_NAME}", "layers": SIZES["num_hidden_layers"], "layers_of_model": SIZES["num_hidden_layers"],
+                   "hidden": SIZES["hidden_size"],
                    "heads": SIZES["num_attention_heads"], "kv_heads": SIZES["num_key_value_heads"], "head_dim": SIZES["head_dim"],
                    "intermediate": SIZES["intermediate_size"], "vocab": SIZES["vocab_size"], "global_batch": a.batch,
                    "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "context_mean": round(main_run["context_mean"]),
