@@ -35,6 +35,7 @@ struct MmaParams {
     const __nv_bfloat16* w;      // [N, K]
     void* out;
     int M, N, K, ldx, kc, ks;    // kc: columns staged at a time (a multiple of 32 * ks); ks: warps = splits of K
+    int tpb;                     // tiles of eight units a block works through with one staging of x
     const int32_t* positions;
     const float* cos_t;
     const float* sin_t;
@@ -130,12 +131,12 @@ __global__ void __launch_bounds__(256) skinny_mma_kernel(const MmaParams p) {
     const int K = p.K, ks = p.ks;
     const int units = (EPI == ME_SWIGLU) ? p.N / 2 : (p.N + 1) / 2;
 
-    // this lane's two weight rows: the first and second row of unit (tile*8 + g)
-    const int u = blockIdx.x * 8 + g;
-    const bool on = u < units;
+    // this lane's two weight rows: the first and second row of unit (tile*8 + g); the block starts at tile blockIdx.x * tpb
+    int u = blockIdx.x * p.tpb * 8 + g;
+    bool on = u < units;
     int r0 = 0, r1 = 0;
     if (on) mma_unit_rows<EPI>(p, u, r0, r1);
-    const bool has1 = on && r1 < p.N;
+    bool has1 = on && r1 < p.N;
     const T* w0 = p.w + (size_t)r0 * K;
     const T* w1 = p.w + (size_t)(has1 ? r1 : r0) * K;
 
@@ -208,12 +209,25 @@ __global__ void __launch_bounds__(256) skinny_mma_kernel(const MmaParams p) {
         }
     }
 
+    const bool one_chunk = p.kc >= K;                   // then x is staged once for all of the block's tiles
+  for (int it = 0; it < p.tpb; it++) {
+    if (it > 0) {
+        u += 8;
+        if ((u - g) >= units) break;                    // the same for the whole block
+        on = u < units;
+        r0 = r1 = 0;
+        if (on) mma_unit_rows<EPI>(p, u, r0, r1);
+        has1 = on && r1 < p.N;
+        w0 = p.w + (size_t)r0 * K;
+        w1 = p.w + (size_t)(has1 ? r1 : r0) * K;
+    }
     float d[MG][4];
 #pragma unroll
     for (int mg = 0; mg < MG; mg++) { d[mg][0] = d[mg][1] = d[mg][2] = d[mg][3] = 0.0f; }
 
     for (int kb = 0; kb < K; kb += p.kc) {
         const int kn = min(p.kc, K - kb);               // a multiple of 32
+        if (it == 0 || !one_chunk) {
         __syncthreads();                                // inv_rms is written; the previous chunk has been read
         // stage rows 0..M-1 (rows up to MG*8 are zero) of columns kb .. kb+kn
         for (int m = warp; m < MG * 8; m += ks) {
@@ -243,11 +257,12 @@ __global__ void __launch_bounds__(256) skinny_mma_kernel(const MmaParams p) {
             }
         }
         __syncthreads();
+        }
         // this warp's share of the chunk: the runs of 32 columns whose index is warp modulo ks.  A chunk starts
         // at a multiple of 32 * ks, so which warp adds a run, and in which order, depends on K alone.
         const int nblk = kn / 32;
         for (int b = warp; b < nblk; b += UN * ks) {
-            if (kb != 0 || b != warp) {                 // the first batch of the first chunk is already on its way
+            if (it != 0 || kb != 0 || b != warp) {      // the first batch of the block's first tile is already on its way
 #pragma unroll
                 for (int i = 0; i < UN; i++) {
                     if (b + i * ks < nblk) {
@@ -284,10 +299,12 @@ __global__ void __launch_bounds__(256) skinny_mma_kernel(const MmaParams p) {
         if (!on) continue;
         // lane (g, q): unit u; batch rows mg*8 + 2q and + 1; s.x, s.y are row r0's sums, s.z, s.w row r1's
         const int m = mg * 8 + 2 * q;
-        const bool first = mg == warp;                  // this pass has its extras in registers already
+        const bool first = it == 0 && mg == warp;       // this pass has its extras in registers already
         if (m < p.M) mma_finish<EPI>(p, u, r0, r1, has1, m, s.x, s.z, first, pre_slot[0], pre_cos[0], pre_sin[0], old[0]);
         if (m + 1 < p.M) mma_finish<EPI>(p, u, r0, r1, has1, m + 1, s.y, s.w, first, pre_slot[1], pre_cos[1], pre_sin[1], old[1]);
     }
+    __syncthreads();                                    // the partial sums have been read: the next tile may write its own
+  }
 }
 
 template <int EPI, bool NORM>
@@ -309,7 +326,13 @@ static int launch_mma(MmaParams p, cudaStream_t stream) {
     if (kc <= 0) return VK_TOO_LARGE;
     p.kc = kc;
     const int units = (EPI == ME_SWIGLU) ? p.N / 2 : (p.N + 1) / 2;
-    const int blocks = (units + 7) / 8;
+    const int tiles = (units + 7) / 8;
+    // a block stages x (and computes the norm) for itself: with many tiles a block takes several, as long as
+    // about two blocks a multiprocessor remain
+    int tpb = tiles / (2 * 148);
+    tpb = tpb < 1 ? 1 : (tpb > 8 ? 8 : tpb);
+    p.tpb = tpb;
+    const int blocks = (tiles + tpb - 1) / tpb;
     const size_t smem = (size_t)rows * (kc + MM_XPAD) * 2 + (size_t)ks * mg * 32 * 4 * sizeof(float);
 #define LAUNCH(MGV)                                                                                                         \
     {                                                                                                                       \
@@ -359,7 +382,7 @@ VK_API int vk_linear_skinny_mma(const void* x, const int32_t* rows, const float*
             !slot || !cache)
             return VK_BAD_SHAPE;
     }
-    MmaParams p{x, rows, norm_w, eps, (const __nv_bfloat16*)w, out, M, N, K, ldx, 0, 0, positions, cos_t, sin_t, slot,
+    MmaParams p{x, rows, norm_w, eps, (const __nv_bfloat16*)w, out, M, N, K, ldx, 0, 0, 1, positions, cos_t, sin_t, slot,
                 (__nv_bfloat16*)cache, nh, nkv, hd, page_size};
     return norm_w ? mma_dispatch<true>(epi, p, stream) : mma_dispatch<false>(epi, p, stream);
 }
