@@ -240,7 +240,7 @@ class ModelRunner:
         return logits
 
     # -- decoding through CUDA graphs -----------------------------------------------------------
-    def _decode_context(self, entries: Sequence[StepEntry], B: int) -> Tuple[StepContext, torch.Tensor]:
+    def _decode_context(self, entries: Sequence[StepEntry], B: int, views: bool = True):
         """The context of a batch of single tokens, padded to B segments, at fixed offsets in the
         metadata buffer so that a captured graph finds every array where it was at capture.  A padding
         segment has one token at position 0 that writes nothing (slot -1) and reads page 0."""
@@ -281,8 +281,11 @@ class ModelRunner:
                 bt[i, :len(row)] = row
         dev = self._meta_dev
         dev[:total].copy_(st.host[:total], non_blocking=True)
-        st.event = torch.cuda.Event()
+        if st.event is None:
+            st.event = torch.cuda.Event()
         st.event.record()
+        if not views:               # a replay needs the arrays in place, not their description
+            return None, None
         groups = []
         for g in range(n_groups):
             o_sm = o_groups + g * (B + B * maxb)
@@ -301,8 +304,8 @@ class ModelRunner:
         while B < S:
             B *= 2
         B = min(B, self.max_segments) if S <= self.max_segments else S
-        ctx, rows = self._decode_context(entries, B)
         held = self._graphs.get(B)
+        ctx, rows = self._decode_context(entries, B, views=held is None)
         if held is None:
             # the first batch of this size runs eagerly (it also makes the workspace buffers), then the
             # same launches are captured; the captured graph is replayed from the next step on

@@ -60,6 +60,19 @@ class Request:
         return self.prompt + self.output
 
     @property
+    def last_token(self) -> int:
+        return self.output[-1] if self.output else self.prompt[-1]
+
+    def tokens_between(self, a: int, b: int) -> List[int]:
+        """tokens[a:b] without building the whole list."""
+        n = len(self.prompt)
+        if b <= n:
+            return self.prompt[a:b]
+        if a >= n:
+            return self.output[a - n:b - n]
+        return self.prompt[a:] + self.output[:b - n]
+
+    @property
     def remaining(self) -> int:
         """Tokens not yet run through the model."""
         return len(self.prompt) + len(self.output) - self.num_computed
@@ -144,7 +157,7 @@ class Scheduler:
                 break
             self._preempt(self.running[-1])    # most recently admitted; may be the one that lacked the page
         for req in decodes:
-            plan.append(Planned(req, [req.tokens[-1]], True))
+            plan.append(Planned(req, [req.last_token], True))
         budget -= len(decodes)
         planned_ids = {p.request.request_id for p in plan}
 
@@ -159,7 +172,7 @@ class Scheduler:
                 continue
             need = self._pages_for(req, n)
             free = [f - k for f, k in zip(free, need)]
-            toks = req.tokens[req.num_computed:req.num_computed + n]
+            toks = req.tokens_between(req.num_computed, req.num_computed + n)
             plan.append(Planned(req, toks, n == req.remaining))
             budget -= n
 
@@ -178,7 +191,7 @@ class Scheduler:
             self.running.append(req)
             need = self._pages_for(req, n)
             free = [f - k for f, k in zip(free, need)]
-            toks = req.tokens[req.num_computed:req.num_computed + n]
+            toks = req.tokens_between(req.num_computed, req.num_computed + n)
             plan.append(Planned(req, toks, n == req.remaining))
             budget -= n
         if not plan and self.has_work():
