@@ -206,35 +206,64 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_rows_kernel(
     if (tid == 0) out[r] = id >= 0 ? id : 0;
 }
 
-// Greedy only: ids[r] = lowest id of the maximum of logits[r, :].
-__global__ void __launch_bounds__(SAMPLE_THREADS) argmax_rows_kernel(const float* __restrict__ logits, int32_t* __restrict__ out,
-                                                                     int vocab) {
-    __shared__ float scratch[32];
-    __shared__ int best_id;
-    const int r = blockIdx.x, tid = threadIdx.x;
+// Greedy only: ids[r] = lowest id of the maximum of logits[r, :].  A row is shared by `parts` blocks (grid.y);
+// each packs its best (value, id) into one 64-bit key whose order is "larger value first, then lower id" and
+// folds it into the row's slot with atomicMax; the slot starts at zero (the host clears it on the stream) and the
+// block that arrives last writes the id and leaves the slot zero for the next launch.
+__device__ __forceinline__ unsigned long long argmax_key(float v, int id) {
+    uint32_t b = __float_as_uint(v + 0.0f);                   // -0 becomes +0: equal values, equal keys
+    b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);          // order-preserving map of float32 to unsigned
+    return ((unsigned long long)b << 32) | (uint32_t)(0x7fffffff - id);
+}
+
+__global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ logits, int32_t* __restrict__ out,
+                                                          unsigned long long* __restrict__ slots, int* __restrict__ arrived, int vocab) {
+    __shared__ unsigned long long wbest[8];
+    const int r = blockIdx.x, part = blockIdx.y, parts = gridDim.y, tid = threadIdx.x;
+    dependency_wait();
     const float* l = logits + (size_t)r * vocab;
-    float mx = -INFINITY;
-    for (int i = tid; i < vocab; i += blockDim.x) mx = fmaxf(mx, l[i]);
-    mx = block_max(mx, scratch);
-    if (tid == 0) best_id = vocab;
+    const int per = (vocab + parts - 1) / parts;
+    const int lo = part * per, hi = min(vocab, lo + per);
+    unsigned long long best = 0;                              // below every real key (a NaN maps above or below, never 0... ids keep it distinct)
+    for (int i = lo + tid; i < hi; i += 256) {
+        const unsigned long long k = argmax_key(l[i], i);
+        best = k > best ? k : best;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    if ((tid & 31) == 0) wbest[tid >> 5] = best;
     __syncthreads();
-    int mine = vocab;
-    for (int i = tid; i < vocab; i += blockDim.x)
-        if (l[i] == mx && i < mine) mine = i;
-    if (mine < vocab) atomicMin(&best_id, mine);
-    __syncthreads();
-    if (tid == 0) out[r] = best_id < vocab ? best_id : 0;
+    if (tid == 0) {
+        for (int w = 1; w < 8; w++) best = wbest[w] > best ? wbest[w] : best;
+        atomicMax(&slots[r], best);
+        __threadfence();
+        if (atomicAdd(&arrived[r], 1) == parts - 1) {
+            __threadfence();
+            const unsigned long long k = atomicExch(&slots[r], 0ull);
+            out[r] = k ? (int)(0x7fffffff - (uint32_t)(k & 0xffffffffu)) : 0;
+            arrived[r] = 0;
+        }
+    }
 }
 
 }  // namespace vk
 
 using namespace vk;
 
-VK_API int vk_argmax_rows(const float* logits, int32_t* out, int rows, int vocab, cudaStream_t stream) {
+// scratch: rows * 12 bytes (a 64-bit slot and an arrival counter per row), zero before the first launch; the kernel
+// leaves it zero.
+VK_API int vk_argmax_rows(const float* logits, int32_t* out, void* scratch, int rows, int vocab, cudaStream_t stream) {
     if (rows <= 0) return VK_OK;
-    if (vocab <= 0) return VK_BAD_SHAPE;
-    argmax_rows_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, out, vocab);
-    return launch_status();
+    if (vocab <= 0 || !scratch) return VK_BAD_SHAPE;
+    if ((uintptr_t)scratch % 8) return VK_BAD_ALIGNMENT;
+    // enough blocks a row to use the machine: about 4096 columns each, at most 32 parts
+    int parts = (vocab + 4095) / 4096;
+    parts = parts < 1 ? 1 : (parts > 32 ? 32 : parts);
+    unsigned long long* slots = (unsigned long long*)scratch;
+    int* arrived = (int*)(slots + rows);
+    return launch_dependent(argmax_rows_kernel, dim3(rows, parts), dim3(256), 0, stream, logits, out, slots, arrived, vocab);
 }
 
 // probs: scratch [rows, vocab] float32.  temperature <= 0 on a row means greedy for that row.

@@ -240,12 +240,19 @@ def add_inplace(y: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
     return y
 
 
+_argmax_scratch = None
+
+
 def argmax_rows(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[r] = the lowest id among the maxima of logits[r, :]."""
     _req(logits, "logits", torch.float32, 2); _req(out, "out", torch.int32, 1)
     if out.shape[0] != logits.shape[0]:
         raise KernelError("argmax_rows: out and logits differ in rows")
-    _check(lib().vk_argmax_rows(_p(logits), _p(out), logits.shape[0], logits.shape[1], _stream()), "argmax_rows")
+    global _argmax_scratch
+    rows = logits.shape[0]
+    if _argmax_scratch is None or _argmax_scratch.numel() < rows * 12 or _argmax_scratch.device != logits.device:
+        _argmax_scratch = torch.zeros(max(rows, 256) * 12, dtype=torch.uint8, device=logits.device)
+    _check(lib().vk_argmax_rows(_p(logits), _p(out), _p(_argmax_scratch), rows, logits.shape[1], _stream()), "argmax_rows")
     return out
 
 
