@@ -349,6 +349,7 @@ def linear_tcgen05_rope(x: torch.Tensor, wqkv: torch.Tensor, q_out: torch.Tensor
 
 EPI_SAME, EPI_F32, EPI_ACC, EPI_SWIGLU, EPI_ROPE = 0, 1, 2, 3, 4
 SKINNY_MAX_ROWS = 64
+FUSED_NORM_MAX_ROWS = 16     # every block of the few-rows kernel recomputes the norm of all rows: beyond this a norm kernel runs once
 
 
 def skinny_takes(dtype: torch.dtype, M: int, K: int, N: int = 0) -> bool:

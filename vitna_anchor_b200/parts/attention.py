@@ -43,7 +43,8 @@ class PagedAttention(Mixer):
 
     def fuses_norm(self, norm, ctx: StepContext) -> bool:
         from .norms import RMSNorm
-        return isinstance(norm, RMSNorm) and ops.skinny_takes(ctx.dtype, ctx.num_tokens, self.hidden, self.qd + 2 * self.kvd)
+        return (isinstance(norm, RMSNorm) and ctx.num_tokens <= ops.FUSED_NORM_MAX_ROWS
+                and ops.skinny_takes(ctx.dtype, ctx.num_tokens, self.hidden, self.qd + 2 * self.kvd))
 
     def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCacheView, residual: torch.Tensor,
                 write_cache: bool = True, norm=None) -> None:
@@ -56,6 +57,11 @@ class PagedAttention(Mixer):
         if norm is not None and rot == self.hd and write_cache:
             # few rows: norm, the three projections, the rotation and the cache write in one launch
             q = ops.linear_skinny(xn, self.wqkv, q_buf, ops.EPI_ROPE, norm_weight=norm.weight, eps=norm.eps,
+                                  rope=(ctx.positions, cos, sin, meta.slot_mapping, cache.pages, self.nh, self.nkv, self.hd))
+        elif (norm is None and rot == self.hd and write_cache and xn.stride(0) % 8 == 0 and xn.data_ptr() % 16 == 0
+              and ops.skinny_takes(ctx.dtype, T, self.hidden, self.qd + 2 * self.kvd)):
+            # a few dozen rows: the norm ran once for all of them; projections, rotation and cache write in one launch
+            q = ops.linear_skinny(xn, self.wqkv, q_buf, ops.EPI_ROPE,
                                   rope=(ctx.positions, cos, sin, meta.slot_mapping, cache.pages, self.nh, self.nkv, self.hd))
         elif (norm is None and T > ops.SKINNY_MAX_ROWS and rot == self.hd and self.hd in (64, 128) and write_cache
               and ops.tcgen05_takes(xn, self.wqkv)):

@@ -21,7 +21,8 @@ class SwiGLU(FeedForward):
 
     def fuses_norm(self, norm, ctx: StepContext) -> bool:
         from .norms import RMSNorm
-        return isinstance(norm, RMSNorm) and ops.skinny_takes(ctx.dtype, ctx.num_tokens, self.hidden, 2 * self.intermediate)
+        return (isinstance(norm, RMSNorm) and ctx.num_tokens <= ops.FUSED_NORM_MAX_ROWS
+                and ops.skinny_takes(ctx.dtype, ctx.num_tokens, self.hidden, 2 * self.intermediate))
 
     def forward(self, xn: torch.Tensor, ctx: StepContext, residual: torch.Tensor, norm=None) -> None:
         T = ctx.num_tokens
@@ -30,6 +31,10 @@ class SwiGLU(FeedForward):
         if norm is not None:
             # few rows: norm, gate and up, and silu(gate) * up in one launch
             act = ops.linear_skinny(xn, self.w_gate_up, act_buf, ops.EPI_SWIGLU, norm_weight=norm.weight, eps=norm.eps)
+        elif (xn.stride(0) % 8 == 0 and xn.data_ptr() % 16 == 0
+              and ops.skinny_takes(ctx.dtype, T, self.hidden, 2 * self.intermediate)):
+            # a few dozen rows: the norm ran once for all of them; gate, up and silu(gate) * up in one launch
+            act = ops.linear_skinny(xn, self.w_gate_up, act_buf, ops.EPI_SWIGLU)
         elif T > ops.SKINNY_MAX_ROWS and self.intermediate % 8 == 0 and ops.tcgen05_takes(xn, self.w_gate_up):
             # prompt-sized batch in bfloat16: gate, up and silu(gate) * up in one tcgen05 kernel
             act = ops.linear_tcgen05_swiglu(xn, self.w_gate_up, act_buf)
