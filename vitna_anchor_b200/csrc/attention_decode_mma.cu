@@ -5,7 +5,8 @@
 // (token, kv-head tile) combines them in split order.  What differs is the arithmetic of a block: the
 // query heads that share a key-value head (up to 16 a block) are the 16 rows of an m16n8k16 product.
 //
-//   copy      keys and values of the split into shared memory with cp.async (one trip for both)
+//   copy      keys and values of the split into shared memory with cp.async (one trip for both); the queries go
+//             straight from global memory into the registers of the 16-row operand
 //   scores    warp w: S[16 heads x 32 keys] = Q K^T for keys 32w .. 32w+31
 //   softmax   row maximum and row sum over the split's 256 keys (through shared memory), float32
 //   p * v     the probabilities go to shared memory as a high and a low bfloat16 part (p = hi + lo to
@@ -36,85 +37,114 @@ __device__ __forceinline__ void dm_mma(float* d, const uint32_t* a, uint32_t b0,
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <int HD>
-__global__ void __launch_bounds__(DM_THREADS, 2) attention_decode_mma_kernel(
-    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_tables,
-    const int32_t* __restrict__ token_seg, const int32_t* __restrict__ positions, const int32_t* __restrict__ tok_list,
-    __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int nh,
-    int nkv, int page_size, int max_blocks, int max_splits, int counter_tiles, float scale, int window) {
-    typedef __nv_bfloat16 T;
-    constexpr int LD = HD + 8;                  // padded rows: ldmatrix and 16-byte copies stay free of bank conflicts
-    constexpr int LP = DM_SPLIT + 8;            // padded rows of P
-    constexpr int KSTEPS = HD / 16, DBLK = HD / 8;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    T* sk = reinterpret_cast<T*>(smem_raw);     // [256][LD]
-    T* sv = sk + DM_SPLIT * LD;                 // [256][LD]
-    T* sq = sv + DM_SPLIT * LD;                 // [16][LD]
-    T* sph = sq + DM_ROWS * LD;                 // [16][LP] high parts of p
-    T* spl = sph + DM_ROWS * LP;                // [16][LP] low parts
-    float* wstat = reinterpret_cast<float*>(spl + DM_ROWS * LP);   // [8 warps][16 rows]: maxima, then sums
-    float* wts = wstat + 8 * DM_ROWS;           // [16][max 128 splits] weights of the combine
-    __shared__ float row_m[DM_ROWS], row_l[DM_ROWS];
-    __shared__ int is_last;
+// One unit of work: a token, a tile of up to 16 query heads that share a key-value head, a split of 256 keys.
+struct DmItem {
+    bool active;
+    int zi, t, y, split, kvh, h0, gt, pos, lo, first_split, last_split, n_active, k0, nkeys;
+    const int32_t* bt;
+};
 
-    const int g = nh / nkv;
+struct DmArgs {
+    const __nv_bfloat16* q;
+    const __nv_bfloat16* cache;
+    const int32_t* block_tables;
+    const int32_t* token_seg;
+    const int32_t* positions;
+    const int32_t* tok_list;
+    __nv_bfloat16* out;
+    float* part_o;
+    float* part_ml;
+    int* counters;
+    int nh, nkv, page_size, max_blocks, max_splits, counter_tiles;
+    float scale;
+    int window;
+};
+
+__device__ __forceinline__ DmItem dm_item(const DmArgs& a, int zi, int y, int split) {
+    DmItem it;
+    const int g = a.nh / a.nkv;
     const int tiles_per_kv = (g + DM_ROWS - 1) / DM_ROWS;
-    const int split = blockIdx.x;
-    const int kvh = blockIdx.y / tiles_per_kv;
-    const int h0 = kvh * g + (blockIdx.y % tiles_per_kv) * DM_ROWS;
-    const int gt = min(DM_ROWS, kvh * g + g - h0);
-    const int zi = blockIdx.z;
-    const int t = tok_list ? tok_list[zi] : zi;
+    it.zi = zi; it.y = y; it.split = split;
+    it.kvh = y / tiles_per_kv;
+    it.h0 = it.kvh * g + (y % tiles_per_kv) * DM_ROWS;
+    it.gt = min(DM_ROWS, it.kvh * g + g - it.h0);
+    it.t = a.tok_list ? a.tok_list[zi] : zi;
+    it.pos = a.positions[it.t];
+    it.lo = (a.window > 0 && it.pos - a.window + 1 > 0) ? it.pos - a.window + 1 : 0;
+    it.first_split = it.lo / DM_SPLIT;
+    it.last_split = it.pos / DM_SPLIT;
+    it.active = split >= it.first_split && split <= it.last_split;
+    it.n_active = it.last_split - it.first_split + 1;
+    it.k0 = split * DM_SPLIT;
+    it.nkeys = min(DM_SPLIT, it.pos - it.k0 + 1);
+    it.bt = a.block_tables + (size_t)a.token_seg[it.t] * a.max_blocks;
+    return it;
+}
+
+// Ask for the item's keys and values (thread = key) with cp.async; rows that do not count are zeroed
+// (never counted, p = 0, but 0 * garbage must not be NaN).  No commit: the caller groups the copies.
+template <int HD>
+__device__ __forceinline__ void dm_copy(const DmArgs& a, const DmItem& it, __nv_bfloat16* sk, __nv_bfloat16* sv) {
+    typedef __nv_bfloat16 T;
+    constexpr int LD = HD + 8;
+    const int tid = threadIdx.x;
+    const int key = it.k0 + tid;
+    const bool valid = tid < it.nkeys && key >= it.lo;
+    T* dk = sk + tid * LD;
+    T* dv = sv + tid * LD;
+    if (valid) {
+        const size_t page_stride = (size_t)2 * a.nkv * a.page_size * HD;
+        const T* kr = a.cache + (size_t)it.bt[key / a.page_size] * page_stride + ((size_t)it.kvh * a.page_size + key % a.page_size) * HD;
+        const size_t v_off = (size_t)a.nkv * a.page_size * HD;
+#pragma unroll
+        for (int c = 0; c < HD; c += 8) {
+            dm_cp_async16(dk + c, kr + c);
+            dm_cp_async16(dv + c, kr + v_off + c);
+        }
+    } else {
+#pragma unroll
+        for (int c = 0; c < HD; c += 8) {
+            *reinterpret_cast<uint4*>(dk + c) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(dv + c) = make_uint4(0, 0, 0, 0);
+        }
+    }
+}
+
+// The queries of the item's heads as the 16-row operand of m16n8k16, straight from global memory into registers
+// (rows beyond the item's heads are zero): lane (gq, qd) holds rows gq and gq+8, columns 2qd, 2qd+1 and +8 of each k-step.
+template <int HD>
+__device__ __forceinline__ void dm_load_q(const DmArgs& a, const DmItem& it, uint32_t (*qf)[4]) {
+    const int lane = threadIdx.x & 31, gq = lane >> 2, qd = lane & 3;
+    const __nv_bfloat16* r0 = a.q + ((size_t)it.t * a.nh + it.h0 + gq) * HD + 2 * qd;
+    const __nv_bfloat16* r1 = r0 + (size_t)8 * HD;
+    const bool on0 = gq < it.gt, on1 = gq + 8 < it.gt;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ks++) {
+        qf[ks][0] = on0 ? *reinterpret_cast<const uint32_t*>(r0 + ks * 16) : 0u;
+        qf[ks][1] = on1 ? *reinterpret_cast<const uint32_t*>(r1 + ks * 16) : 0u;
+        qf[ks][2] = on0 ? *reinterpret_cast<const uint32_t*>(r0 + ks * 16 + 8) : 0u;
+        qf[ks][3] = on1 ? *reinterpret_cast<const uint32_t*>(r1 + ks * 16 + 8) : 0u;
+    }
+}
+
+// Everything after the copy has landed (and a block-wide barrier): scores, softmax, p * v, the partial or final
+// result, and the combine by the block that arrives last.  Ends with every thread past its last use of the buffers
+// except for a final barrier, which the caller provides before reusing them.
+template <int HD>
+__device__ __forceinline__ void dm_compute(const DmArgs& a, const DmItem& it, __nv_bfloat16* sk, __nv_bfloat16* sv,
+                                           const uint32_t (*qf)[4], __nv_bfloat16* sph, __nv_bfloat16* spl, float* wstat, float* wts,
+                                           float* row_m, float* row_l, int* is_last) {
+    typedef __nv_bfloat16 T;
+    constexpr int LD = HD + 8, LP = DM_SPLIT + 8, KSTEPS = HD / 16, DBLK = HD / 8;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gq = lane >> 2, qd = lane & 3;
-
-    const int pos = positions[t];
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int first_split = lo / DM_SPLIT, last_split = pos / DM_SPLIT;
-    if (split < first_split || split > last_split) return;
-    const int n_active = last_split - first_split + 1;
-    const int k0 = split * DM_SPLIT;
-    const int nkeys = min(DM_SPLIT, pos - k0 + 1);
-
-    const int32_t* bt = block_tables + (size_t)token_seg[t] * max_blocks;
-    const size_t page_stride = (size_t)2 * nkv * page_size * HD;
-    const size_t v_off = (size_t)nkv * page_size * HD;
-    const int key = k0 + tid;
-    const bool valid = tid < nkeys && key >= lo;
-    const size_t my_row = valid ? (size_t)bt[key / page_size] * page_stride + ((size_t)kvh * page_size + key % page_size) * HD : 0;
-
-    dependency_wait();                          // q and the cache come from the kernels before this one
-    let_dependents_start();
-
-    // ---- copy: thread = key -------------------------------------------------------------------------------
-    {
-        T* dk = sk + tid * LD;
-        T* dv = sv + tid * LD;
-        if (valid) {
-            const T* kr = cache + my_row;
-#pragma unroll
-            for (int c = 0; c < HD; c += 8) {
-                dm_cp_async16(dk + c, kr + c);
-                dm_cp_async16(dv + c, kr + v_off + c);
-            }
-        } else {                                // never counted (p = 0), but 0 * garbage must not be NaN
-#pragma unroll
-            for (int c = 0; c < HD; c += 8) {
-                *reinterpret_cast<uint4*>(dk + c) = make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4*>(dv + c) = make_uint4(0, 0, 0, 0);
-            }
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        // q of this block's heads, rows beyond them zero
-        for (int i = tid; i < DM_ROWS * (HD / 8); i += DM_THREADS) {
-            const int r = i / (HD / 8), c = (i % (HD / 8)) * 8;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (r < gt) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * nh + h0 + r) * HD + c);
-            *reinterpret_cast<uint4*>(sq + r * LD + c) = v;
-        }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
-    __syncthreads();
+    const int nh = a.nh, max_splits = a.max_splits;
+    const float scale = a.scale;
+    const int zi = it.zi, t = it.t, split = it.split, h0 = it.h0, gt = it.gt, pos = it.pos, lo = it.lo, k0 = it.k0;
+    const int first_split = it.first_split, last_split = it.last_split, n_active = it.n_active;
+    __nv_bfloat16* out = a.out;
+    float* part_o = a.part_o;
+    float* part_ml = a.part_ml;
 
     // ---- scores of keys 32*warp .. +31: four blocks of 8 keys ---------------------------------------------
     float s[4][4];
@@ -122,14 +152,12 @@ __global__ void __launch_bounds__(DM_THREADS, 2) attention_decode_mma_kernel(
     for (int nb = 0; nb < 4; nb++) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f; }
 #pragma unroll
     for (int ks = 0; ks < KSTEPS; ks++) {
-        uint32_t a[4];
-        dm_ldsm_x4(a[0], a[1], a[2], a[3], sq + (lane & 15) * LD + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
         for (int nb2 = 0; nb2 < 2; nb2++) {
             uint32_t b0, b1, b2, b3;
             dm_ldsm_x4(b0, b1, b2, b3, sk + (warp * 32 + nb2 * 16 + (lane & 7) + ((lane >> 4) << 3)) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
-            dm_mma(s[nb2 * 2], a, b0, b1);
-            dm_mma(s[nb2 * 2 + 1], a, b2, b3);
+            dm_mma(s[nb2 * 2], qf[ks], b0, b1);
+            dm_mma(s[nb2 * 2 + 1], qf[ks], b2, b3);
         }
     }
     // scale, mask; rows gq and gq+8 (heads), keys warp*32 + nb*8 + 2*qd + {0,1}
@@ -221,7 +249,7 @@ __global__ void __launch_bounds__(DM_THREADS, 2) attention_decode_mma_kernel(
             }
         }
     }
-    if (single) return;
+    if (!single) {
     if (tid < gt) {
         float* ml = part_ml + (((size_t)zi * nh + h0 + tid) * max_splits + split) * 2;
         ml[0] = row_m[tid];
@@ -231,16 +259,16 @@ __global__ void __launch_bounds__(DM_THREADS, 2) attention_decode_mma_kernel(
     // ---- the last block of this (token, kv-head tile) combines ----------------------------------------------
     __threadfence();
     __syncthreads();
-    int* counter = counters + (size_t)zi * counter_tiles + blockIdx.y;
+    int* counter = a.counters + (size_t)zi * a.counter_tiles + it.y;
     if (tid == 0) {
         const int old = atomicAdd(counter, 1);
-        is_last = old == n_active - 1;
-        if (is_last) *counter = 0;              // ready for the next launch
+        *is_last = old == n_active - 1;
+        if (*is_last) *counter = 0;             // ready for the next launch
     }
     __syncthreads();
-    if (!is_last) return;
+    if (*is_last) {
     __threadfence();
-    float* mxs = reinterpret_cast<float*>(sk);  // [16][n_active] maxima of the splits (the keys are no longer needed)
+    float* mxs = wts + DM_ROWS * 128;           // [16][n_active] maxima of the splits
     for (int i = tid; i < gt * n_active; i += DM_THREADS) {
         const int h = i / n_active, sp = first_split + i % n_active;
         const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (((size_t)zi * nh + h0 + h) * max_splits + sp) * 2));
@@ -276,6 +304,51 @@ __global__ void __launch_bounds__(DM_THREADS, 2) attention_decode_mma_kernel(
         for (; j < n_active; j++) o += __ldcg(po + (size_t)j * HD) * wts[h * 128 + j];
         out[((size_t)t * nh + h0 + h) * HD + d] = __float2bfloat16_rn(o * row_l[h]);
     }
+    }
+    }
+}
+
+// Shared memory of a block: keys [256][HD+8], values [256][HD+8], and 512 bytes of per-warp maxima and sums.  The
+// probabilities (high and low parts, [16][264] each) lie over the keys, which are dead once every warp has its scores
+// (when the keys' rows are too short for that, HD = 16, they get a place of their own); the combine's weights and maxima
+// (16 KB) lie over the values, dead once p * v is done.  74 KB at HD = 64: three blocks a multiprocessor.
+template <int HD> struct DmSmem {
+    static constexpr int LD = HD + 8, LP = DM_SPLIT + 8;
+    static constexpr bool P_OVER_K = 2 * DM_ROWS * LP <= DM_SPLIT * LD;
+    static constexpr size_t KV_BYTES = (size_t)2 * DM_SPLIT * LD * 2;
+    static constexpr size_t P_BYTES = P_OVER_K ? 0 : (size_t)2 * DM_ROWS * LP * 2;
+    static constexpr size_t W_NEED = (size_t)2 * DM_ROWS * 128 * 4;            // the combine's weights and maxima
+    static constexpr bool W_OVER_V = (size_t)DM_SPLIT * LD * 2 >= W_NEED;
+    static constexpr size_t W_BYTES = W_OVER_V ? 0 : W_NEED;
+    static constexpr size_t BYTES = KV_BYTES + P_BYTES + W_BYTES + 8 * DM_ROWS * 4;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(DM_THREADS, 3) attention_decode_mma_kernel(const DmArgs a) {
+    typedef __nv_bfloat16 T;
+    typedef DmSmem<HD> L;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T* sk = reinterpret_cast<T*>(smem_raw);                 // [256][LD]
+    T* sv = sk + DM_SPLIT * L::LD;                          // [256][LD]
+    T* sph = L::P_OVER_K ? sk : sv + DM_SPLIT * L::LD;      // [16][LP] high parts of p
+    T* spl = sph + DM_ROWS * L::LP;                         // [16][LP] low parts
+    float* wts = L::W_OVER_V ? reinterpret_cast<float*>(sv)   // [16][128] weights of the combine, then [16][128] maxima
+                             : reinterpret_cast<float*>(smem_raw + L::KV_BYTES + L::P_BYTES);
+    float* wstat = reinterpret_cast<float*>(smem_raw + L::KV_BYTES + L::P_BYTES + L::W_BYTES);   // [8 warps][16 rows]: maxima, then sums
+    __shared__ float row_m[DM_ROWS], row_l[DM_ROWS];
+    __shared__ int is_last;
+
+    const DmItem it = dm_item(a, blockIdx.z, blockIdx.y, blockIdx.x);      // from the step's metadata, which no kernel writes
+    if (!it.active) return;
+    dependency_wait();                          // q and the cache come from the kernels before this one
+    let_dependents_start();
+    dm_copy<HD>(a, it, sk, sv);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    uint32_t qf[HD / 16][4];
+    dm_load_q<HD>(a, it, qf);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    dm_compute<HD>(a, it, sk, sv, qf, sph, spl, wstat, wts, row_m, row_l, &is_last);
 }
 
 template <int HD>
@@ -283,17 +356,21 @@ static int launch_dm(const void* q, const void* cache, const int32_t* bt, const 
                      const int32_t* tok_list, void* out, float* part_o, float* part_ml, int* counters, int n_tokens, int nh, int nkv,
                      int page_size, int max_blocks, int splits, int grid_splits, int counter_tiles, float scale, int window,
                      cudaStream_t stream) {
-    constexpr int LD = HD + 8, LP = DM_SPLIT + 8;
-    const size_t smem = (size_t)(2 * DM_SPLIT * LD + DM_ROWS * LD + 2 * DM_ROWS * LP) * 2 + (size_t)(8 * DM_ROWS + DM_ROWS * 128) * 4;
+    const int g = nh / nkv, tiles = nkv * ((g + DM_ROWS - 1) / DM_ROWS);
+    DmArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bt, token_seg, positions, tok_list, (__nv_bfloat16*)out, part_o,
+             part_ml, counters, nh, nkv, page_size, max_blocks, splits, counter_tiles, scale, window};
+    // Three blocks a multiprocessor pay when there are several waves of blocks; with a single wave (a small batch)
+    // two blocks and a larger first-level cache were measured faster, so the small launch asks for more shared
+    // memory than it uses.
+    const long long blocks = (long long)n_tokens * tiles * grid_splits;
+    size_t smem = DmSmem<HD>::BYTES;
+    if (blocks < 3 * 148 * 2 && smem < 100 * 1024) smem = 100 * 1024;
     auto kern = attention_decode_mma_kernel<HD>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    const int g = nh / nkv, tiles = nkv * ((g + DM_ROWS - 1) / DM_ROWS);
-    return launch_dependent(kern, dim3(grid_splits, tiles, n_tokens), dim3(DM_THREADS), smem, stream, (const __nv_bfloat16*)q,
-                            (const __nv_bfloat16*)cache, bt, token_seg, positions, tok_list, (__nv_bfloat16*)out, part_o, part_ml,
-                            counters, nh, nkv, page_size, max_blocks, splits, counter_tiles, scale, window);
+    return launch_dependent(kern, dim3(grid_splits, tiles, n_tokens), dim3(DM_THREADS), smem, stream, a);
 }
 
 // Called by vk_attention_decode for bfloat16 and the head sizes built here.  Returns VK_BAD_SHAPE for other head sizes.
