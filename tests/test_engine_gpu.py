@@ -157,3 +157,35 @@ def test_command_line(sharp_dirs, tmp_path):
     assert r.returncode == 1 and "cuda" in r.stderr
     r = subprocess.run(exe + ["generate", "--model", model, "--ids", "1,2", "--speculate", "4"], capture_output=True, text=True)
     assert r.returncode == 1 and "Unknown or incomplete option: --speculate" in r.stderr
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 8e-2)])
+def test_steps_with_the_same_counts_replay_a_captured_graph(dtype, tol, sharp_dirs):
+    """Three requests run the same schedule of steps (a prompt portion of 70 beside... the same counts each time):
+    the first time eagerly, the second time while being captured, from then on as replays of that graph, with other
+    tokens, positions and pages each time.  Every logits row against the plain implementation."""
+    from vitna_anchor_b200.engine.loading import load_model
+    from vitna_anchor_b200.engine.runner import ModelRunner, StepEntry
+    cfg, W = P.read_model(sharp_dirs["tinyB"])
+    rng = np.random.default_rng(21)
+    runner = ModelRunner(load_model(sharp_dirs["tinyB"], dtype), page_size=8, num_pages=64, max_requests=4, max_batch_tokens=128)
+    worst, replays_before = 0.0, runner.graph_replays
+    for round_ in range(4):
+        a = [int(t) for t in rng.integers(0, cfg["V"], 90)]
+        b = [int(t) for t in rng.integers(0, cfg["V"], 40)]
+        pa, pb = P.forward(cfg, W, a), P.forward(cfg, W, b)
+        ra, rb = f"a{round_}", f"b{round_}"
+        runner.open(ra); runner.open(rb)
+        got = runner.step([StepEntry(ra, a[:70], [69])]).cpu().numpy()                                  # a prompt portion alone
+        worst = max(worst, np.abs(got[0] - pa[69]).max())
+        got = runner.step([StepEntry(ra, a[70:71], [0]), StepEntry(rb, b[:33], [0, 32])]).cpu().numpy()    # a decoded token beside a portion
+        worst = max(worst, np.abs(got[0] - pa[70]).max(), np.abs(got[1] - pb[0]).max(), np.abs(got[2] - pb[32]).max())
+        got = runner.step([StepEntry(rb, b[33:40], [6]), StepEntry(ra, a[71:90], [18])]).cpu().numpy()     # two portions
+        worst = max(worst, np.abs(got[0] - pb[39]).max(), np.abs(got[1] - pa[89]).max())
+        if round_ % 2:            # leave pages held in odd rounds so that later rounds land on other pages
+            runner.close(ra)
+        else:
+            runner.close(ra); runner.close(rb)
+    assert runner.graph_replays - replays_before >= 6, "the repeated steps were meant to be replayed"
+    assert worst <= tol * max(1.0, float(np.abs(pa).max()))
+    runner.cache.check()
