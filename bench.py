@@ -151,6 +151,7 @@ def decode_run(model_dir, batch, steps, warmup, clocks, with_e2e):
         clocks.active = False
         n_groups = len(eng.runner.cache.groups)
         meta_ints = 7 * batch + 1 + n_groups * (batch + batch * eng.runner.max_blocks)
+        eng.flush()                         # the last step's ids (the engine runs a step ahead of the host's copy of them)
         out["e2e"] = {"value": batch * steps / wall, "unit": "tokens/s", "h2d_bytes_per_step": meta_ints * 4,
                       "d2h_bytes_per_step": batch * 4, "ms_per_step": wall / steps * 1e3,
                       "device_ms_per_step": ev0.elapsed_time(ev1) / steps}

@@ -189,3 +189,29 @@ def test_steps_with_the_same_counts_replay_a_captured_graph(dtype, tol, sharp_di
     assert runner.graph_replays - replays_before >= 6, "the repeated steps were meant to be replayed"
     assert worst <= tol * max(1.0, float(np.abs(pa).max()))
     runner.cache.check()
+
+
+def test_decoding_a_step_ahead_of_the_host_gives_the_same_tokens(sharp_dirs):
+    """With the overlap (ids stay on the device and feed the next step; the host reads them a step later) and
+    without it: the same tokens, greedy and sampled, for requests that end at different steps, are admitted while
+    others decode, and are preempted for want of pages; no placeholder is left in any output."""
+    from vitna_anchor_b200.engine.engine import Engine
+    rng = np.random.default_rng(17)
+    V = TINIES["tinyA"]["config"]["vocab_size"]
+    prompts = [[int(t) for t in rng.integers(0, V, n)] for n in (3, 11, 20, 6, 9)]
+    new = [5, 23, 9, 31, 2]
+    outs = {}
+    for pipeline in (False, True):
+        eng = Engine(sharp_dirs["tinyA"], dtype="float32", kv_block=4, parallel=3, num_pages=26, max_batch_tokens=16, pipeline=pipeline)
+        for kw in (dict(), dict(temperature=0.9, top_p=0.9)):
+            reqs = [eng.add_request(p, max_new=n, seed=40 + i, **kw) for i, (p, n) in enumerate(zip(prompts, new))]
+            finished = eng.run()
+            assert sorted(id(r) for r in finished) == sorted(id(r) for r in reqs)
+            for r, n in zip(reqs, new):
+                assert len(r.output) == n and all(0 <= t < V for t in r.output)
+            outs[(pipeline, bool(kw))] = [list(r.output) for r in reqs]
+        assert eng.runner.cache.free_pages() == [26]
+        if pipeline:
+            assert eng.runner.graph_replays > 10
+    assert outs[(True, False)] == outs[(False, False)]
+    assert outs[(True, True)] == outs[(False, True)]

@@ -145,9 +145,22 @@ __global__ void add_cast_inplace_kernel(float* __restrict__ y, const T* __restri
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) y[i] += to_f32<T>(x[i]);
 }
 
+// tokens[i] = ids[src[i]] where src[i] >= 0: the ids a step's sampling left on the device become the next step's
+// input tokens without a trip through the host.
+__global__ void take_tokens_kernel(int32_t* __restrict__ tokens, const int32_t* __restrict__ ids, const int32_t* __restrict__ src, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n && src[i] >= 0) tokens[i] = ids[src[i]];
+}
+
 }  // namespace vk
 
 using namespace vk;
+
+VK_API int vk_take_tokens(int32_t* tokens, const int32_t* ids, const int32_t* src, int n, cudaStream_t stream) {
+    if (n <= 0) return VK_OK;
+    take_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, ids, src, n);
+    return launch_status();
+}
 
 static inline int grid_for(size_t n, int threads) {
     size_t g = (n + threads - 1) / threads;

@@ -19,13 +19,13 @@ from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .loading import load_model
 from .runner import ModelRunner, StepEntry, StepFailed
-from .scheduler import Planned, Request, RequestRefused, Scheduler  # noqa: F401
+from .scheduler import PENDING, Planned, Request, RequestRefused, Scheduler  # noqa: F401
 
 
 class Engine:
     def __init__(self, model: str, *, dtype: str = "bfloat16", ctx: Optional[int] = None, parallel: int = 8,
                  kv_block: int = 16, num_pages: Optional[int] = None, max_batch_tokens: int = 2048,
-                 device: str = "cuda", cuda_graphs: bool = True):
+                 device: str = "cuda", cuda_graphs: bool = True, pipeline: bool = True):
         if str(device) not in ("cuda", "cuda:0"):
             raise ValueError(f"--device is cuda; this engine has no path for {device}")
         if not torch.cuda.is_available():
@@ -42,6 +42,13 @@ class Engine:
         self.sampler = Sampler(self.model.vocab_size, parallel, "cuda")
         self._next_id = 0
         self.last_timing: Dict[str, float] = {}
+        # Decoding one step ahead of the host: the ids a step samples stay on the device and become the next step's
+        # tokens there, while the host reads them a step later (see step()).
+        self.pipeline = pipeline and cuda_graphs
+        self._inflight = None            # (requests, index of the pending token in each request's output, host ids, event)
+        self._ids_host = [torch.empty(parallel, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._ids_turn = 0
+        self._held: List[Request] = []   # finished, but their last token has not arrived yet
 
     # -- requests -----------------------------------------------------------------------------
     def add_request(self, ids: Sequence[int], *, max_new: int = 64, temperature: float = 0.0, top_k: int = 0,
@@ -59,30 +66,90 @@ class Engine:
         return req
 
     def step(self, logits_sink=None) -> List[Request]:
-        """Plan one batch, run it, sample, and hand the tokens back to the scheduler.  Returns finished requests."""
+        """Plan one batch, run it, sample, and hand the tokens back to the scheduler.  Returns finished requests.
+
+        While the batches are single decoded tokens of requests without stop ids, the host does not wait for a step's
+        ids before it issues the next step: the next step takes its tokens from the sampler's device buffer
+        (ModelRunner.step's token_source), the host's copy of the ids arrives a step later, and until then the
+        request's output holds PENDING in that place.  A request is returned as finished only when its tokens are
+        all there.  Anything else (a prompt portion in the batch, stop ids, a logits sink) first waits for what is
+        pending, so the results are the same as without the overlap."""
         plan = self.scheduler.schedule()
+        sampling = [p.request for p in plan if p.samples]
+        pending_now = self._inflight is not None
         entries = [StepEntry(p.request.request_id, p.tokens, [len(p.tokens) - 1] if p.samples else []) for p in plan]
+        can_feed = (self.pipeline and logits_sink is None and self.runner.decode_graph_takes(entries)
+                    and all(not r.stop_ids for r in sampling))
+        token_source = None
+        if pending_now:
+            if can_feed:
+                reqs, _, _, _ = self._inflight
+                where = {id(r): i for i, r in enumerate(reqs)}
+                src = [where.get(id(p.request), -1) if p.tokens[0] == PENDING else -1 for p in plan]
+                for e in entries:
+                    if e.tokens[0] == PENDING:
+                        e.tokens = [0]           # replaced on the device
+                token_source = (self.sampler.last_ids(), src)
+            else:
+                self._resolve()
+                for p, e in zip(plan, entries):
+                    p.refresh()
+                    e.tokens = p.tokens
         try:
-            logits = self.runner.step(entries)
+            logits = self.runner.step(entries, token_source)
         except StepFailed:
             # the step computed nothing: its requests end with an error and keep what they had
+            self._resolve()
             failed = [p.request for p in plan]
             for req in failed:
                 self.scheduler.fail(req)
-            return failed
-        sampling = [p.request for p in plan if p.samples]
+            return failed + self._release()
+        if token_source is not None:
+            self._resolve()                      # the step before: its ids have been on their way for a whole step
         tokens: List[int] = []
         if sampling:
             if logits_sink is not None:
                 logits_sink(sampling, logits)
+            if can_feed:
+                ids = self.sampler.sample_async(logits, [r.sampling for r in sampling], [r.rng for r in sampling])
+                host = self._ids_host[self._ids_turn]
+                self._ids_turn ^= 1
+                host[:len(sampling)].copy_(ids, non_blocking=True)
+                event = torch.cuda.Event()
+                event.record()
+                done = self.scheduler.update(plan, [PENDING] * len(sampling))
+                self._inflight = (sampling, [len(r.output) - 1 for r in sampling], host, event)
+                self._held += done
+                return self._release()
             tokens = self.sampler.sample(logits, [r.sampling for r in sampling], [r.rng for r in sampling])
-        return self.scheduler.update(plan, tokens)
+        return self.scheduler.update(plan, tokens) + self._release()
+
+    def _resolve(self) -> None:
+        """Wait for the ids of the step in flight and put them where PENDING stands."""
+        if self._inflight is None:
+            return
+        reqs, places, host, event = self._inflight
+        self._inflight = None
+        event.synchronize()
+        for r, place, tok in zip(reqs, places, host[:len(reqs)].tolist()):
+            r.output[place] = int(tok)
+
+    def _release(self) -> List[Request]:
+        """Finished requests whose tokens are all known."""
+        ready = [r for r in self._held if PENDING not in r.output[-1:]]
+        self._held = [r for r in self._held if PENDING in r.output[-1:]]
+        return ready
+
+    def flush(self) -> List[Request]:
+        """Wait for whatever is still on its way; returns the finished requests that were held back for it."""
+        self._resolve()
+        return self._release()
 
     def run(self, logits_sink=None) -> List[Request]:
         done: List[Request] = []
         while self.scheduler.has_work():
             done += self.step(logits_sink)
-        return done
+        return done + self.flush()
 
     # -- the one call most users make -------------------------------------------------------------
     def generate(self, ids: Union[Sequence[int], Sequence[Sequence[int]]], *, max_new: int = 64, temperature: float = 0.0,
@@ -110,11 +177,13 @@ class Engine:
             while self.scheduler.has_work():
                 self.step(sink)
                 if t_first is None and all(r.output for r in reqs):
+                    self.flush()
                     torch.cuda.synchronize()
                     t_first = time.perf_counter()
         finally:
             if out_file:
                 out_file.close()
+        self.flush()
         torch.cuda.synchronize()
         t1 = time.perf_counter()
         n_after = sum(max(0, len(r.output) - 1) for r in reqs)

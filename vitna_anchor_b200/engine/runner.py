@@ -88,6 +88,8 @@ class ModelRunner:
         self._seen_shapes: Dict[tuple, int] = {}
         self.graph_mixed_steps = True            # steps with prompt portions are captured too, once their counts repeat
         self.max_graphs = 48
+        self._src_dev = None
+        self._src_host = None
         self.graph_replays = 0
 
     # -- requests ---------------------------------------------------------------------------
@@ -103,6 +105,10 @@ class ModelRunner:
     def fail_step_once(self, position: int = 0) -> None:
         """The next step that would compute `position` of any request raises StepFailed instead."""
         self._fail_at = position
+
+    def decode_graph_takes(self, entries: Sequence[StepEntry]) -> bool:
+        """Whether the batch is single tokens, each wanted: the decode graph's case."""
+        return self.cuda_graphs and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries)
 
     # -- the step ---------------------------------------------------------------------------
     def _validate(self, entries: Sequence[StepEntry]) -> Tuple[int, int]:
@@ -212,9 +218,13 @@ class ModelRunner:
             pre_tiles=None if s_tiles is None else dev[s_tiles].view(-1, 4))
         return ctx, (dev[s_rows] if R else None)
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], token_source: Optional[Tuple[torch.Tensor, Sequence[int]]] = None) -> Optional[torch.Tensor]:
         """Run the batch.  Returns float32 logits [wanted places, vocab] on the device, in the order of the
-        entries and of each entry's `want`, or None when nothing is wanted."""
+        entries and of each entry's `want`, or None when nothing is wanted.
+
+        token_source = (ids, src): only for a batch of single tokens that goes through the decode graph; entry i
+        with src[i] >= 0 takes its token from the device tensor ids[src[i]] (what an earlier step's sampling left
+        there) instead of from entries[i].tokens, so the host need not wait for that step."""
         T, R = self._validate(entries)
         plan = [(e.request_id, len(e.tokens)) for e in entries]
         if self._fail_at is not None:
@@ -225,8 +235,10 @@ class ModelRunner:
                     raise StepFailed(f"the step that computes position {lo} failed as the test asked")
         self.cache.reserve_step(plan)         # OutOfPages leaves everything as it was
         try:
-            if self.cuda_graphs and T == len(entries) == R and all(len(e.want) == 1 for e in entries):
-                logits = self._decode_step(entries)
+            if self.decode_graph_takes(entries):
+                logits = self._decode_step(entries, token_source)
+            elif token_source is not None:
+                raise StepError("tokens can be taken from the device only by a batch of single tokens")
             elif self.cuda_graphs and self.graph_mixed_steps and 0 < R <= 64:
                 logits = self._graphed_step(entries, T, R)
             else:
@@ -298,7 +310,7 @@ class ModelRunner:
             max_seg_len=1, max_context=self.max_model_len, decode_only=True, num_dec=B)
         return ctx, dev[o_rows:o_rows + B]
 
-    def _decode_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def _decode_step(self, entries: Sequence[StepEntry], token_source=None) -> torch.Tensor:
         S = len(entries)
         B = 1
         while B < S:
@@ -306,6 +318,16 @@ class ModelRunner:
         B = min(B, self.max_segments) if S <= self.max_segments else S
         held = self._graphs.get(B)
         ctx, rows = self._decode_context(entries, B, views=held is None)
+        if token_source is not None:
+            ids, src = token_source
+            if self._src_dev is None:
+                self._src_dev = torch.empty(self.max_segments, dtype=torch.int32, device=self.device)
+                self._src_host = [torch.empty(self.max_segments, dtype=torch.int32).pin_memory() for _ in range(4)]
+            host = self._src_host[self._stage_i]
+            host[:B] = -1
+            host[:S] = torch.as_tensor(list(src), dtype=torch.int32)
+            self._src_dev[:B].copy_(host[:B], non_blocking=True)
+            ops.take_tokens(self._meta_dev[:B], ids, self._src_dev[:B])      # the tokens are the first B words of the metadata
         if held is None:
             # the first batch of this size runs eagerly (it also makes the workspace buffers), then the
             # same launches are captured; the captured graph is replayed from the next step on

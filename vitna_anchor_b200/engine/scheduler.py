@@ -78,11 +78,19 @@ class Request:
         return len(self.prompt) + len(self.output) - self.num_computed
 
 
+PENDING = -1     # a token that has been sampled on the device and not yet read by the host
+
+
 @dataclass
 class Planned:
     request: Request
     tokens: List[int]          # the tokens this step runs for the request
     samples: bool              # the step reaches the request's last token: its logits are wanted
+    start: int = 0             # index of tokens[0] among the request's tokens (prompt + output)
+
+    def refresh(self) -> None:
+        """Read the tokens again (a token that was pending when the plan was made has arrived)."""
+        self.tokens = self.request.tokens_between(self.start, self.start + len(self.tokens))
 
 
 class Scheduler:
@@ -157,7 +165,7 @@ class Scheduler:
                 break
             self._preempt(self.running[-1])    # most recently admitted; may be the one that lacked the page
         for req in decodes:
-            plan.append(Planned(req, [req.last_token], True))
+            plan.append(Planned(req, [req.last_token], True, len(req.prompt) + len(req.output) - 1))
         budget -= len(decodes)
         planned_ids = {p.request.request_id for p in plan}
 
@@ -173,7 +181,7 @@ class Scheduler:
             need = self._pages_for(req, n)
             free = [f - k for f, k in zip(free, need)]
             toks = req.tokens_between(req.num_computed, req.num_computed + n)
-            plan.append(Planned(req, toks, n == req.remaining))
+            plan.append(Planned(req, toks, n == req.remaining, req.num_computed))
             budget -= n
 
         # 3. admit waiting requests, oldest first, while a slot and pages for a first portion are free
@@ -192,7 +200,7 @@ class Scheduler:
             need = self._pages_for(req, n)
             free = [f - k for f, k in zip(free, need)]
             toks = req.tokens_between(req.num_computed, req.num_computed + n)
-            plan.append(Planned(req, toks, n == req.remaining))
+            plan.append(Planned(req, toks, n == req.remaining, req.num_computed))
             budget -= n
         if not plan and self.has_work():
             # nothing fits although requests exist: only possible when running requests hold every page

@@ -240,6 +240,14 @@ def add_inplace(y: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
     return y
 
 
+def take_tokens(tokens: torch.Tensor, ids: torch.Tensor, src: torch.Tensor) -> None:
+    """tokens[i] = ids[src[i]] where src[i] >= 0 (all int32, on the device)."""
+    _req(tokens, "tokens", torch.int32, 1); _req(ids, "ids", torch.int32, 1); _req(src, "src", torch.int32, 1)
+    if src.shape[0] != tokens.shape[0]:
+        raise KernelError("take_tokens: tokens and src differ in length")
+    _check(lib().vk_take_tokens(_p(tokens), _p(ids), _p(src), tokens.shape[0], _stream()), "take_tokens")
+
+
 _argmax_scratch = None
 
 

@@ -29,6 +29,10 @@ class Sampler:
         """One token id per row of logits [R, vocab]; draws one uniform from rngs[r] for each sampled row."""
         return self.sample_async(logits, params, rngs).tolist()
 
+    def last_ids(self) -> torch.Tensor:
+        """The device buffer sample_async writes: row r holds the id of row r of the latest call."""
+        return self._out
+
     def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams], rngs: Sequence[SplitMix64]) -> torch.Tensor:
         R = logits.shape[0]
         if R > self.max_rows or len(params) != R:
