@@ -25,7 +25,8 @@
 namespace vk {
 
 enum { ME_SAME = 0, ME_F32 = 1, ME_ACC = 2, ME_SWIGLU = 3, ME_ROPE = 4 };
-constexpr int MM_XPAD = 8;           // elements of padding per staged row (keeps 16-byte loads free of bank conflicts)
+// Staged rows are 64 bytes (mod 128) apart, so that the eight lanes of a quarter warp (two rows, four 16-byte
+// columns) read eight different 16-byte bank groups.
 
 struct MmaParams {
     const void* x;               // NORM: float32 [*, K] rows of stride ldx; else bfloat16 [M, K] rows of stride ldx
@@ -35,7 +36,8 @@ struct MmaParams {
     const __nv_bfloat16* w;      // [N, K]
     void* out;
     int M, N, K, ldx, kc, ks;    // kc: columns staged at a time (a multiple of 32 * ks); ks: warps = splits of K
-    int tpb;                     // tiles of eight units a block works through with one staging of x
+    int xstride;                 // elements of bfloat16 between two staged rows
+    int tpb;                     // most tiles of eight units a block works through (tile = blockIdx.x + i * gridDim.x)
     const int32_t* positions;
     const float* cos_t;
     const float* sin_t;
@@ -43,6 +45,10 @@ struct MmaParams {
     __nv_bfloat16* cache;
     int nh, nkv, hd, page_size;
 };
+
+__device__ __forceinline__ void mm_cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
 
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
@@ -117,22 +123,25 @@ __device__ __forceinline__ void mma_finish(const MmaParams& p, int u, int r0, in
     }
 }
 
-// MG: groups of eight batch rows (1, 2, 4 or 8).  blockDim.x = 32 * ks.  grid.x = ceil(units / 8).
-template <int EPI, bool NORM, int MG>
-__global__ void __launch_bounds__(256) skinny_mma_kernel(const MmaParams p) {
+// MG: groups of eight batch rows (1, 2, 4 or 8).  PIPE: the variant for long rows (two batches of loads a warp in flight).
+// blockDim.x = 32 * ks.  Block b works on tiles b, b + gridDim.x, ...
+template <int EPI, bool NORM, int MG, bool PIPE>
+__global__ void __launch_bounds__(256, MG <= 4 ? 2 : 1) skinny_mma_kernel(const MmaParams p) {
     typedef __nv_bfloat16 T;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int xstride = p.kc + MM_XPAD;
-    T* xs = reinterpret_cast<T*>(smem_raw);                                   // [MG*8][kc + pad]
-    float* red = reinterpret_cast<float*>(smem_raw + (size_t)MG * 8 * xstride * sizeof(T));   // [ks][MG][32][4]
-    __shared__ float inv_rms[MG * 8];
+    const int xstride = p.xstride;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, q = lane & 3;
     const int K = p.K, ks = p.ks;
+    // [MG*8][xstride] staged rows.  With the norm a row first holds the float32 input (4K bytes) and then, in its
+    // first half, the normalised bfloat16 values; the norm's weights follow the rows.
+    T* xs = reinterpret_cast<T*>(smem_raw);
+    float* nw_s = reinterpret_cast<float*>(smem_raw + (size_t)MG * 8 * xstride * sizeof(T));
+    float* red = nw_s + (NORM ? K : 0);                                        // [ks][MG][32][4]
     const int units = (EPI == ME_SWIGLU) ? p.N / 2 : (p.N + 1) / 2;
 
-    // this lane's two weight rows: the first and second row of unit (tile*8 + g); the block starts at tile blockIdx.x * tpb
-    int u = blockIdx.x * p.tpb * 8 + g;
+    // this lane's two weight rows: the first and second row of unit (tile*8 + g)
+    int u = blockIdx.x * 8 + g;
     bool on = u < units;
     int r0 = 0, r1 = 0;
     if (on) mma_unit_rows<EPI>(p, u, r0, r1);
@@ -142,8 +151,8 @@ __global__ void __launch_bounds__(256) skinny_mma_kernel(const MmaParams p) {
 
     // The first weights of this warp are asked for before anything that depends on the kernel before this one:
     // they are most of the wait of a decode layer, and they are nobody's output.
-    constexpr int UN = 4;                               // runs of 32 columns in flight: 8 loads of 16 bytes per lane
-    uint4 wr[UN], ws[UN];
+    constexpr int UN = 4;                               // runs of 32 columns in a batch: 8 loads of 16 bytes per lane
+    uint4 wr[UN], ws[UN], wr2[PIPE ? UN : 1], ws2[PIPE ? UN : 1];
     {
         const int nblk0 = min(p.kc, K) / 32;
 #pragma unroll
@@ -154,8 +163,21 @@ __global__ void __launch_bounds__(256) skinny_mma_kernel(const MmaParams p) {
                 ws[i] = __ldg(reinterpret_cast<const uint4*>(w1 + col));
             }
         }
+        if (PIPE) {
+#pragma unroll
+            for (int i = 0; i < UN; i++) {
+                if (warp + (UN + i) * ks < nblk0) {
+                    const int col = (warp + (UN + i) * ks) * 32 + q * 8;
+                    wr2[i] = __ldg(reinterpret_cast<const uint4*>(w0 + col));
+                    ws2[i] = __ldg(reinterpret_cast<const uint4*>(w1 + col));
+                }
+            }
+        }
     }
-    // what the first finishing pass of this lane needs besides the sums, also nobody's output
+    if (NORM) {                                         // the norm's weights, nobody's output either
+        for (int k = tid * 4; k < K; k += blockDim.x * 4) mm_cp_async16(nw_s + k, p.norm_w + k);
+    }
+    // what the first finishing pass of this lane needs besides the sums
     const int m_first = warp * 8 + 2 * q;               // rows m_first, m_first + 1 of row group `warp`
     int pre_slot[2] = {-1, -1}, pre_pos[2] = {0, 0};
     float pre_cos[2] = {1.0f, 1.0f}, pre_sin[2] = {0.0f, 0.0f};
@@ -181,6 +203,17 @@ __global__ void __launch_bounds__(256) skinny_mma_kernel(const MmaParams p) {
     dependency_wait();
     let_dependents_start();
 
+    if (NORM) {
+        // One trip to memory for all rows: every warp asks for its rows (float32) into their staging rows, then
+        // norms them where they lie.  A row's sum of squares is one warp's, in a fixed order.
+        for (int m = warp; m < p.M; m += ks) {
+            const int src = p.rows ? p.rows[m] : m;
+            const float* xr = reinterpret_cast<const float*>(p.x) + (size_t)src * p.ldx;
+            float* xf = reinterpret_cast<float*>(xs + (size_t)m * xstride);
+            for (int k = lane * 4; k < K; k += 128) mm_cp_async16(xf + k, xr + k);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     // the values the residual sum adds to (read now, used at the end)
     float old[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};
     if (EPI == ME_ACC && on && warp < MG) {
@@ -193,26 +226,50 @@ __global__ void __launch_bounds__(256) skinny_mma_kernel(const MmaParams p) {
             }
         }
     }
-
     if (NORM) {
-        for (int m = warp; m < p.M; m += ks) {          // a warp per row: the sum of squares over the whole row
-            const int src = p.rows ? p.rows[m] : m;
-            const float* xr = reinterpret_cast<const float*>(p.x) + (size_t)src * p.ldx;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                // the norm's weights came through all threads
+        for (int m = warp; m < MG * 8; m += ks) {
+            T* dst = xs + (size_t)m * xstride;
+            if (m >= p.M) {
+                for (int k = lane * 8; k < K; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
+                continue;
+            }
+            const float* xf = reinterpret_cast<const float*>(dst);
             float ss = 0.0f;
-#pragma unroll 4
             for (int k = lane * 4; k < K; k += 128) {
-                const float4 v = *reinterpret_cast<const float4*>(xr + k);
+                const float4 v = *reinterpret_cast<const float4*>(xf + k);
                 ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
             }
             ss = warp_sum(ss);
-            if (lane == 0) inv_rms[m] = 1.0f / sqrtf(ss / (float)K + p.eps);
+            const float inv = 1.0f / sqrtf(ss / (float)K + p.eps);
+            // 128 columns at a time, upwards: the bfloat16 values of a run never reach float32 values not yet read
+            for (int k0 = 0; k0 < K; k0 += 128) {
+                const int k = k0 + lane * 4;
+                float4 xv = make_float4(0.0f, 0.0f, 0.0f, 0.0f), wv = xv;
+                if (k < K) {
+                    xv = *reinterpret_cast<const float4*>(xf + k);
+                    wv = *reinterpret_cast<const float4*>(nw_s + k);
+                }
+                __syncwarp();
+                if (k < K) {
+                    __nv_bfloat162 lo = __floats2bfloat162_rn((xv.x * inv) * wv.x, (xv.y * inv) * wv.y);
+                    __nv_bfloat162 hi = __floats2bfloat162_rn((xv.z * inv) * wv.z, (xv.w * inv) * wv.w);
+                    uint2 v;
+                    v.x = *reinterpret_cast<uint32_t*>(&lo);
+                    v.y = *reinterpret_cast<uint32_t*>(&hi);
+                    *reinterpret_cast<uint2*>(dst + k) = v;
+                }
+                __syncwarp();
+            }
         }
+        __syncthreads();
     }
 
     const bool one_chunk = p.kc >= K;                   // then x is staged once for all of the block's tiles
   for (int it = 0; it < p.tpb; it++) {
     if (it > 0) {
-        u += 8;
+        u += gridDim.x * 8;
         if ((u - g) >= units) break;                    // the same for the whole block
         on = u < units;
         r0 = r1 = 0;
@@ -227,61 +284,69 @@ __global__ void __launch_bounds__(256) skinny_mma_kernel(const MmaParams p) {
 
     for (int kb = 0; kb < K; kb += p.kc) {
         const int kn = min(p.kc, K - kb);               // a multiple of 32
-        if (it == 0 || !one_chunk) {
-        __syncthreads();                                // inv_rms is written; the previous chunk has been read
-        // stage rows 0..M-1 (rows up to MG*8 are zero) of columns kb .. kb+kn
-        for (int m = warp; m < MG * 8; m += ks) {
-            T* dst = xs + m * xstride;
-            if (m >= p.M) {
-                for (int k = lane * 8; k < kn; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
-            } else if (NORM) {
-                const int src = p.rows ? p.rows[m] : m;
-                const float* xr = reinterpret_cast<const float*>(p.x) + (size_t)src * p.ldx + kb;
-                const float* nw = p.norm_w + kb;
-                const float inv = inv_rms[m];
+        if (!NORM && (it == 0 || !one_chunk)) {
+            __syncthreads();                            // the previous chunk has been read
+            // stage rows 0..M-1 (rows up to MG*8 are zero) of columns kb .. kb+kn
+            for (int m = warp; m < MG * 8; m += ks) {
+                T* dst = xs + (size_t)m * xstride;
+                if (m >= p.M) {
+                    for (int k = lane * 8; k < kn; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
+                } else {
+                    const T* xr = reinterpret_cast<const T*>(p.x) + (size_t)m * p.ldx + kb;
 #pragma unroll 4
-                for (int k = lane * 4; k < kn; k += 128) {
-                    const float4 xv = *reinterpret_cast<const float4*>(xr + k);
-                    const float4 wv = *reinterpret_cast<const float4*>(nw + k);
-                    __nv_bfloat162 lo = __floats2bfloat162_rn((xv.x * inv) * wv.x, (xv.y * inv) * wv.y);
-                    __nv_bfloat162 hi = __floats2bfloat162_rn((xv.z * inv) * wv.z, (xv.w * inv) * wv.w);
-                    uint2 v;
-                    v.x = *reinterpret_cast<uint32_t*>(&lo);
-                    v.y = *reinterpret_cast<uint32_t*>(&hi);
-                    *reinterpret_cast<uint2*>(dst + k) = v;
+                    for (int k = lane * 8; k < kn; k += 256) *reinterpret_cast<uint4*>(dst + k) = *reinterpret_cast<const uint4*>(xr + k);
                 }
-            } else {
-                const T* xr = reinterpret_cast<const T*>(p.x) + (size_t)m * p.ldx + kb;
-#pragma unroll 4
-                for (int k = lane * 8; k < kn; k += 256) *reinterpret_cast<uint4*>(dst + k) = *reinterpret_cast<const uint4*>(xr + k);
             }
-        }
-        __syncthreads();
+            __syncthreads();
         }
         // this warp's share of the chunk: the runs of 32 columns whose index is warp modulo ks.  A chunk starts
         // at a multiple of 32 * ks, so which warp adds a run, and in which order, depends on K alone.
         const int nblk = kn / 32;
-        for (int b = warp; b < nblk; b += UN * ks) {
-            if (it != 0 || kb != 0 || b != warp) {      // the first batch of the block's first tile is already on its way
+        const bool fresh = it == 0 && kb == 0;          // then the first loads are already on their way
+        auto load_batch = [&](uint4* r, uint4* t, int b) {
 #pragma unroll
-                for (int i = 0; i < UN; i++) {
-                    if (b + i * ks < nblk) {
-                        const int col = kb + (b + i * ks) * 32 + q * 8;
-                        wr[i] = __ldg(reinterpret_cast<const uint4*>(w0 + col));
-                        ws[i] = __ldg(reinterpret_cast<const uint4*>(w1 + col));
-                    }
+            for (int i = 0; i < UN; i++) {
+                if (b + i * ks < nblk) {
+                    const int col = kb + (b + i * ks) * 32 + q * 8;
+                    r[i] = __ldg(reinterpret_cast<const uint4*>(w0 + col));
+                    t[i] = __ldg(reinterpret_cast<const uint4*>(w1 + col));
                 }
             }
+        };
+        auto use_batch = [&](const uint4* r, const uint4* t, int b) {
 #pragma unroll
             for (int i = 0; i < UN; i++) {
                 if (b + i * ks < nblk) {
 #pragma unroll
                     for (int mg = 0; mg < MG; mg++) {
-                        const uint4 xv = *reinterpret_cast<const uint4*>(xs + (mg * 8 + g) * xstride + (b + i * ks) * 32 + q * 8);
-                        mma_bf16(d[mg], wr[i].x, ws[i].x, wr[i].y, ws[i].y, xv.x, xv.y);
-                        mma_bf16(d[mg], wr[i].z, ws[i].z, wr[i].w, ws[i].w, xv.z, xv.w);
+                        const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)(mg * 8 + g) * xstride + (b + i * ks) * 32 + q * 8);
+                        mma_bf16(d[mg], r[i].x, t[i].x, r[i].y, t[i].y, xv.x, xv.y);
+                        mma_bf16(d[mg], r[i].z, t[i].z, r[i].w, t[i].w, xv.z, xv.w);
                     }
                 }
+            }
+        };
+        if (PIPE) {
+            // long rows: two batches of loads are in flight, one being used while the next travels
+            int b = warp;
+            if (!fresh) load_batch(wr, ws, b);
+            bool have2 = fresh;
+            while (b < nblk) {
+                int b2 = b + UN * ks;
+                if (b2 < nblk && !have2) load_batch(wr2, ws2, b2);
+                have2 = false;
+                use_batch(wr, ws, b);
+                b = b2;
+                if (b >= nblk) break;
+                b2 = b + UN * ks;
+                if (b2 < nblk) load_batch(wr, ws, b2);
+                use_batch(wr2, ws2, b);
+                b = b2;
+            }
+        } else {
+            for (int b = warp; b < nblk; b += UN * ks) {
+                if (!fresh || b != warp) load_batch(wr, ws, b);
+                use_batch(wr, ws, b);
             }
         }
     }
@@ -318,25 +383,36 @@ static int launch_mma(MmaParams p, cudaStream_t stream) {
         if (nblk % cand == 0) ks = cand;
     if (!ks) { ks = 8; while (ks > 1 && nblk / ks < 2) ks--; }
     p.ks = ks;
-    // columns staged at a time: all of K if the rows fit in 160 KB, else the largest multiple of 32*ks that does
+    // columns staged at a time: all of K if the rows fit in 160 KB, else the largest multiple of 32*ks that does.
+    // With the norm a row is staged whole, in float32.
     const int rows = mg * 8;
     int kc = p.K;
-    const int fit = (163840 / (rows * 2) - MM_XPAD) / (32 * ks) * (32 * ks);
-    if (kc > fit) kc = fit;
-    if (kc <= 0) return VK_TOO_LARGE;
+    size_t stride_bytes;
+    if (NORM) {
+        stride_bytes = (size_t)4 * p.K + 64;            // K is a multiple of 32: 4K is a multiple of 128
+    } else {
+        const int fit = ((163840 / rows - 64) / 2) / (32 * ks) * (32 * ks);
+        if (kc > fit) kc = fit;
+        if (kc <= 0) return VK_TOO_LARGE;
+        stride_bytes = (size_t)2 * kc + ((2 * kc) % 128 == 64 ? 0 : 64);
+    }
     p.kc = kc;
+    p.xstride = (int)(stride_bytes / 2);
+    const size_t smem = (size_t)rows * stride_bytes + (NORM ? (size_t)4 * p.K : 0) + (size_t)ks * mg * 32 * 4 * sizeof(float);
+    if (smem > 220 * 1024) return VK_TOO_LARGE;
     const int units = (EPI == ME_SWIGLU) ? p.N / 2 : (p.N + 1) / 2;
     const int tiles = (units + 7) / 8;
-    // a block stages x (and computes the norm) for itself: with many tiles a block takes several, as long as
-    // about two blocks a multiprocessor remain
-    int tpb = tiles / (2 * 148);
-    tpb = tpb < 1 ? 1 : (tpb > 8 ? 8 : tpb);
-    p.tpb = tpb;
-    const int blocks = (tiles + tpb - 1) / tpb;
-    const size_t smem = (size_t)rows * (kc + MM_XPAD) * 2 + (size_t)ks * mg * 32 * 4 * sizeof(float);
+    // a block stages x (and computes the norm) for itself, so there are no more blocks than are resident at once
+    // (two a multiprocessor, one if the staged rows are large); each takes every gridDim.x-th tile
+    const int resident = 148 * (smem + 1024 <= 113 * 1024 ? 2 : 1);
+    const int blocks = tiles < resident ? tiles : resident;
+    p.tpb = (tiles + blocks - 1) / blocks;
+    const bool pipe = nblk / ks > 4;                    // more than one batch of four runs a warp
 #define LAUNCH(MGV)                                                                                                         \
+    if (pipe) LAUNCH2(MGV, true) else LAUNCH2(MGV, false)
+#define LAUNCH2(MGV, PV)                                                                                                    \
     {                                                                                                                       \
-        auto kern = skinny_mma_kernel<EPI, NORM, MGV>;                                                                      \
+        auto kern = skinny_mma_kernel<EPI, NORM, MGV, PV>;                                                                  \
         if (smem > 48 * 1024) {                                                                                             \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);             \
             if (e != cudaSuccess) return (int)e;                                                                            \
@@ -346,6 +422,7 @@ static int launch_mma(MmaParams p, cudaStream_t stream) {
     }
     if (mg == 1) LAUNCH(1) else if (mg == 2) LAUNCH(2) else if (mg == 4) LAUNCH(4) else LAUNCH(8)
 #undef LAUNCH
+#undef LAUNCH2
     return launch_status();
 }
 
@@ -382,7 +459,7 @@ VK_API int vk_linear_skinny_mma(const void* x, const int32_t* rows, const float*
             !slot || !cache)
             return VK_BAD_SHAPE;
     }
-    MmaParams p{x, rows, norm_w, eps, (const __nv_bfloat16*)w, out, M, N, K, ldx, 0, 0, 1, positions, cos_t, sin_t, slot,
+    MmaParams p{x, rows, norm_w, eps, (const __nv_bfloat16*)w, out, M, N, K, ldx, 0, 0, 0, 1, positions, cos_t, sin_t, slot,
                 (__nv_bfloat16*)cache, nh, nkv, hd, page_size};
     return norm_w ? mma_dispatch<true>(epi, p, stream) : mma_dispatch<false>(epi, p, stream);
 }

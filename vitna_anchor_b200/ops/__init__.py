@@ -360,6 +360,23 @@ SKINNY_MAX_ROWS = 64
 FUSED_NORM_MAX_ROWS = 16     # every block of the few-rows kernel recomputes the norm of all rows: beyond this a norm kernel runs once
 
 
+def _row_groups(M: int) -> int:
+    return 8 if M <= 8 else 16 if M <= 16 else 32 if M <= 32 else 64
+
+
+def _mma_norm_smem(M: int, K: int) -> int:
+    """Shared memory of the tensor-core few-rows kernel with the fused norm: the rows staged whole in float32."""
+    return _row_groups(M) * (4 * K + 64) + 4 * K + 8 * (_row_groups(M) // 8) * 512
+
+
+def fused_norm_takes(dtype: torch.dtype, M: int, K: int, N: int) -> bool:
+    """Whether norm and product should be one launch: few rows, and (bfloat16) rows small enough in float32 that
+    two blocks share a multiprocessor."""
+    if M > FUSED_NORM_MAX_ROWS or not skinny_takes(dtype, M, K, N):
+        return False
+    return dtype == torch.float32 or K % 32 != 0 or _mma_norm_smem(M, K) <= 112 * 1024
+
+
 def skinny_takes(dtype: torch.dtype, M: int, K: int, N: int = 0) -> bool:
     """Whether the few-rows kernel should take this product (else the tile kernels do the work).  Every block
     stages all M rows for itself, so many rows times many blocks (a large N) is left to the tile kernels."""
@@ -410,7 +427,8 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int,
     if tuple(out.shape) != want[epi][0]:
         raise KernelError(f"linear_skinny: out is {tuple(out.shape)}, expected {want[epi][0]}")
     if (w.dtype == torch.bfloat16 and K % 32 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and not force_simt
-            and (ldx % 4 == 0 and norm_weight.data_ptr() % 16 == 0 if norm_weight is not None else ldx % 8 == 0)):
+            and (ldx % 4 == 0 and norm_weight.data_ptr() % 16 == 0 and _mma_norm_smem(M, K) <= 220 * 1024
+                 if norm_weight is not None else ldx % 8 == 0)):
         # bfloat16: the tensor-core kernel
         _check(lib().vk_linear_skinny_mma(_p(x), _p(rows), _p(norm_weight), ctypes.c_float(eps), _p(w), _p(out), M, N, K, ldx,
                                           epi, _p(pos), _p(cos), _p(sin), _p(slot), _p(cache), nh, nkv, hd, ps, _stream()),

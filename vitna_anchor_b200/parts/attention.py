@@ -43,8 +43,7 @@ class PagedAttention(Mixer):
 
     def fuses_norm(self, norm, ctx: StepContext) -> bool:
         from .norms import RMSNorm
-        return (isinstance(norm, RMSNorm) and ctx.num_tokens <= ops.FUSED_NORM_MAX_ROWS
-                and ops.skinny_takes(ctx.dtype, ctx.num_tokens, self.hidden, self.qd + 2 * self.kvd))
+        return isinstance(norm, RMSNorm) and ops.fused_norm_takes(ctx.dtype, ctx.num_tokens, self.hidden, self.qd + 2 * self.kvd)
 
     def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCacheView, residual: torch.Tensor,
                 write_cache: bool = True, norm=None) -> None:

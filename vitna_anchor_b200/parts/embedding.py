@@ -42,7 +42,7 @@ class LMHead(Part):
 
     def fuses_norm(self, norm, ctx: StepContext, rows: int) -> bool:
         from .norms import RMSNorm
-        return isinstance(norm, RMSNorm) and rows <= ops.FUSED_NORM_MAX_ROWS and ops.skinny_takes(ctx.dtype, rows, self.hidden, self.vocab)
+        return isinstance(norm, RMSNorm) and ops.fused_norm_takes(ctx.dtype, rows, self.hidden, self.vocab)
 
     def forward_normed(self, x: torch.Tensor, rows: torch.Tensor, norm, ctx: StepContext) -> torch.Tensor:
         """logits of rmsnorm(x[rows]) in one launch (few rows); x is the float32 residual stream."""

@@ -21,8 +21,7 @@ class SwiGLU(FeedForward):
 
     def fuses_norm(self, norm, ctx: StepContext) -> bool:
         from .norms import RMSNorm
-        return (isinstance(norm, RMSNorm) and ctx.num_tokens <= ops.FUSED_NORM_MAX_ROWS
-                and ops.skinny_takes(ctx.dtype, ctx.num_tokens, self.hidden, 2 * self.intermediate))
+        return isinstance(norm, RMSNorm) and ops.fused_norm_takes(ctx.dtype, ctx.num_tokens, self.hidden, 2 * self.intermediate)
 
     def forward(self, xn: torch.Tensor, ctx: StepContext, residual: torch.Tensor, norm=None) -> None:
         T = ctx.num_tokens
