@@ -83,13 +83,17 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
     dependency_wait();                                 // q and the cache come from the kernels before this one
     let_dependents_start();
 
-    if (ASYNC && valid) {
-        const T* kr = cache + my_row;
-        T* dk = sk + tid * lds;
-        T* dv = sv + tid * lds;
-        for (int c = 0; c < hd; c += V) {
-            dec_cp_async16(dk + c, kr + c);
-            dec_cp_async16(dv + c, kr + v_off + c);
+    if (ASYNC) {
+        // consecutive threads take consecutive 16-byte pieces: a warp's request covers whole lines of a page
+        const int ch = hd / V;
+        for (int c = tid; c < DEC_SPLIT * ch; c += DEC_THREADS) {
+            const int kl = c / ch, part = c - kl * ch;
+            const int kk = k0 + kl;
+            if (kl < nkeys && kk >= lo) {
+                const T* kr = cache + (size_t)bt[kk / page_size] * page_stride + ((size_t)kvh * page_size + kk % page_size) * hd + part * V;
+                dec_cp_async16(sk + kl * lds + part * V, kr);
+                dec_cp_async16(sv + kl * lds + part * V, kr + v_off);
+            }
         }
     }
     if (ASYNC) asm volatile("cp.async.commit_group;" ::: "memory");

@@ -81,31 +81,31 @@ __device__ __forceinline__ DmItem dm_item(const DmArgs& a, int zi, int y, int sp
     return it;
 }
 
-// Ask for the item's keys and values (thread = key) with cp.async; rows that do not count are zeroed
-// (never counted, p = 0, but 0 * garbage must not be NaN).  No commit: the caller groups the copies.
+// Ask for the item's keys and values with cp.async: consecutive threads take consecutive 16-byte pieces, so a
+// warp's request covers whole 128-byte lines (the keys of a page lie one after the other).  Rows that do not
+// count are zeroed (never counted, p = 0, but 0 * garbage must not be NaN).  No commit: the caller groups the copies.
 template <int HD>
 __device__ __forceinline__ void dm_copy(const DmArgs& a, const DmItem& it, __nv_bfloat16* sk, __nv_bfloat16* sv) {
     typedef __nv_bfloat16 T;
-    constexpr int LD = HD + 8;
+    constexpr int LD = HD + 8, CH = HD / 8;             // CH pieces of 16 bytes a row
     const int tid = threadIdx.x;
-    const int key = it.k0 + tid;
-    const bool valid = tid < it.nkeys && key >= it.lo;
-    T* dk = sk + tid * LD;
-    T* dv = sv + tid * LD;
-    if (valid) {
-        const size_t page_stride = (size_t)2 * a.nkv * a.page_size * HD;
-        const T* kr = a.cache + (size_t)it.bt[key / a.page_size] * page_stride + ((size_t)it.kvh * a.page_size + key % a.page_size) * HD;
-        const size_t v_off = (size_t)a.nkv * a.page_size * HD;
+    const size_t page_stride = (size_t)2 * a.nkv * a.page_size * HD;
+    const size_t v_off = (size_t)a.nkv * a.page_size * HD;
 #pragma unroll
-        for (int c = 0; c < HD; c += 8) {
-            dm_cp_async16(dk + c, kr + c);
-            dm_cp_async16(dv + c, kr + v_off + c);
-        }
-    } else {
-#pragma unroll
-        for (int c = 0; c < HD; c += 8) {
-            *reinterpret_cast<uint4*>(dk + c) = make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(dv + c) = make_uint4(0, 0, 0, 0);
+    for (int i = 0; i < CH; i++) {
+        const int c = i * DM_THREADS + tid;
+        const int kl = c / CH, part = c % CH;
+        const int key = it.k0 + kl;
+        T* dk = sk + kl * LD + part * 8;
+        T* dv = sv + kl * LD + part * 8;
+        if (kl < it.nkeys && key >= it.lo) {
+            const T* kr = a.cache + (size_t)it.bt[key / a.page_size] * page_stride +
+                          ((size_t)it.kvh * a.page_size + key % a.page_size) * HD + part * 8;
+            dm_cp_async16(dk, kr);
+            dm_cp_async16(dv, kr + v_off);
+        } else {
+            *reinterpret_cast<uint4*>(dk) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(dv) = make_uint4(0, 0, 0, 0);
         }
     }
 }
