@@ -5,13 +5,16 @@
 // (token, kv-head tile) combines them in split order.  What differs is the arithmetic of a block: the
 // query heads that share a key-value head (up to 16 a block) are the 16 rows of an m16n8k16 product.
 //
-//   copy      keys and values of the split into shared memory with cp.async (one trip for both); the queries go
+// Within a block every warp works alone on 32 of the split's keys, with no barrier until the end:
+//
+//   copy      the warp's keys and values into shared memory with cp.async, whole lines at a time; the queries go
 //             straight from global memory into the registers of the 16-row operand
-//   scores    warp w: S[16 heads x 32 keys] = Q K^T for keys 32w .. 32w+31
-//   softmax   row maximum and row sum over the split's 256 keys (through shared memory), float32
-//   p * v     the probabilities go to shared memory as a high and a low bfloat16 part (p = hi + lo to
-//             about 2^-17, see attention_prefill.cu); warp w computes every head's output for its own
-//             slice of the head dimensions over ALL keys, so no sum across warps is needed
+//   scores    S[16 heads x 32 keys] = Q K^T
+//   softmax   against the warp's own row maxima, float32
+//   p * v     the probabilities go from the score registers straight into the 16-row operand, as a high and a
+//             low bfloat16 part (p = hi + lo to about 2^-17, see attention_prefill.cu)
+//   meet      the eight warps' unnormalised parts are weighted by exp(own maximum - row maximum) and added in
+//             warp order
 //
 // Instantiated for head sizes 16, 32, 64, 96 and 128; attention_decode.cu takes the others and float32.
 #include "common.cuh"
@@ -55,7 +58,7 @@ struct DmArgs {
     float* part_o;
     float* part_ml;
     int* counters;
-    int nh, nkv, page_size, max_blocks, max_splits, counter_tiles;
+    int nh, nkv, page_size, page_shift, max_blocks, max_splits, counter_tiles;   // page_shift: log2 of page_size, or -1
     float scale;
     int window;
 };
@@ -81,26 +84,36 @@ __device__ __forceinline__ DmItem dm_item(const DmArgs& a, int zi, int y, int sp
     return it;
 }
 
-// Ask for the item's keys and values with cp.async: consecutive threads take consecutive 16-byte pieces, so a
-// warp's request covers whole 128-byte lines (the keys of a page lie one after the other).  Rows that do not
-// count are zeroed (never counted, p = 0, but 0 * garbage must not be NaN).  No commit: the caller groups the copies.
+__device__ __forceinline__ void dm_ldsm_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ uint32_t dm_pack(float x, float y) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(x, y);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Warp w asks for keys and values 32w .. 32w+31 of the split with cp.async: consecutive lanes take consecutive
+// 16-byte pieces, so a request covers whole 128-byte lines (the keys of a page lie one after the other).  Rows
+// that do not count are zeroed (never counted, p = 0, but 0 * garbage must not be NaN).  No commit.
 template <int HD>
-__device__ __forceinline__ void dm_copy(const DmArgs& a, const DmItem& it, __nv_bfloat16* sk, __nv_bfloat16* sv) {
+__device__ __forceinline__ void dm_copy_warp(const DmArgs& a, const DmItem& it, __nv_bfloat16* sk, __nv_bfloat16* sv) {
     typedef __nv_bfloat16 T;
     constexpr int LD = HD + 8, CH = HD / 8;             // CH pieces of 16 bytes a row
-    const int tid = threadIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t page_stride = (size_t)2 * a.nkv * a.page_size * HD;
     const size_t v_off = (size_t)a.nkv * a.page_size * HD;
 #pragma unroll
     for (int i = 0; i < CH; i++) {
-        const int c = i * DM_THREADS + tid;
-        const int kl = c / CH, part = c % CH;
+        const int c = i * 32 + lane;
+        const int kl = warp * 32 + c / CH, part = c % CH;
         const int key = it.k0 + kl;
         T* dk = sk + kl * LD + part * 8;
         T* dv = sv + kl * LD + part * 8;
         if (kl < it.nkeys && key >= it.lo) {
-            const T* kr = a.cache + (size_t)it.bt[key / a.page_size] * page_stride +
-                          ((size_t)it.kvh * a.page_size + key % a.page_size) * HD + part * 8;
+            const int pg = a.page_shift >= 0 ? key >> a.page_shift : key / a.page_size;
+            const int off = key - pg * a.page_size;
+            const T* kr = a.cache + (size_t)it.bt[pg] * page_stride + ((size_t)it.kvh * a.page_size + off) * HD + part * 8;
             dm_cp_async16(dk, kr);
             dm_cp_async16(dv, kr + v_off);
         } else {
@@ -127,131 +140,176 @@ __device__ __forceinline__ void dm_load_q(const DmArgs& a, const DmItem& it, uin
     }
 }
 
-// Everything after the copy has landed (and a block-wide barrier): scores, softmax, p * v, the partial or final
-// result, and the combine by the block that arrives last.  Ends with every thread past its last use of the buffers
-// except for a final barrier, which the caller provides before reusing them.
+// Shared memory of a block: keys [256][HD+8], values [256][HD+8], the warps' maxima and sums [8][16][2] and the
+// weights of the warps' parts [8][16].  A warp's unnormalised output [16][HD] float32 lies over its own 32 keys,
+// dead once it has its scores; the combine's weights and maxima (16 KB) lie over the values, dead once every
+// warp has its p * v.  74 KB at HD = 64: three blocks a multiprocessor.
+template <int HD> struct DmSmem {
+    static constexpr int LD = HD + 8;
+    static constexpr size_t KV_BYTES = (size_t)2 * DM_SPLIT * LD * 2;
+    static constexpr size_t W_NEED = (size_t)2 * DM_ROWS * 128 * 4;            // the combine's weights and maxima
+    static constexpr bool W_OVER_V = (size_t)DM_SPLIT * LD * 2 >= W_NEED;
+    static constexpr size_t W_BYTES = W_OVER_V ? 0 : W_NEED;
+    static constexpr size_t BYTES = KV_BYTES + W_BYTES + (8 * DM_ROWS * 2 + 8 * DM_ROWS) * 4;
+};
+
+// Every warp works alone on its 32 keys: copy, scores, softmax against its own maximum, p * v with the
+// probabilities going from the score registers straight into the 16-row operand (as a high and a low bfloat16
+// part, p = hi + lo to about 2^-17).  Only then do the warps meet: their eight parts are weighted and added in
+// warp order, and the block leaves its partial (or, for a single split, the result).
 template <int HD>
-__device__ __forceinline__ void dm_compute(const DmArgs& a, const DmItem& it, __nv_bfloat16* sk, __nv_bfloat16* sv,
-                                           const uint32_t (*qf)[4], __nv_bfloat16* sph, __nv_bfloat16* spl, float* wstat, float* wts,
-                                           float* row_m, float* row_l, int* is_last) {
+__global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 3 : 1) attention_decode_mma_kernel(const DmArgs a) {
     typedef __nv_bfloat16 T;
-    constexpr int LD = HD + 8, LP = DM_SPLIT + 8, KSTEPS = HD / 16, DBLK = HD / 8;
+    typedef DmSmem<HD> L;
+    constexpr int LD = HD + 8, KSTEPS = HD / 16, DBLK = HD / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T* sk = reinterpret_cast<T*>(smem_raw);                 // [256][LD]
+    T* sv = sk + DM_SPLIT * LD;                             // [256][LD]
+    float* wts = L::W_OVER_V ? reinterpret_cast<float*>(sv)   // [16][128] weights of the combine, then [16][128] maxima
+                             : reinterpret_cast<float*>(smem_raw + L::KV_BYTES);
+    float* wml = reinterpret_cast<float*>(smem_raw + L::KV_BYTES + L::W_BYTES);   // [8 warps][16 rows][2]: maximum, sum
+    float* wes = wml + 8 * DM_ROWS * 2;                     // [8 warps][16 rows]: weight of the warp's part
+    __shared__ float row_m[DM_ROWS], row_l[DM_ROWS];
+    __shared__ int is_last;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gq = lane >> 2, qd = lane & 3;
+
+    const DmItem it = dm_item(a, blockIdx.z, blockIdx.y, blockIdx.x);      // from the step's metadata, which no kernel writes
+    if (!it.active) return;
     const int nh = a.nh, max_splits = a.max_splits;
-    const float scale = a.scale;
     const int zi = it.zi, t = it.t, split = it.split, h0 = it.h0, gt = it.gt, pos = it.pos, lo = it.lo, k0 = it.k0;
-    const int first_split = it.first_split, last_split = it.last_split, n_active = it.n_active;
-    __nv_bfloat16* out = a.out;
-    float* part_o = a.part_o;
-    float* part_ml = a.part_ml;
+    const int first_split = it.first_split, n_active = it.n_active;
+    // keys of this warp: wk0 .. wk0+31; the warp has work if one of them counts
+    const int wk0 = k0 + warp * 32;
+    const bool warp_on = wk0 <= pos && wk0 + 31 >= lo;
+    dependency_wait();                          // q and the cache come from the kernels before this one
+    let_dependents_start();
 
-    // ---- scores of keys 32*warp .. +31: four blocks of 8 keys ---------------------------------------------
-    float s[4][4];
-#pragma unroll
-    for (int nb = 0; nb < 4; nb++) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f; }
-#pragma unroll
-    for (int ks = 0; ks < KSTEPS; ks++) {
-#pragma unroll
-        for (int nb2 = 0; nb2 < 2; nb2++) {
-            uint32_t b0, b1, b2, b3;
-            dm_ldsm_x4(b0, b1, b2, b3, sk + (warp * 32 + nb2 * 16 + (lane & 7) + ((lane >> 4) << 3)) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
-            dm_mma(s[nb2 * 2], qf[ks], b0, b1);
-            dm_mma(s[nb2 * 2 + 1], qf[ks], b2, b3);
-        }
-    }
-    // scale, mask; rows gq and gq+8 (heads), keys warp*32 + nb*8 + 2*qd + {0,1}
-    float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int nb = 0; nb < 4; nb++) {
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-            const int kk = k0 + warp * 32 + nb * 8 + qd * 2 + (e & 1);
-            const float v = (kk <= pos && kk >= lo) ? s[nb][e] * scale : -INFINITY;
-            s[nb][e] = v;
-            mx[e >> 1] = fmaxf(mx[e >> 1], v);
-        }
-    }
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-    }
-    if (qd == 0) { wstat[warp * DM_ROWS + gq] = mx[0]; wstat[warp * DM_ROWS + gq + 8] = mx[1]; }
-    __syncthreads();
-    float m[2];
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-        float v = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < 8; w++) v = fmaxf(v, wstat[w * DM_ROWS + gq + 8 * r]);
-        m[r] = v;                               // finite: the split has at least one key that every row sees
-    }
-    __syncthreads();                            // wstat is reused for the sums
-    float rs[2] = {0.0f, 0.0f};
-#pragma unroll
-    for (int nb = 0; nb < 4; nb++) {
-        const float p0 = expf(s[nb][0] - m[0]), p1 = expf(s[nb][1] - m[0]);
-        const float p2 = expf(s[nb][2] - m[1]), p3 = expf(s[nb][3] - m[1]);
-        rs[0] += p0 + p1;
-        rs[1] += p2 + p3;
-        const int col = warp * 32 + nb * 8 + qd * 2;
-        __nv_bfloat162 h01 = __floats2bfloat162_rn(p0, p1), h23 = __floats2bfloat162_rn(p2, p3);
-        *reinterpret_cast<__nv_bfloat162*>(sph + gq * LP + col) = h01;
-        *reinterpret_cast<__nv_bfloat162*>(sph + (gq + 8) * LP + col) = h23;
-        *reinterpret_cast<__nv_bfloat162*>(spl + gq * LP + col) =
-            __floats2bfloat162_rn(p0 - __bfloat162float(h01.x), p1 - __bfloat162float(h01.y));
-        *reinterpret_cast<__nv_bfloat162*>(spl + (gq + 8) * LP + col) =
-            __floats2bfloat162_rn(p2 - __bfloat162float(h23.x), p3 - __bfloat162float(h23.y));
-    }
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-        rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
-        rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
-    }
-    if (qd == 0) { wstat[warp * DM_ROWS + gq] = rs[0]; wstat[warp * DM_ROWS + gq + 8] = rs[1]; }
-    __syncthreads();
-    if (tid < DM_ROWS) {
-        float l = 0.0f;
-#pragma unroll
-        for (int w = 0; w < 8; w++) l += wstat[w * DM_ROWS + tid];
-        row_l[tid] = l;
-    }
-    if (warp == 0 && qd == 0) { row_m[gq] = m[0]; row_m[gq + 8] = m[1]; }
+    float* wo = reinterpret_cast<float*>(sk + warp * 32 * LD);       // [16][HD], over the warp's own keys
+    if (warp_on) {
+        dm_copy_warp<HD>(a, it, sk, sv);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        uint32_t qf[KSTEPS][4];
+        dm_load_q<HD>(a, it, qf);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
 
-    // ---- p * v: warp w computes the 8-wide blocks of head dimensions w, w+8, ... over all 256 keys ------------------
-    const bool single = n_active == 1;
-    __syncthreads();                            // row_l, row_m and P are written
-    for (int db = warp; db < DBLK; db += 8) {
-        float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 4
-        for (int kk = 0; kk < DM_SPLIT / 16; kk++) {
-            uint32_t ah[4], al[4], b0, b1;
-            dm_ldsm_x4(ah[0], ah[1], ah[2], ah[3], sph + (lane & 15) * LP + kk * 16 + (lane >> 4) * 8);
-            dm_ldsm_x4(al[0], al[1], al[2], al[3], spl + (lane & 15) * LP + kk * 16 + (lane >> 4) * 8);
-            dm_ldsm_x2_trans(b0, b1, sv + (kk * 16 + (lane & 15)) * LD + db * 8);
-            dm_mma(o, ah, b0, b1);
-            dm_mma(o, al, b0, b1);
-        }
-        // rows gq, gq+8 (heads), dimensions db*8 + 2*qd + {0,1}
+        // ---- scores of the warp's 32 keys: four blocks of 8 keys --------------------------------------------
+        float s[4][4];
 #pragma unroll
-        for (int r = 0; r < 2; r++) {
-            const int row = gq + 8 * r;
-            if (row >= gt) continue;
-            const int d = db * 8 + qd * 2;
-            if (single) {
-                const float inv = 1.0f / row_l[row];
-                *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)t * nh + h0 + row) * HD + d) =
-                    __floats2bfloat162_rn(o[2 * r] * inv, o[2 * r + 1] * inv);
-            } else {
-                *reinterpret_cast<float2*>(part_o + (((size_t)zi * nh + h0 + row) * max_splits + split) * HD + d) =
-                    make_float2(o[2 * r], o[2 * r + 1]);
+        for (int nb = 0; nb < 4; nb++) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f; }
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ks++) {
+#pragma unroll
+            for (int nb2 = 0; nb2 < 2; nb2++) {
+                uint32_t b0, b1, b2, b3;
+                dm_ldsm_x4(b0, b1, b2, b3, sk + (warp * 32 + nb2 * 16 + (lane & 7) + ((lane >> 4) << 3)) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
+                dm_mma(s[nb2 * 2], qf[ks], b0, b1);
+                dm_mma(s[nb2 * 2 + 1], qf[ks], b2, b3);
             }
         }
+        // scale, mask; rows gq and gq+8 (heads), keys wk0 + nb*8 + 2*qd + {0,1}
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nb = 0; nb < 4; nb++) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int kk = wk0 + nb * 8 + qd * 2 + (e & 1);
+                const float v = (kk <= pos && kk >= lo) ? s[nb][e] * a.scale : -INFINITY;
+                s[nb][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        }
+        float rs[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int r = 0; r < 2; r++) {           // finite: the warp has at least one key that every row sees
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        }
+        uint32_t ph[2][4], pl[2][4];            // the 16-row operand of the two k-steps of 16 keys, high and low parts
+#pragma unroll
+        for (int nb = 0; nb < 4; nb++) {
+            const float p0 = expf(s[nb][0] - mx[0]), p1 = expf(s[nb][1] - mx[0]);
+            const float p2 = expf(s[nb][2] - mx[1]), p3 = expf(s[nb][3] - mx[1]);
+            rs[0] += p0 + p1;
+            rs[1] += p2 + p3;
+            const __nv_bfloat162 h01 = __floats2bfloat162_rn(p0, p1), h23 = __floats2bfloat162_rn(p2, p3);
+            const int kk = nb >> 1, hi = (nb & 1) * 2;
+            ph[kk][hi] = *reinterpret_cast<const uint32_t*>(&h01);
+            ph[kk][hi + 1] = *reinterpret_cast<const uint32_t*>(&h23);
+            pl[kk][hi] = dm_pack(p0 - __bfloat162float(h01.x), p1 - __bfloat162float(h01.y));
+            pl[kk][hi + 1] = dm_pack(p2 - __bfloat162float(h23.x), p3 - __bfloat162float(h23.y));
+        }
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
+            rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
+        }
+        if (qd == 0) {
+            *reinterpret_cast<float2*>(wml + (warp * DM_ROWS + gq) * 2) = make_float2(mx[0], rs[0]);
+            *reinterpret_cast<float2*>(wml + (warp * DM_ROWS + gq + 8) * 2) = make_float2(mx[1], rs[1]);
+        }
+
+        // ---- p * v over the warp's keys, all head dimensions ------------------------------------------------
+        float o[DBLK][4];
+#pragma unroll
+        for (int db = 0; db < DBLK; db++) { o[db][0] = o[db][1] = o[db][2] = o[db][3] = 0.0f; }
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++) {
+#pragma unroll
+            for (int db = 0; db < DBLK; db += 2) {
+                uint32_t b0, b1, b2, b3;
+                dm_ldsm_x4_trans(b0, b1, b2, b3, sv + (warp * 32 + kk * 16 + (lane & 15)) * LD + (db + (lane >> 4)) * 8);
+                dm_mma(o[db], ph[kk], b0, b1);
+                dm_mma(o[db], pl[kk], b0, b1);
+                dm_mma(o[db + 1], ph[kk], b2, b3);
+                dm_mma(o[db + 1], pl[kk], b2, b3);
+            }
+        }
+        __syncwarp();                           // every lane is past its reads of the warp's keys
+#pragma unroll
+        for (int db = 0; db < DBLK; db++) {
+            const int d = db * 8 + qd * 2;
+            if (gq < gt) *reinterpret_cast<float2*>(wo + gq * HD + d) = make_float2(o[db][0], o[db][1]);
+            if (gq + 8 < gt) *reinterpret_cast<float2*>(wo + (gq + 8) * HD + d) = make_float2(o[db][2], o[db][3]);
+        }
+    } else if (lane < DM_ROWS) {
+        *reinterpret_cast<float2*>(wml + (warp * DM_ROWS + lane) * 2) = make_float2(-INFINITY, 0.0f);
     }
-    if (!single) {
+    __syncthreads();
+
+    // ---- the warps' parts meet: row maximum, weights, sum; thread (row, warp) for the statistics -------------
+    if (tid < DM_ROWS * 8) {
+        const int row = tid >> 3, w = tid & 7;
+        const float2 ml = *reinterpret_cast<const float2*>(wml + (w * DM_ROWS + row) * 2);
+        float m = ml.x;
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+        const float e = ml.x == -INFINITY ? 0.0f : expf(ml.x - m);
+        float l = ml.y * e;
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        l += __shfl_xor_sync(0xffffffffu, l, 4);
+        wes[w * DM_ROWS + row] = e;
+        if (w == 0) { row_m[row] = m; row_l[row] = l; }
+    }
+    __syncthreads();
+    const bool single = n_active == 1;
+    for (int i = tid; i < gt * HD; i += DM_THREADS) {
+        const int row = i / HD, d = i % HD;
+        float acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) {
+            const float e = wes[w * DM_ROWS + row];
+            if (e != 0.0f) acc += reinterpret_cast<const float*>(sk + w * 32 * LD)[row * HD + d] * e;
+        }
+        if (single) a.out[((size_t)t * nh + h0 + row) * HD + d] = __float2bfloat16_rn(acc / row_l[row]);
+        else a.part_o[(((size_t)zi * nh + h0 + row) * max_splits + split) * HD + d] = acc;
+    }
+    if (single) return;
     if (tid < gt) {
-        float* ml = part_ml + (((size_t)zi * nh + h0 + tid) * max_splits + split) * 2;
+        float* ml = a.part_ml + (((size_t)zi * nh + h0 + tid) * max_splits + split) * 2;
         ml[0] = row_m[tid];
         ml[1] = row_l[tid];
     }
@@ -262,16 +320,16 @@ __device__ __forceinline__ void dm_compute(const DmArgs& a, const DmItem& it, __
     int* counter = a.counters + (size_t)zi * a.counter_tiles + it.y;
     if (tid == 0) {
         const int old = atomicAdd(counter, 1);
-        *is_last = old == n_active - 1;
-        if (*is_last) *counter = 0;             // ready for the next launch
+        is_last = old == n_active - 1;
+        if (is_last) *counter = 0;              // ready for the next launch
     }
     __syncthreads();
-    if (*is_last) {
+    if (!is_last) return;
     __threadfence();
     float* mxs = wts + DM_ROWS * 128;           // [16][n_active] maxima of the splits
     for (int i = tid; i < gt * n_active; i += DM_THREADS) {
         const int h = i / n_active, sp = first_split + i % n_active;
-        const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (((size_t)zi * nh + h0 + h) * max_splits + sp) * 2));
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml + (((size_t)zi * nh + h0 + h) * max_splits + sp) * 2));
         mxs[i] = ml.x;
         wts[h * 128 + (sp - first_split)] = ml.y;
     }
@@ -290,7 +348,7 @@ __device__ __forceinline__ void dm_compute(const DmArgs& a, const DmItem& it, __
     __syncthreads();
     for (int i = tid; i < gt * HD; i += DM_THREADS) {
         const int h = i / HD, d = i % HD;
-        const float* po = part_o + (((size_t)zi * nh + h0 + h) * max_splits + first_split) * HD + d;
+        const float* po = a.part_o + (((size_t)zi * nh + h0 + h) * max_splits + first_split) * HD + d;
         float o = 0.0f;
         int j = 0;
         for (; j + 4 <= n_active; j += 4) {
@@ -302,53 +360,8 @@ __device__ __forceinline__ void dm_compute(const DmArgs& a, const DmItem& it, __
             o += a3 * wts[h * 128 + j + 3];
         }
         for (; j < n_active; j++) o += __ldcg(po + (size_t)j * HD) * wts[h * 128 + j];
-        out[((size_t)t * nh + h0 + h) * HD + d] = __float2bfloat16_rn(o * row_l[h]);
+        a.out[((size_t)t * nh + h0 + h) * HD + d] = __float2bfloat16_rn(o * row_l[h]);
     }
-    }
-    }
-}
-
-// Shared memory of a block: keys [256][HD+8], values [256][HD+8], and 512 bytes of per-warp maxima and sums.  The
-// probabilities (high and low parts, [16][264] each) lie over the keys, which are dead once every warp has its scores
-// (when the keys' rows are too short for that, HD = 16, they get a place of their own); the combine's weights and maxima
-// (16 KB) lie over the values, dead once p * v is done.  74 KB at HD = 64: three blocks a multiprocessor.
-template <int HD> struct DmSmem {
-    static constexpr int LD = HD + 8, LP = DM_SPLIT + 8;
-    static constexpr bool P_OVER_K = 2 * DM_ROWS * LP <= DM_SPLIT * LD;
-    static constexpr size_t KV_BYTES = (size_t)2 * DM_SPLIT * LD * 2;
-    static constexpr size_t P_BYTES = P_OVER_K ? 0 : (size_t)2 * DM_ROWS * LP * 2;
-    static constexpr size_t W_NEED = (size_t)2 * DM_ROWS * 128 * 4;            // the combine's weights and maxima
-    static constexpr bool W_OVER_V = (size_t)DM_SPLIT * LD * 2 >= W_NEED;
-    static constexpr size_t W_BYTES = W_OVER_V ? 0 : W_NEED;
-    static constexpr size_t BYTES = KV_BYTES + P_BYTES + W_BYTES + 8 * DM_ROWS * 4;
-};
-
-template <int HD>
-__global__ void __launch_bounds__(DM_THREADS, 3) attention_decode_mma_kernel(const DmArgs a) {
-    typedef __nv_bfloat16 T;
-    typedef DmSmem<HD> L;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    T* sk = reinterpret_cast<T*>(smem_raw);                 // [256][LD]
-    T* sv = sk + DM_SPLIT * L::LD;                          // [256][LD]
-    T* sph = L::P_OVER_K ? sk : sv + DM_SPLIT * L::LD;      // [16][LP] high parts of p
-    T* spl = sph + DM_ROWS * L::LP;                         // [16][LP] low parts
-    float* wts = L::W_OVER_V ? reinterpret_cast<float*>(sv)   // [16][128] weights of the combine, then [16][128] maxima
-                             : reinterpret_cast<float*>(smem_raw + L::KV_BYTES + L::P_BYTES);
-    float* wstat = reinterpret_cast<float*>(smem_raw + L::KV_BYTES + L::P_BYTES + L::W_BYTES);   // [8 warps][16 rows]: maxima, then sums
-    __shared__ float row_m[DM_ROWS], row_l[DM_ROWS];
-    __shared__ int is_last;
-
-    const DmItem it = dm_item(a, blockIdx.z, blockIdx.y, blockIdx.x);      // from the step's metadata, which no kernel writes
-    if (!it.active) return;
-    dependency_wait();                          // q and the cache come from the kernels before this one
-    let_dependents_start();
-    dm_copy<HD>(a, it, sk, sv);
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    uint32_t qf[HD / 16][4];
-    dm_load_q<HD>(a, it, qf);
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();
-    dm_compute<HD>(a, it, sk, sv, qf, sph, spl, wstat, wts, row_m, row_l, &is_last);
 }
 
 template <int HD>
@@ -357,8 +370,10 @@ static int launch_dm(const void* q, const void* cache, const int32_t* bt, const 
                      int page_size, int max_blocks, int splits, int grid_splits, int counter_tiles, float scale, int window,
                      cudaStream_t stream) {
     const int g = nh / nkv, tiles = nkv * ((g + DM_ROWS - 1) / DM_ROWS);
+    int shift = -1;
+    for (int b = 0; b < 30; b++) if ((1 << b) == page_size) shift = b;
     DmArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bt, token_seg, positions, tok_list, (__nv_bfloat16*)out, part_o,
-             part_ml, counters, nh, nkv, page_size, max_blocks, splits, counter_tiles, scale, window};
+             part_ml, counters, nh, nkv, page_size, shift, max_blocks, splits, counter_tiles, scale, window};
     // Three blocks a multiprocessor pay when there are several waves of blocks; with a single wave (a small batch)
     // two blocks and a larger first-level cache were measured faster, so the small launch asks for more shared
     // memory than it uses.
