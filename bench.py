@@ -45,6 +45,7 @@ MODELS = {
 MODEL_NAME = "135M"
 SIZES = dict(MODELS[MODEL_NAME])
 PROMPT_LEN, CONTEXT, KV_BLOCK, PREFILL_TOKENS = 2048, 4096, 16, 2048
+PROFILE_REGION = ""     # "decode" or "prefill": that timed region is bracketed by cudaProfilerStart/Stop (ncu --profile-from-start off)
 
 
 def peaks():
@@ -165,11 +166,15 @@ def decode_run(model_dir, batch, steps, warmup, clocks, with_e2e):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = ops.launch_count()
     clocks.active = True
+    if PROFILE_REGION == "decode":
+        torch.cuda.profiler.start()
     ev0.record()
     for _ in range(steps):
         ops.argmax_rows(runner.step(entries), ids)
     ev1.record()
     torch.cuda.synchronize()
+    if PROFILE_REGION == "decode":
+        torch.cuda.profiler.stop()
     clocks.active = False
     ms = ev0.elapsed_time(ev1) / steps
     ctx_mean = sum(runner.length(r.request_id) for r in reqs) / batch - steps / 2.0
@@ -195,12 +200,16 @@ def prefill_run(model_dir, clocks, repeats=5):
         torch.cuda.synchronize()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         clocks.active = i >= 3
+        if PROFILE_REGION == "prefill" and i == repeats + 2:
+            torch.cuda.profiler.start()
         t0 = time.perf_counter()
         ev0.record()
         runner.step([StepEntry(i, prompt, [PREFILL_TOKENS - 1])])
         ev1.record()
         host_ms = (time.perf_counter() - t0) * 1e3          # time to issue the step's launches
         torch.cuda.synchronize()
+        if PROFILE_REGION == "prefill" and i == repeats + 2:
+            torch.cuda.profiler.stop()
         clocks.active = False
         if i >= 3:
             times.append(ev0.elapsed_time(ev1))
@@ -256,6 +265,8 @@ def main():
     ap.add_argument("--model", default="135M", choices=sorted(MODELS), help="layer sizes: SmolLM2-135M (the default), 360M or 1.7B")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the prefill")
     ap.add_argument("--only-prefill", action="store_true", help="run the prefill measurement alone (for profiling)")
+    ap.add_argument("--profile-region", default="", choices=["", "decode", "prefill"],
+                    help="bracket the timed decode steps (or the last prefill) with cudaProfilerStart/Stop, for ncu --profile-from-start off")
     ap.add_argument("--only-gemm", action="store_true", help="time the tcgen05 product alone at the models' shapes, M = 2,048")
     a = ap.parse_args()
     if a.impl == "reference":
@@ -266,8 +277,9 @@ def main():
         print(f"bench.py measures one GPU; --gpus {a.gpus} is not supported by this engine")
         return 2
     a.warmup = max(a.warmup, 3)
-    global MODEL_NAME
+    global MODEL_NAME, PROFILE_REGION
     MODEL_NAME = a.model
+    PROFILE_REGION = a.profile_region
     SIZES.clear()
     SIZES.update(MODELS[a.model])
     import torch

@@ -124,7 +124,7 @@ __device__ __forceinline__ void mma_finish(const MmaParams& p, int u, int r0, in
 }
 
 // MG: groups of eight batch rows (1, 2, 4 or 8).  PIPE: the variant for long rows (two batches of loads a warp in flight).
-// blockDim.x = 32 * ks.  Block b works on tiles b, b + gridDim.x, ...
+// blockDim.x = 32 * ks.  Block (b, y) works on tiles b, b + gridDim.x, ... for batch rows y * MG*8 ...
 template <int EPI, bool NORM, int MG, bool PIPE>
 __global__ void __launch_bounds__(256, MG <= 4 ? 2 : 1) skinny_mma_kernel(const MmaParams p) {
     typedef __nv_bfloat16 T;
@@ -133,6 +133,7 @@ __global__ void __launch_bounds__(256, MG <= 4 ? 2 : 1) skinny_mma_kernel(const 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, q = lane & 3;
     const int K = p.K, ks = p.ks;
+    const int m0 = blockIdx.y * (MG * 8);               // the block's batch rows: m0 .. m0 + MG*8 - 1
     // [MG*8][xstride] staged rows.  With the norm a row first holds the float32 input (4K bytes) and then, in its
     // first half, the normalised bfloat16 values; the norm's weights follow the rows.
     T* xs = reinterpret_cast<T*>(smem_raw);
@@ -178,7 +179,7 @@ __global__ void __launch_bounds__(256, MG <= 4 ? 2 : 1) skinny_mma_kernel(const 
         for (int k = tid * 4; k < K; k += blockDim.x * 4) mm_cp_async16(nw_s + k, p.norm_w + k);
     }
     // what the first finishing pass of this lane needs besides the sums
-    const int m_first = warp * 8 + 2 * q;               // rows m_first, m_first + 1 of row group `warp`
+    const int m_first = m0 + warp * 8 + 2 * q;          // rows m_first, m_first + 1 of row group `warp`
     int pre_slot[2] = {-1, -1}, pre_pos[2] = {0, 0};
     float pre_cos[2] = {1.0f, 1.0f}, pre_sin[2] = {0.0f, 0.0f};
     if (EPI == ME_ROPE && on && warp < MG) {
@@ -206,8 +207,8 @@ __global__ void __launch_bounds__(256, MG <= 4 ? 2 : 1) skinny_mma_kernel(const 
     if (NORM) {
         // One trip to memory for all rows: every warp asks for its rows (float32) into their staging rows, then
         // norms them where they lie.  A row's sum of squares is one warp's, in a fixed order.
-        for (int m = warp; m < p.M; m += ks) {
-            const int src = p.rows ? p.rows[m] : m;
+        for (int m = warp; m < MG * 8 && m0 + m < p.M; m += ks) {
+            const int src = p.rows ? p.rows[m0 + m] : m0 + m;
             const float* xr = reinterpret_cast<const float*>(p.x) + (size_t)src * p.ldx;
             float* xf = reinterpret_cast<float*>(xs + (size_t)m * xstride);
             for (int k = lane * 4; k < K; k += 128) mm_cp_async16(xf + k, xr + k);
@@ -231,7 +232,7 @@ __global__ void __launch_bounds__(256, MG <= 4 ? 2 : 1) skinny_mma_kernel(const 
         __syncthreads();                                // the norm's weights came through all threads
         for (int m = warp; m < MG * 8; m += ks) {
             T* dst = xs + (size_t)m * xstride;
-            if (m >= p.M) {
+            if (m0 + m >= p.M) {
                 for (int k = lane * 8; k < K; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
                 continue;
             }
@@ -289,10 +290,10 @@ __global__ void __launch_bounds__(256, MG <= 4 ? 2 : 1) skinny_mma_kernel(const 
             // stage rows 0..M-1 (rows up to MG*8 are zero) of columns kb .. kb+kn
             for (int m = warp; m < MG * 8; m += ks) {
                 T* dst = xs + (size_t)m * xstride;
-                if (m >= p.M) {
+                if (m0 + m >= p.M) {
                     for (int k = lane * 8; k < kn; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
                 } else {
-                    const T* xr = reinterpret_cast<const T*>(p.x) + (size_t)m * p.ldx + kb;
+                    const T* xr = reinterpret_cast<const T*>(p.x) + (size_t)(m0 + m) * p.ldx + kb;
 #pragma unroll 4
                     for (int k = lane * 8; k < kn; k += 256) *reinterpret_cast<uint4*>(dst + k) = *reinterpret_cast<const uint4*>(xr + k);
                 }
@@ -363,7 +364,7 @@ __global__ void __launch_bounds__(256, MG <= 4 ? 2 : 1) skinny_mma_kernel(const 
         }
         if (!on) continue;
         // lane (g, q): unit u; batch rows mg*8 + 2q and + 1; s.x, s.y are row r0's sums, s.z, s.w row r1's
-        const int m = mg * 8 + 2 * q;
+        const int m = m0 + mg * 8 + 2 * q;
         const bool first = it == 0 && mg == warp;       // this pass has its extras in registers already
         if (m < p.M) mma_finish<EPI>(p, u, r0, r1, has1, m, s.x, s.z, first, pre_slot[0], pre_cos[0], pre_sin[0], old[0]);
         if (m + 1 < p.M) mma_finish<EPI>(p, u, r0, r1, has1, m + 1, s.y, s.w, first, pre_slot[1], pre_cos[1], pre_sin[1], old[1]);
@@ -374,7 +375,13 @@ __global__ void __launch_bounds__(256, MG <= 4 ? 2 : 1) skinny_mma_kernel(const 
 
 template <int EPI, bool NORM>
 static int launch_mma(MmaParams p, cudaStream_t stream) {
-    const int mg = p.M <= 8 ? 1 : p.M <= 16 ? 2 : p.M <= 32 ? 4 : 8;
+    const int units = (EPI == ME_SWIGLU) ? p.N / 2 : (p.N + 1) / 2;
+    const int tiles = (units + 7) / 8;
+    // Batch rows a block: all of them (in groups of eight), unless the weights make too few tiles to fill the
+    // machine; then the rows are split over blocks too, and the weights come several times, from the second-level cache.
+    int mg = p.M <= 8 ? 1 : p.M <= 16 ? 2 : p.M <= 32 ? 4 : 8;
+    while (mg > 1 && tiles * ((p.M + 8 * mg - 1) / (8 * mg)) < 120) mg /= 2;
+    const int ychunks = (p.M + 8 * mg - 1) / (8 * mg);
     const int nblk = p.K / 32;
     // warps that split K (K alone decides): between 4 and 8 if that divides the runs of 32 columns evenly,
     // else as many as leave a warp at least two runs
@@ -400,8 +407,6 @@ static int launch_mma(MmaParams p, cudaStream_t stream) {
     p.xstride = (int)(stride_bytes / 2);
     const size_t smem = (size_t)rows * stride_bytes + (NORM ? (size_t)4 * p.K : 0) + (size_t)ks * mg * 32 * 4 * sizeof(float);
     if (smem > 220 * 1024) return VK_TOO_LARGE;
-    const int units = (EPI == ME_SWIGLU) ? p.N / 2 : (p.N + 1) / 2;
-    const int tiles = (units + 7) / 8;
     // a block stages x (and computes the norm) for itself, so there are no more blocks than are resident at once
     // (two a multiprocessor, one if the staged rows are large); each takes every gridDim.x-th tile
     const int resident = 148 * (smem + 1024 <= 113 * 1024 ? 2 : 1);
@@ -417,7 +422,7 @@ static int launch_mma(MmaParams p, cudaStream_t stream) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);             \
             if (e != cudaSuccess) return (int)e;                                                                            \
         }                                                                                                                   \
-        const int rc = launch_dependent(kern, dim3(blocks), dim3(32 * ks), smem, stream, p);                                \
+        const int rc = launch_dependent(kern, dim3(blocks, ychunks), dim3(32 * ks), smem, stream, p);                                \
         if (rc != 0) return rc;                                                                                             \
     }
     if (mg == 1) LAUNCH(1) else if (mg == 2) LAUNCH(2) else if (mg == 4) LAUNCH(4) else LAUNCH(8)

@@ -357,24 +357,33 @@ def linear_tcgen05_rope(x: torch.Tensor, wqkv: torch.Tensor, q_out: torch.Tensor
 
 EPI_SAME, EPI_F32, EPI_ACC, EPI_SWIGLU, EPI_ROPE = 0, 1, 2, 3, 4
 SKINNY_MAX_ROWS = 64
-FUSED_NORM_MAX_ROWS = 16     # every block of the few-rows kernel recomputes the norm of all rows: beyond this a norm kernel runs once
+FUSED_NORM_MAX_ROWS = 16     # a block of the few-rows kernel norms every row it stages: beyond this many a norm kernel runs once
 
 
-def _row_groups(M: int) -> int:
-    return 8 if M <= 8 else 16 if M <= 16 else 32 if M <= 32 else 64
+def _mma_rows_per_block(M: int, N: int) -> int:
+    """Batch rows a block of the tensor-core few-rows kernel stages (its launcher's rule): all of them in groups
+    of eight, fewer when the weights make too few tiles to fill the machine."""
+    tiles = ((N + 1) // 2 + 7) // 8
+    mg = 1 if M <= 8 else 2 if M <= 16 else 4 if M <= 32 else 8
+    while mg > 1 and tiles * -(-M // (8 * mg)) < 120:
+        mg //= 2
+    return 8 * mg
 
 
-def _mma_norm_smem(M: int, K: int) -> int:
-    """Shared memory of the tensor-core few-rows kernel with the fused norm: the rows staged whole in float32."""
-    return _row_groups(M) * (4 * K + 64) + 4 * K + 8 * (_row_groups(M) // 8) * 512
+def _mma_norm_smem(M: int, K: int, N: int) -> int:
+    """Shared memory of the tensor-core few-rows kernel with the fused norm: a block's rows staged whole in float32."""
+    rows = _mma_rows_per_block(M, N)
+    return rows * (4 * K + 64) + 4 * K + 8 * (rows // 8) * 512
 
 
 def fused_norm_takes(dtype: torch.dtype, M: int, K: int, N: int) -> bool:
-    """Whether norm and product should be one launch: few rows, and (bfloat16) rows small enough in float32 that
-    two blocks share a multiprocessor."""
-    if M > FUSED_NORM_MAX_ROWS or not skinny_takes(dtype, M, K, N):
+    """Whether norm and product should be one launch.  Every block norms the rows it stages, so the rows of a
+    block must be few (at most 16) and, in float32, small enough that two blocks share a multiprocessor."""
+    if not skinny_takes(dtype, M, K, N):
         return False
-    return dtype == torch.float32 or K % 32 != 0 or _mma_norm_smem(M, K) <= 112 * 1024
+    if dtype == torch.float32 or K % 32 != 0:
+        return M <= FUSED_NORM_MAX_ROWS
+    return _mma_rows_per_block(M, N) <= FUSED_NORM_MAX_ROWS and _mma_norm_smem(M, K, N) <= 112 * 1024
 
 
 def skinny_takes(dtype: torch.dtype, M: int, K: int, N: int = 0) -> bool:
@@ -427,7 +436,7 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int,
     if tuple(out.shape) != want[epi][0]:
         raise KernelError(f"linear_skinny: out is {tuple(out.shape)}, expected {want[epi][0]}")
     if (w.dtype == torch.bfloat16 and K % 32 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and not force_simt
-            and (ldx % 4 == 0 and norm_weight.data_ptr() % 16 == 0 and _mma_norm_smem(M, K) <= 220 * 1024
+            and (ldx % 4 == 0 and norm_weight.data_ptr() % 16 == 0 and _mma_norm_smem(M, K, N) <= 220 * 1024
                  if norm_weight is not None else ldx % 8 == 0)):
         # bfloat16: the tensor-core kernel
         _check(lib().vk_linear_skinny_mma(_p(x), _p(rows), _p(norm_weight), ctypes.c_float(eps), _p(w), _p(out), M, N, K, ldx,
