@@ -1,0 +1,333 @@
+// Causal attention of prompt portions over the paged cache on the fifth-generation tensor cores (bfloat16, head
+// size 64): softmax(q k^T * scale) v with float32 scores, running maxima and sums (the softmax of
+// engine/src/model.c:932-956, computed tile by tile).
+//
+// One block takes a tile of up to 128 consecutive tokens of one request and one query head, and walks over the
+// request's keys 64 at a time:
+//
+//   warp 4   TMA: the query tile once; per step the keys and values of the step's pages, straight from the cache
+//            (a box of one page's rows for one key-value head, 128-byte swizzle) into a three-stage ring
+//   warp 5   one lane issues tcgen05.mma: S[128 x 64] = Q K^T into one of two score buffers in tensor memory (the
+//            next step's scores are computed while the softmax warps work on this step's), and, once the
+//            probabilities lie in shared memory, O[128 x 64] += P V (V as it lies in the cache: the N-major operand)
+//   warps 0-3  one query row per thread: read the row of S from tensor memory, mask, maximum, 2^x, write the
+//            probabilities as a high and a low bfloat16 part (p = hi + lo to about 2^-17, so that P V matches
+//            float32 probabilities) in the swizzled K-major layout the tensor core reads
+//
+// O stays in tensor memory for the whole walk.  A row's reference maximum is only raised when the step's maximum
+// exceeds it by more than 2^8 (then the warp scales its rows of O and the row's sum); until then the
+// probabilities are taken against the older maximum and may reach 256, which float32 sums and the two bfloat16
+// parts hold as well as values up to 1.  The result is normalised by the row's sum at the end.
+//
+// A row's result does not depend on what else is in the batch: its keys are walked in 64s from absolute position
+// 0 (or the window's first tile), and every decision above is the row's own.
+//
+// Every wait on an mbarrier is bounded: after about a second the waiter sets *error (a word the host reads),
+// the block stops, and its tensor memory is freed.
+//
+// tiles [n_tiles][4] int32: first token (flat index), rows (1..128), position of the first token, segment.
+#include "tcgen05_common.cuh"
+
+namespace vk {
+
+constexpr int AT_BM = 128, AT_BN = 64, AT_THREADS = 192, AT_STAGES = 3;
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ float at_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const int32_t* __restrict__ block_tables,
+    const int32_t* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int max_blocks, float scale,
+    int window, int* error) {
+    static_assert(HD == 64, "one 128-byte row per key");
+    constexpr int STAGES = AT_STAGES;
+    constexpr uint32_t Q_BYTES = AT_BM * HD * 2, KV_BYTES = AT_BN * HD * 2, P_BYTES = AT_BM * AT_BN * 2;
+    constexpr uint32_t K_OFF = Q_BYTES, V_OFF = K_OFF + STAGES * KV_BYTES, PH_OFF = V_OFF + STAGES * KV_BYTES, PL_OFF = PH_OFF + P_BYTES,
+                       BAR_OFF = PL_OFF + P_BYTES;
+    constexpr uint32_t TMEM_COLS = 256;              // S in columns 0..63 and 64..127 (two buffers), O in 128..191
+    constexpr float RAISE = 8.0f;                    // the reference maximum follows when the step's exceeds it by 2^8
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + BAR_OFF);
+    uint64_t* kv_full = q_full + 1;                  // [STAGES]
+    uint64_t* kv_empty = kv_full + STAGES;           // [STAGES]
+    uint64_t* s_full = kv_empty + STAGES;            // [2]
+    uint64_t* p_full = s_full + 2;
+    uint64_t* pv_done = p_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+    __shared__ int failed;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = gridDim.x - 1 - blockIdx.x;     // later tiles of a prompt have more keys: start them first
+    const int h = blockIdx.y;
+    const int kvh = h / (nh / nkv);
+    const int tok0 = tiles[tile * 4 + 0], rows = tiles[tile * 4 + 1], pos0 = tiles[tile * 4 + 2], seg = tiles[tile * 4 + 3];
+    const int last_pos = pos0 + rows - 1;
+    const int lo_first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;     // lowest key any row needs
+    const int kt0 = lo_first / AT_BN, kt1 = last_pos / AT_BN, n_it = kt1 - kt0 + 1;
+
+    if (threadIdx.x == 0) {
+        failed = 0;
+        mbar_init(q_full, 1);
+        for (int s = 0; s < STAGES; s++) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+        mbar_init(&s_full[0], 1);
+        mbar_init(&s_full[1], 1);
+        mbar_init(p_full, AT_BM);
+        mbar_init(pv_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_s = *tmem_slot, tmem_o = tmem_s + 2 * AT_BN;
+
+    if (warp == 4) {
+        // ---- producer ------------------------------------------------------------------------------------
+        if (lane == 0) {
+            mbar_expect_tx(q_full, Q_BYTES);
+            tma_load_2d(smem, &map_q, h * HD, tok0, q_full);      // rows beyond the batch read as zero
+        }
+        const int32_t* bt = block_tables + (size_t)seg * max_blocks;
+        const int box_rows = page_size < AT_BN ? page_size : AT_BN, boxes = AT_BN / box_rows;
+        for (int i = 0; i < n_it; i++) {
+            const int s = i % STAGES, key0 = (kt0 + i) * AT_BN;
+            if (i >= STAGES) {
+                const bool ok = mbar_wait(&kv_empty[s], ((i / STAGES) - 1) & 1);
+                if (!__all_sync(0xffffffffu, ok)) { if (lane == 0) give_up(error, &failed, 11); break; }
+            }
+            // boxes that hold a key some row needs; the rows of the others are never counted (p = 0) and the
+            // values' rows beyond the last position are zeroed by the softmax warps
+            int nb = (last_pos - key0) / box_rows + 1;
+            nb = nb < boxes ? nb : boxes;
+            if (lane == 0) mbar_expect_tx(&kv_full[s], (uint32_t)nb * 2 * box_rows * HD * 2);
+            __syncwarp();
+            if (lane < nb) {
+                const int key = key0 + lane * box_rows;
+                const int page = bt[key / page_size], off = key % page_size;
+                const int yk = (page * 2 * nkv + kvh) * page_size + off;
+                const int yv = ((page * 2 + 1) * nkv + kvh) * page_size + off;
+                tma_load_2d(smem + K_OFF + s * KV_BYTES + lane * box_rows * (HD * 2), &map_kv, 0, yk, &kv_full[s]);
+                tma_load_2d(smem + V_OFF + s * KV_BYTES + lane * box_rows * (HD * 2), &map_kv, 0, yv, &kv_full[s]);
+            }
+        }
+    } else if (warp == 5) {
+        // ---- tensor core ---------------------------------------------------------------------------------
+        if (lane == 0) {
+            const uint32_t idesc_qk = umma_idesc_bf16(AT_BM, AT_BN);
+            const uint32_t idesc_pv = umma_idesc_bf16(AT_BM, HD) | (1u << 16);        // B (the values) is N-major
+            const uint32_t q_addr = smem_u32(smem), ph_addr = smem_u32(smem + PH_OFF), pl_addr = smem_u32(smem + PL_OFF);
+            auto scores = [&](int i) -> bool {        // S[i & 1] = Q K_i^T
+                const int s = i % STAGES;
+                if (!mbar_wait(&kv_full[s], (i / STAGES) & 1)) { give_up(error, &failed, 13); return false; }
+                tc_fence_after();
+                const uint32_t k_addr = smem_u32(smem + K_OFF + s * KV_BYTES);
+#pragma unroll
+                for (int k = 0; k < HD / 16; k++)
+                    umma_bf16(tmem_s + (i & 1) * AT_BN, umma_desc_sw128(q_addr + k * 32), umma_desc_sw128(k_addr + k * 32), idesc_qk, k != 0);
+                umma_commit(&s_full[i & 1]);
+                return true;
+            };
+            bool ok = mbar_wait(q_full, 0);
+            if (!ok) give_up(error, &failed, 12);
+            ok = ok && scores(0);
+            for (int i = 0; i < n_it && ok; i++) {
+                // the next step's scores go into the other buffer while the softmax warps work on this step's
+                if (i + 1 < n_it && !scores(i + 1)) break;
+                if (!mbar_wait(p_full, i & 1)) { give_up(error, &failed, 14); break; }
+                tc_fence_after();
+                const uint32_t v_addr = smem_u32(smem + V_OFF + (i % STAGES) * KV_BYTES);
+                // 16 keys an instruction: two groups of eight 128-byte rows of the values
+#pragma unroll
+                for (int k = 0; k < AT_BN / 16; k++)
+                    umma_bf16(tmem_o, umma_desc_sw128(ph_addr + k * 32), umma_desc_sw128(v_addr + k * 2048), idesc_pv, (i | k) != 0);
+#pragma unroll
+                for (int k = 0; k < AT_BN / 16; k++)
+                    umma_bf16(tmem_o, umma_desc_sw128(pl_addr + k * 32), umma_desc_sw128(v_addr + k * 2048), idesc_pv, 1);
+                umma_commit(&kv_empty[i % STAGES]);
+                umma_commit(pv_done);
+            }
+        }
+    } else {
+        // ---- softmax: thread = query row ---------------------------------------------------------------------
+        const int r = warp * 32 + lane;
+        const bool valid = r < rows;
+        const int my_pos = pos0 + r;
+        const int my_lo = (window > 0 && my_pos - window + 1 > 0) ? my_pos - window + 1 : 0;
+        const float scale_log2 = scale * 1.4426950408889634f;
+        const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+        uint8_t* ph_row = smem + PH_OFF + r * 128;
+        uint8_t* pl_row = smem + PL_OFF + r * 128;
+        float m = -INFINITY, l = 0.0f;              // the row's reference maximum (log2 units) and its sum against it
+        bool ok = true;
+        for (int i = 0; i < n_it; i++) {
+            const int key0 = (kt0 + i) * AT_BN;
+            if (!__all_sync(0xffffffffu, mbar_wait(&s_full[i & 1], (i >> 1) & 1))) { if (lane == 0) give_up(error, &failed, 15); ok = false; break; }
+            tc_fence_after();
+            uint32_t sr[AT_BN];
+            tmem_ld32_nowait(tmem_s + (i & 1) * AT_BN + lane_off, sr);
+            tmem_ld32_nowait(tmem_s + (i & 1) * AT_BN + lane_off + 32, sr + 32);
+            tmem_wait_ld();
+            tmem_loaded(sr);
+            tmem_loaded(sr + 32);
+            // raw scores: the maximum commutes with the (positive) scale; masked keys become -inf only on tiles that
+            // touch the diagonal, the window's edge or rows beyond the tile's own
+            if (!valid || key0 + AT_BN - 1 > my_pos || key0 < my_lo) {
+#pragma unroll
+                for (int j = 0; j < AT_BN; j++) {
+                    const int kk = key0 + j;
+                    if (!(valid && kk <= my_pos && kk >= my_lo)) sr[j] = 0xff800000u;
+                }
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < AT_BN; j++) mx = fmaxf(mx, __uint_as_float(sr[j]));
+            mx *= scale_log2;
+            bool pv_waited = false;
+            if (i == 0) {
+                m = mx;                             // O is written, not added to, by the first step
+            } else {
+                const bool raise = mx > m + RAISE;  // also the first counted key after none (m = -inf)
+                if (__any_sync(0xffffffffu, raise)) {
+                    // scale this warp's rows of O (and the sums) to the new maxima; every earlier P V must have landed
+                    if (!__all_sync(0xffffffffu, mbar_wait(pv_done, (i - 1) & 1))) { if (lane == 0) give_up(error, &failed, 16); ok = false; break; }
+                    pv_waited = true;
+                    tc_fence_after();
+                    const float alpha = raise ? at_ex2(m - mx) : 1.0f;
+#pragma unroll
+                    for (int c = 0; c < HD; c += 32) {
+                        uint32_t orr[32];
+                        tmem_ld32(tmem_o + lane_off + c, orr);
+                        tmem_loaded(orr);
+#pragma unroll
+                        for (int j = 0; j < 32; j++) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * alpha);
+                        tmem_st32(tmem_o + lane_off + c, orr);
+                    }
+                    tmem_wait_st();
+                    l *= alpha;
+                    if (raise) m = mx;
+                }
+            }
+            const float m_use = m == -INFINITY ? 0.0f : m;
+            // the probabilities may only replace the last step's once its P V has read them
+            if (i > 0 && !pv_waited) {
+                if (!__all_sync(0xffffffffu, mbar_wait(pv_done, (i - 1) & 1))) { if (lane == 0) give_up(error, &failed, 17); ok = false; break; }
+            }
+            float sum = 0.0f;
+#pragma unroll
+            for (int j8 = 0; j8 < AT_BN; j8 += 8) {
+                uint32_t hi[4], lo[4];
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    const float p0 = at_ex2(fmaf(__uint_as_float(sr[j8 + j]), scale_log2, -m_use));
+                    const float p1 = at_ex2(fmaf(__uint_as_float(sr[j8 + j + 1]), scale_log2, -m_use));
+                    sum += p0 + p1;
+                    const __nv_bfloat162 hv = __floats2bfloat162_rn(p0, p1);
+                    hi[j / 2] = *reinterpret_cast<const uint32_t*>(&hv);
+                    lo[j / 2] = at_pack(p0 - __bfloat162float(hv.x), p1 - __bfloat162float(hv.y));
+                }
+                const int chunk = (j8 >> 3) ^ (r & 7);            // 128-byte swizzle: 16-byte piece index xor row mod 8
+                *reinterpret_cast<uint4*>(ph_row + chunk * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4*>(pl_row + chunk * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            }
+            l += sum;
+            // the values' rows beyond the last position (pages not loaded, slots not yet written): never counted,
+            // but 0 * garbage must not be NaN
+            if (kt0 + i == kt1 && (last_pos & (AT_BN - 1)) != AT_BN - 1) {
+                const int z0 = (last_pos & (AT_BN - 1)) + 1;
+                uint8_t* vs = smem + V_OFF + (i % STAGES) * KV_BYTES;
+                for (int idx = r; idx < (AT_BN - z0) * 8; idx += AT_BM)
+                    *reinterpret_cast<uint4*>(vs + (z0 + idx / 8) * 128 + (idx & 7) * 16) = make_uint4(0, 0, 0, 0);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // P (and the zeros) are for the tensor core
+            tc_fence_before();
+            mbar_arrive(p_full);
+        }
+        if (ok && !__all_sync(0xffffffffu, mbar_wait(pv_done, (n_it - 1) & 1))) { if (lane == 0) give_up(error, &failed, 18); ok = false; }
+        if (ok) {
+            tc_fence_after();
+            const float inv = 1.0f / l;
+            __nv_bfloat16* dst = out + ((size_t)(tok0 + r) * nh + h) * HD;
+#pragma unroll
+            for (int c = 0; c < HD; c += 32) {
+                uint32_t orr[32];
+                tmem_ld32(tmem_o + lane_off + c, orr);
+                tmem_loaded(orr);
+                if (valid) {
+#pragma unroll
+                    for (int d = 0; d < 32; d += 8) {
+                        uint4 v;
+                        v.x = at_pack(__uint_as_float(orr[d]) * inv, __uint_as_float(orr[d + 1]) * inv);
+                        v.y = at_pack(__uint_as_float(orr[d + 2]) * inv, __uint_as_float(orr[d + 3]) * inv);
+                        v.z = at_pack(__uint_as_float(orr[d + 4]) * inv, __uint_as_float(orr[d + 5]) * inv);
+                        v.w = at_pack(__uint_as_float(orr[d + 6]) * inv, __uint_as_float(orr[d + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c + d) = v;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        if (failed) __nanosleep(200000);      // after a failed wait: let copies in flight land
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// A [rows, cols] bfloat16 matrix with row stride ld (elements), read in boxes of box_rows x 64 columns, 128-byte swizzle.
+static bool at_make_map(CUtensorMap* map, const void* base, long long rows, int cols, long long ld, int box_rows) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace vk
+
+using namespace vk;
+
+// q [n_tokens, nh*hd] bfloat16; cache [pages][2][nkv][page_size][hd] bfloat16 (one layer); tiles [n_tiles][4] with up to 128
+// rows a tile; out as q.  hd = 64; page_size a multiple of 8 that divides 64 or is a multiple of it.
+// error: a word the kernel sets (non-zero) if a bounded wait ran out.  VK_BAD_SHAPE for what this kernel does not take.
+VK_API int vk_attention_prefill_tcgen05(const void* q, const void* cache, const int32_t* block_tables, const int32_t* tiles, void* out,
+                                        int n_tokens, int n_tiles, int pages, int nh, int nkv, int hd, int page_size, int max_blocks,
+                                        float scale, int window, int* error, cudaStream_t stream) {
+    if (n_tiles <= 0) return VK_OK;
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || max_blocks <= 0 || window < 0 || n_tokens <= 0 || pages <= 0 || !error)
+        return VK_BAD_SHAPE;
+    if (hd != 64 || page_size % 8 != 0 || (AT_BN % page_size != 0 && page_size % AT_BN != 0)) return VK_BAD_SHAPE;
+    if (nh > 65535) return VK_TOO_LARGE;
+    const long long cache_rows = (long long)pages * 2 * nkv * page_size;
+    if (cache_rows >= (1ll << 31)) return VK_TOO_LARGE;
+    if (((uintptr_t)q % 16) || ((uintptr_t)cache % 16) || ((uintptr_t)out % 16)) return VK_BAD_ALIGNMENT;
+    CUtensorMap mq, mkv;
+    if (!at_make_map(&mq, q, n_tokens, nh * hd, (long long)nh * hd, AT_BM)) return VK_BAD_SHAPE;
+    if (!at_make_map(&mkv, cache, cache_rows, hd, hd, page_size < AT_BN ? page_size : AT_BN)) return VK_BAD_SHAPE;
+    const size_t smem = (size_t)AT_BM * 64 * 2 + 2 * AT_STAGES * AT_BN * 64 * 2 + 2 * AT_BM * AT_BN * 2 + 1024 + 128;
+    auto kern = attention_prefill_tcgen05_kernel<64>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    return launch_plain(kern, dim3(n_tiles, nh), dim3(AT_THREADS), smem, stream, mq, mkv, block_tables, tiles, (__nv_bfloat16*)out, nh,
+                        nkv, page_size, max_blocks, scale, window, error);
+}

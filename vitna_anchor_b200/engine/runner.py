@@ -74,7 +74,7 @@ class ModelRunner:
         self.max_segments = max_requests
         n_groups = len(self.cache.groups)
         most = max(max_batch_tokens, self.max_segments)
-        self._meta_len = 6 * most + 64 + 3 * self.max_segments + 1 + n_groups * (most + self.max_segments * self.max_blocks)
+        self._meta_len = 6 * most + 64 + 7 * self.max_segments + most // 16 + 1 + n_groups * (most + self.max_segments * self.max_blocks)
         self._staging = [_Staging(self._meta_len, True) for _ in range(4)]
         self._stage_i = 0
         self._meta_dev = torch.zeros(self._meta_len, dtype=torch.int32, device=self.device)
@@ -188,6 +188,9 @@ class ModelRunner:
                  for i in range(S) if lens[i] > 1 for o in range(0, lens[i], 64)]
         off = (off + 3) & ~3                                   # 16-byte alignment for what follows
         s_tiles = put(np.asarray(tiles, dtype=np.int32).reshape(-1), 4 * len(tiles)) if tiles else None
+        big = [(int(seg_starts[i]) + o, min(128, lens[i] - o), first[i] + o, i)
+               for i in range(S) if lens[i] > 1 for o in range(0, lens[i], 128)]
+        s_big = put(np.asarray(big, dtype=np.int32).reshape(-1), 4 * len(big)) if big else None
         group_slices = []
         for g in range(len(self.cache.groups)):
             bt = np.zeros((S, maxb), dtype=np.int32)
@@ -215,7 +218,8 @@ class ModelRunner:
             decode_only=all(n == 1 for n in lens),
             num_dec=len(dec), dec_tokens=None if (s_dec is None or not pre) else dev[s_dec],
             num_pre=len(pre), pre_tokens=None if s_pre is None else dev[s_pre],
-            pre_tiles=None if s_tiles is None else dev[s_tiles].view(-1, 4))
+            pre_tiles=None if s_tiles is None else dev[s_tiles].view(-1, 4),
+            pre_tiles_big=None if s_big is None else dev[s_big].view(-1, 4))
         return ctx, (dev[s_rows] if R else None)
 
     def step(self, entries: Sequence[StepEntry], token_source: Optional[Tuple[torch.Tensor, Sequence[int]]] = None) -> Optional[torch.Tensor]:
@@ -355,7 +359,8 @@ class ModelRunner:
         lens = [len(e.tokens) for e in entries]
         n_dec = sum(1 for n in lens if n == 1)
         n_tiles = sum(-(-n // 64) for n in lens if n > 1)
-        key = ("mixed", T, len(entries), R, n_dec, n_tiles)
+        n_big = sum(-(-n // 128) for n in lens if n > 1)
+        key = ("mixed", T, len(entries), R, n_dec, n_tiles, n_big)
         ctx, rows = self._build_context(entries, T, R, fixed_blocks=self.max_blocks, for_graph=True)
         held = self._graphs.get(key)
         if held is not None:

@@ -483,6 +483,35 @@ def attention_prefill(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: 
     return out
 
 
+def attention_prefill_tcgen05_takes(q: torch.Tensor, cache_layer: torch.Tensor, hd: int) -> bool:
+    """Whether the tcgen05 prompt-attention kernel takes these operands: bfloat16, head size 64, pages of 8, 16, 32
+    or a multiple of 64 slots, q rows dense and 16-byte aligned."""
+    ps = cache_layer.shape[3]
+    return (q.dtype == torch.bfloat16 and hd == 64 and ps % 8 == 0 and (64 % ps == 0 or ps % 64 == 0) and q.dim() == 2
+            and q.stride(1) == 1 and q.stride(0) == q.shape[1] and q.data_ptr() % 16 == 0 and cache_layer.data_ptr() % 16 == 0
+            and cache_layer.is_contiguous())
+
+
+def attention_prefill_tcgen05(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: torch.Tensor, tiles: torch.Tensor,
+                              out: torch.Tensor, nh: int, nkv: int, hd: int, scale: float, window: int = 0) -> torch.Tensor:
+    """Causal attention of prompt portions on the tcgen05 tensor cores (scores and P V in tensor memory, keys and
+    values by TMA straight from the pages).  tiles int32 [n, 4]: first token, rows (1..128), position of the first
+    token, segment."""
+    _req(q, "q", torch.bfloat16, 2); _req(cache_layer, "cache_layer", torch.bfloat16, 5)
+    _req(block_tables, "block_tables", torch.int32, 2); _req(tiles, "tiles", torch.int32, 2); _req(out, "out", torch.bfloat16, 2)
+    page_size = cache_layer.shape[3]
+    if (q.shape[1] != nh * hd or out.shape != q.shape or tuple(cache_layer.shape[1:]) != (2, nkv, page_size, hd) or tiles.shape[1] != 4
+            or out.stride(0) != out.shape[1]):
+        raise KernelError("attention_prefill_tcgen05: shapes do not fit the head counts")
+    if not attention_prefill_tcgen05_takes(q, cache_layer, hd):
+        raise KernelError("attention_prefill_tcgen05: bfloat16, head size 64 and pages of 8, 16, 32 or a multiple of 64 slots only")
+    _check(lib().vk_attention_prefill_tcgen05(_p(q), _p(cache_layer), _p(block_tables), _p(tiles), _p(out), q.shape[0], tiles.shape[0],
+                                              cache_layer.shape[0], nh, nkv, hd, page_size, block_tables.shape[1],
+                                              ctypes.c_float(scale), window, _p(error_word()), _stream()),
+           "attention_prefill_tcgen05")
+    return out
+
+
 def attention(q: torch.Tensor, pages: torch.Tensor, meta, ctx, out: torch.Tensor, nh: int, nkv: int, hd: int,
               scale: float, window: int = 0) -> torch.Tensor:
     """Causal attention of a mixed batch over the paged cache; `meta` is the page group's GroupMeta.
@@ -499,7 +528,10 @@ def attention(q: torch.Tensor, pages: torch.Tensor, meta, ctx, out: torch.Tensor
         attention_decode(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, scratch, cap, nh, nkv, hd, scale,
                          layout, min(layout, max(1, ctx.max_context)), window, ctx.dec_tokens)
     if pre_ok:
-        attention_prefill(q, pages, meta.block_tables, ctx.pre_tiles, out, nh, nkv, hd, scale, window)
+        if ctx.pre_tiles_big is not None and attention_prefill_tcgen05_takes(q, pages, hd) and out.stride(0) == out.shape[1]:
+            attention_prefill_tcgen05(q, pages, meta.block_tables, ctx.pre_tiles_big, out, nh, nkv, hd, scale, window)
+        else:
+            attention_prefill(q, pages, meta.block_tables, ctx.pre_tiles, out, nh, nkv, hd, scale, window)
     if not dec_ok and not pre_ok:
         return attention_rows(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, nh, nkv, hd, scale, window)
     if ctx.num_pre and not pre_ok:

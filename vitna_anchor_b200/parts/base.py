@@ -90,6 +90,7 @@ class StepContext:
     # segments longer than one token cut into tiles of up to 64 tokens: int32 [n, 4] = first token, rows,
     # position of the first token, segment
     pre_tiles: Optional[torch.Tensor] = None
+    pre_tiles_big: Optional[torch.Tensor] = None     # the same cut into tiles of up to 128 tokens
     extra: dict = field(default_factory=dict)
 
 
