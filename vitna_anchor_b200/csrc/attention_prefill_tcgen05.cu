@@ -5,12 +5,13 @@
 // One block takes a tile of up to 128 consecutive tokens of one request and one query head, and walks over the
 // request's keys 64 at a time:
 //
-//   warp 4   TMA: the query tile once; per step the keys and values of the step's pages, straight from the cache
-//            (a box of one page's rows for one key-value head, 128-byte swizzle) into a three-stage ring
-//   warp 5   one lane issues tcgen05.mma: S[128 x 64] = Q K^T into one of two score buffers in tensor memory (the
+//   warp 8   TMA: the query tile once; per step the keys and values of the step's pages, straight from the cache
+//            (a box of one page's rows for one key-value head, 128-byte swizzle) into two three-stage rings
+//   warp 9   one lane issues tcgen05.mma: S[128 x 64] = Q K^T into one of two score buffers in tensor memory (the
 //            next step's scores are computed while the softmax warps work on this step's), and, once the
 //            probabilities lie in shared memory, O[128 x 64] += P V (V as it lies in the cache: the N-major operand)
-//   warps 0-3  one query row per thread: read the row of S from tensor memory, mask, maximum, 2^x, write the
+//   warps 0-7  two threads a query row (warps w and w+4 share rows 32w .. 32w+31 and take 32 of the step's keys
+//            each): read the scores from tensor memory, mask, maximum (the two meet once a step), 2^x, write the
 //            probabilities as a high and a low bfloat16 part (p = hi + lo to about 2^-17, so that P V matches
 //            float32 probabilities) in the swizzled K-major layout the tensor core reads
 //
@@ -30,7 +31,7 @@
 
 namespace vk {
 
-constexpr int AT_BM = 128, AT_BN = 64, AT_THREADS = 192, AT_STAGES = 3;
+constexpr int AT_BM = 128, AT_BN = 64, AT_THREADS = 320, AT_STAGES = 3;
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -60,13 +61,16 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + BAR_OFF);
-    uint64_t* kv_full = q_full + 1;                  // [STAGES]
-    uint64_t* kv_empty = kv_full + STAGES;           // [STAGES]
-    uint64_t* s_full = kv_empty + STAGES;            // [2]
+    uint64_t* k_full = q_full + 1;                   // [STAGES] each: the keys' ring and the values' ring are released
+    uint64_t* k_empty = k_full + STAGES;             // separately, the keys' as soon as their scores are computed
+    uint64_t* v_full = k_empty + STAGES;
+    uint64_t* v_empty = v_full + STAGES;
+    uint64_t* s_full = v_empty + STAGES;             // [2]
     uint64_t* p_full = s_full + 2;
     uint64_t* pv_done = p_full + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
     __shared__ int failed;
+    __shared__ float xmax[4 * AT_BM];              // the halves' maxima of a row, two steps deep; at the end their sums
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = gridDim.x - 1 - blockIdx.x;     // later tiles of a prompt have more keys: start them first
@@ -80,15 +84,15 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
     if (threadIdx.x == 0) {
         failed = 0;
         mbar_init(q_full, 1);
-        for (int s = 0; s < STAGES; s++) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+        for (int s = 0; s < STAGES; s++) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
         mbar_init(&s_full[0], 1);
         mbar_init(&s_full[1], 1);
-        mbar_init(p_full, AT_BM);
+        mbar_init(p_full, 2 * AT_BM);
         mbar_init(pv_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 5) {
+    if (warp == 9) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -97,7 +101,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
     tc_fence_after();
     const uint32_t tmem_s = *tmem_slot, tmem_o = tmem_s + 2 * AT_BN;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ---- producer ------------------------------------------------------------------------------------
         if (lane == 0) {
             mbar_expect_tx(q_full, Q_BYTES);
@@ -105,28 +109,38 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
         }
         const int32_t* bt = block_tables + (size_t)seg * max_blocks;
         const int box_rows = page_size < AT_BN ? page_size : AT_BN, boxes = AT_BN / box_rows;
+        // lane b takes box b of a step: its page comes from the block table, read one step ahead
+        auto page_of = [&](int i) -> int {
+            const int key = (kt0 + i) * AT_BN + lane * box_rows;
+            return (i < n_it && lane < boxes && key <= last_pos) ? bt[key / page_size] : 0;
+        };
+        int page = page_of(0);
         for (int i = 0; i < n_it; i++) {
             const int s = i % STAGES, key0 = (kt0 + i) * AT_BN;
-            if (i >= STAGES) {
-                const bool ok = mbar_wait(&kv_empty[s], ((i / STAGES) - 1) & 1);
-                if (!__all_sync(0xffffffffu, ok)) { if (lane == 0) give_up(error, &failed, 11); break; }
-            }
+            const int page_next = page_of(i + 1);
             // boxes that hold a key some row needs; the rows of the others are never counted (p = 0) and the
             // values' rows beyond the last position are zeroed by the softmax warps
             int nb = (last_pos - key0) / box_rows + 1;
             nb = nb < boxes ? nb : boxes;
-            if (lane == 0) mbar_expect_tx(&kv_full[s], (uint32_t)nb * 2 * box_rows * HD * 2);
-            __syncwarp();
-            if (lane < nb) {
-                const int key = key0 + lane * box_rows;
-                const int page = bt[key / page_size], off = key % page_size;
-                const int yk = (page * 2 * nkv + kvh) * page_size + off;
-                const int yv = ((page * 2 + 1) * nkv + kvh) * page_size + off;
-                tma_load_2d(smem + K_OFF + s * KV_BYTES + lane * box_rows * (HD * 2), &map_kv, 0, yk, &kv_full[s]);
-                tma_load_2d(smem + V_OFF + s * KV_BYTES + lane * box_rows * (HD * 2), &map_kv, 0, yv, &kv_full[s]);
+            const int off = (key0 + lane * box_rows) % page_size;
+            const uint32_t dst = s * KV_BYTES + lane * box_rows * (HD * 2);
+            if (i >= STAGES) {
+                const bool ok = mbar_wait(&k_empty[s], ((i / STAGES) - 1) & 1);
+                if (!__all_sync(0xffffffffu, ok)) { if (lane == 0) give_up(error, &failed, 11); break; }
             }
+            if (lane == 0) mbar_expect_tx(&k_full[s], (uint32_t)nb * box_rows * HD * 2);
+            __syncwarp();
+            if (lane < nb) tma_load_2d(smem + K_OFF + dst, &map_kv, 0, (page * 2 * nkv + kvh) * page_size + off, &k_full[s]);
+            if (i >= STAGES) {
+                const bool ok = mbar_wait(&v_empty[s], ((i / STAGES) - 1) & 1);
+                if (!__all_sync(0xffffffffu, ok)) { if (lane == 0) give_up(error, &failed, 19); break; }
+            }
+            if (lane == 0) mbar_expect_tx(&v_full[s], (uint32_t)nb * box_rows * HD * 2);
+            __syncwarp();
+            if (lane < nb) tma_load_2d(smem + V_OFF + dst, &map_kv, 0, ((page * 2 + 1) * nkv + kvh) * page_size + off, &v_full[s]);
+            page = page_next;
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ---- tensor core ---------------------------------------------------------------------------------
         if (lane == 0) {
             const uint32_t idesc_qk = umma_idesc_bf16(AT_BM, AT_BN);
@@ -134,13 +148,14 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
             const uint32_t q_addr = smem_u32(smem), ph_addr = smem_u32(smem + PH_OFF), pl_addr = smem_u32(smem + PL_OFF);
             auto scores = [&](int i) -> bool {        // S[i & 1] = Q K_i^T
                 const int s = i % STAGES;
-                if (!mbar_wait(&kv_full[s], (i / STAGES) & 1)) { give_up(error, &failed, 13); return false; }
+                if (!mbar_wait(&k_full[s], (i / STAGES) & 1)) { give_up(error, &failed, 13); return false; }
                 tc_fence_after();
                 const uint32_t k_addr = smem_u32(smem + K_OFF + s * KV_BYTES);
 #pragma unroll
                 for (int k = 0; k < HD / 16; k++)
                     umma_bf16(tmem_s + (i & 1) * AT_BN, umma_desc_sw128(q_addr + k * 32), umma_desc_sw128(k_addr + k * 32), idesc_qk, k != 0);
                 umma_commit(&s_full[i & 1]);
+                umma_commit(&k_empty[s]);               // the keys' stage is free once these instructions have read it
                 return true;
             };
             bool ok = mbar_wait(q_full, 0);
@@ -149,6 +164,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
             for (int i = 0; i < n_it && ok; i++) {
                 // the next step's scores go into the other buffer while the softmax warps work on this step's
                 if (i + 1 < n_it && !scores(i + 1)) break;
+                if (!mbar_wait(&v_full[i % STAGES], (i / STAGES) & 1)) { give_up(error, &failed, 20); break; }
                 if (!mbar_wait(p_full, i & 1)) { give_up(error, &failed, 14); break; }
                 tc_fence_after();
                 const uint32_t v_addr = smem_u32(smem + V_OFF + (i % STAGES) * KV_BYTES);
@@ -159,132 +175,141 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
 #pragma unroll
                 for (int k = 0; k < AT_BN / 16; k++)
                     umma_bf16(tmem_o, umma_desc_sw128(pl_addr + k * 32), umma_desc_sw128(v_addr + k * 2048), idesc_pv, 1);
-                umma_commit(&kv_empty[i % STAGES]);
+                umma_commit(&v_empty[i % STAGES]);
                 umma_commit(pv_done);
             }
         }
     } else {
-        // ---- softmax: thread = query row ---------------------------------------------------------------------
-        const int r = warp * 32 + lane;
+        // ---- softmax: two threads a query row, 32 of the step's 64 keys each -----------------------------------
+        const int half = warp >> 2;                  // which 32 keys of a step, and which 32 columns of O
+        const int r = (warp & 3) * 32 + lane;
         const bool valid = r < rows;
         const int my_pos = pos0 + r;
         const int my_lo = (window > 0 && my_pos - window + 1 > 0) ? my_pos - window + 1 : 0;
         const float scale_log2 = scale * 1.4426950408889634f;
-        const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t bar_id = 1 + (warp & 3);      // the two warps of a row quarter meet on this barrier
         uint8_t* ph_row = smem + PH_OFF + r * 128;
         uint8_t* pl_row = smem + PL_OFF + r * 128;
-        float m = -INFINITY, l = 0.0f;              // the row's reference maximum (log2 units) and its sum against it
+        float m = -INFINITY, l = 0.0f;              // the row's reference maximum (log2 units) and this half's sum against it
+        // A failed wait clears `ok`; the thread then only keeps meeting its partner and arriving, so that nobody
+        // waits for it without a limit.
         bool ok = true;
         for (int i = 0; i < n_it; i++) {
-            const int key0 = (kt0 + i) * AT_BN;
-            if (!__all_sync(0xffffffffu, mbar_wait(&s_full[i & 1], (i >> 1) & 1))) { if (lane == 0) give_up(error, &failed, 15); ok = false; break; }
-            tc_fence_after();
-            uint32_t sr[AT_BN];
-            tmem_ld32_nowait(tmem_s + (i & 1) * AT_BN + lane_off, sr);
-            tmem_ld32_nowait(tmem_s + (i & 1) * AT_BN + lane_off + 32, sr + 32);
-            tmem_wait_ld();
-            tmem_loaded(sr);
-            tmem_loaded(sr + 32);
-            // raw scores: the maximum commutes with the (positive) scale; masked keys become -inf only on tiles that
-            // touch the diagonal, the window's edge or rows beyond the tile's own
-            if (!valid || key0 + AT_BN - 1 > my_pos || key0 < my_lo) {
-#pragma unroll
-                for (int j = 0; j < AT_BN; j++) {
-                    const int kk = key0 + j;
-                    if (!(valid && kk <= my_pos && kk >= my_lo)) sr[j] = 0xff800000u;
-                }
-            }
+            const int key0 = (kt0 + i) * AT_BN + half * 32;
+            uint32_t sr[32];
             float mx = -INFINITY;
+            if (ok && !__all_sync(0xffffffffu, mbar_wait(&s_full[i & 1], (i >> 1) & 1))) { if (lane == 0) give_up(error, &failed, 15); ok = false; }
+            if (ok) {
+                tc_fence_after();
+                tmem_ld32(tmem_s + (i & 1) * AT_BN + half * 32 + lane_off, sr);
+                tmem_loaded(sr);
+                // raw scores: the maximum commutes with the (positive) scale; masked keys become -inf only on tiles
+                // that touch the diagonal, the window's edge or rows beyond the tile's own
+                if (!valid || key0 + 31 > my_pos || key0 < my_lo) {
 #pragma unroll
-            for (int j = 0; j < AT_BN; j++) mx = fmaxf(mx, __uint_as_float(sr[j]));
-            mx *= scale_log2;
+                    for (int j = 0; j < 32; j++) {
+                        const int kk = key0 + j;
+                        if (!(valid && kk <= my_pos && kk >= my_lo)) sr[j] = 0xff800000u;
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 32; j++) mx = fmaxf(mx, __uint_as_float(sr[j]));
+                mx *= scale_log2;
+            }
+            xmax[((i & 1) * 2 + half) * AT_BM + r] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+            mx = fmaxf(mx, xmax[((i & 1) * 2 + (half ^ 1)) * AT_BM + r]);
             bool pv_waited = false;
             if (i == 0) {
                 m = mx;                             // O is written, not added to, by the first step
-            } else {
+            } else if (ok) {
                 const bool raise = mx > m + RAISE;  // also the first counted key after none (m = -inf)
                 if (__any_sync(0xffffffffu, raise)) {
-                    // scale this warp's rows of O (and the sums) to the new maxima; every earlier P V must have landed
-                    if (!__all_sync(0xffffffffu, mbar_wait(pv_done, (i - 1) & 1))) { if (lane == 0) give_up(error, &failed, 16); ok = false; break; }
+                    // scale this warp's part of O (and the sums) to the new maxima; every earlier P V must have landed
+                    if (!__all_sync(0xffffffffu, mbar_wait(pv_done, (i - 1) & 1))) { if (lane == 0) give_up(error, &failed, 16); ok = false; }
                     pv_waited = true;
-                    tc_fence_after();
-                    const float alpha = raise ? at_ex2(m - mx) : 1.0f;
-#pragma unroll
-                    for (int c = 0; c < HD; c += 32) {
+                    if (ok) {
+                        tc_fence_after();
+                        const float alpha = raise ? at_ex2(m - mx) : 1.0f;
                         uint32_t orr[32];
-                        tmem_ld32(tmem_o + lane_off + c, orr);
+                        tmem_ld32(tmem_o + lane_off + half * 32, orr);
                         tmem_loaded(orr);
 #pragma unroll
                         for (int j = 0; j < 32; j++) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * alpha);
-                        tmem_st32(tmem_o + lane_off + c, orr);
+                        tmem_st32(tmem_o + lane_off + half * 32, orr);
+                        tmem_wait_st();
+                        l *= alpha;
+                        if (raise) m = mx;
                     }
-                    tmem_wait_st();
-                    l *= alpha;
-                    if (raise) m = mx;
                 }
             }
             const float m_use = m == -INFINITY ? 0.0f : m;
             // the probabilities may only replace the last step's once its P V has read them
-            if (i > 0 && !pv_waited) {
-                if (!__all_sync(0xffffffffu, mbar_wait(pv_done, (i - 1) & 1))) { if (lane == 0) give_up(error, &failed, 17); ok = false; break; }
+            if (ok && i > 0 && !pv_waited) {
+                if (!__all_sync(0xffffffffu, mbar_wait(pv_done, (i - 1) & 1))) { if (lane == 0) give_up(error, &failed, 17); ok = false; }
             }
-            float sum = 0.0f;
+            if (ok) {
+                float sum = 0.0f;
 #pragma unroll
-            for (int j8 = 0; j8 < AT_BN; j8 += 8) {
-                uint32_t hi[4], lo[4];
+                for (int j8 = 0; j8 < 32; j8 += 8) {
+                    uint32_t hi[4], lo[4];
 #pragma unroll
-                for (int j = 0; j < 8; j += 2) {
-                    const float p0 = at_ex2(fmaf(__uint_as_float(sr[j8 + j]), scale_log2, -m_use));
-                    const float p1 = at_ex2(fmaf(__uint_as_float(sr[j8 + j + 1]), scale_log2, -m_use));
-                    sum += p0 + p1;
-                    const __nv_bfloat162 hv = __floats2bfloat162_rn(p0, p1);
-                    hi[j / 2] = *reinterpret_cast<const uint32_t*>(&hv);
-                    lo[j / 2] = at_pack(p0 - __bfloat162float(hv.x), p1 - __bfloat162float(hv.y));
+                    for (int j = 0; j < 8; j += 2) {
+                        const float p0 = at_ex2(fmaf(__uint_as_float(sr[j8 + j]), scale_log2, -m_use));
+                        const float p1 = at_ex2(fmaf(__uint_as_float(sr[j8 + j + 1]), scale_log2, -m_use));
+                        sum += p0 + p1;
+                        const __nv_bfloat162 hv = __floats2bfloat162_rn(p0, p1);
+                        hi[j / 2] = *reinterpret_cast<const uint32_t*>(&hv);
+                        lo[j / 2] = at_pack(p0 - __bfloat162float(hv.x), p1 - __bfloat162float(hv.y));
+                    }
+                    const int chunk = (half * 4 + (j8 >> 3)) ^ (r & 7);      // 128-byte swizzle: 16-byte piece index xor row mod 8
+                    *reinterpret_cast<uint4*>(ph_row + chunk * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<uint4*>(pl_row + chunk * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                 }
-                const int chunk = (j8 >> 3) ^ (r & 7);            // 128-byte swizzle: 16-byte piece index xor row mod 8
-                *reinterpret_cast<uint4*>(ph_row + chunk * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                *reinterpret_cast<uint4*>(pl_row + chunk * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                l += sum;
+                // the values' rows beyond the last position (pages not loaded, slots not yet written): never counted,
+                // but 0 * garbage must not be NaN
+                if (kt0 + i == kt1 && (last_pos & (AT_BN - 1)) != AT_BN - 1 &&
+                    __all_sync(0xffffffffu, mbar_wait(&v_full[i % STAGES], (i / STAGES) & 1))) {      // the values have landed
+                    const int z0 = (last_pos & (AT_BN - 1)) + 1;
+                    uint8_t* vs = smem + V_OFF + (i % STAGES) * KV_BYTES;
+                    for (int idx = half * AT_BM + r; idx < (AT_BN - z0) * 8; idx += 2 * AT_BM)
+                        *reinterpret_cast<uint4*>(vs + (z0 + idx / 8) * 128 + (idx & 7) * 16) = make_uint4(0, 0, 0, 0);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P (and the zeros) are for the tensor core
+                tc_fence_before();
             }
-            l += sum;
-            // the values' rows beyond the last position (pages not loaded, slots not yet written): never counted,
-            // but 0 * garbage must not be NaN
-            if (kt0 + i == kt1 && (last_pos & (AT_BN - 1)) != AT_BN - 1) {
-                const int z0 = (last_pos & (AT_BN - 1)) + 1;
-                uint8_t* vs = smem + V_OFF + (i % STAGES) * KV_BYTES;
-                for (int idx = r; idx < (AT_BN - z0) * 8; idx += AT_BM)
-                    *reinterpret_cast<uint4*>(vs + (z0 + idx / 8) * 128 + (idx & 7) * 16) = make_uint4(0, 0, 0, 0);
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // P (and the zeros) are for the tensor core
-            tc_fence_before();
             mbar_arrive(p_full);
         }
+        // the row's sum is the two halves' (both against the same maximum)
+        xmax[half * AT_BM + r] = l;
+        asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+        l += xmax[(half ^ 1) * AT_BM + r];
         if (ok && !__all_sync(0xffffffffu, mbar_wait(pv_done, (n_it - 1) & 1))) { if (lane == 0) give_up(error, &failed, 18); ok = false; }
         if (ok) {
             tc_fence_after();
             const float inv = 1.0f / l;
-            __nv_bfloat16* dst = out + ((size_t)(tok0 + r) * nh + h) * HD;
+            __nv_bfloat16* dst = out + ((size_t)(tok0 + r) * nh + h) * HD + half * 32;
+            uint32_t orr[32];
+            tmem_ld32(tmem_o + lane_off + half * 32, orr);
+            tmem_loaded(orr);
+            if (valid) {
 #pragma unroll
-            for (int c = 0; c < HD; c += 32) {
-                uint32_t orr[32];
-                tmem_ld32(tmem_o + lane_off + c, orr);
-                tmem_loaded(orr);
-                if (valid) {
-#pragma unroll
-                    for (int d = 0; d < 32; d += 8) {
-                        uint4 v;
-                        v.x = at_pack(__uint_as_float(orr[d]) * inv, __uint_as_float(orr[d + 1]) * inv);
-                        v.y = at_pack(__uint_as_float(orr[d + 2]) * inv, __uint_as_float(orr[d + 3]) * inv);
-                        v.z = at_pack(__uint_as_float(orr[d + 4]) * inv, __uint_as_float(orr[d + 5]) * inv);
-                        v.w = at_pack(__uint_as_float(orr[d + 6]) * inv, __uint_as_float(orr[d + 7]) * inv);
-                        *reinterpret_cast<uint4*>(dst + c + d) = v;
-                    }
+                for (int d = 0; d < 32; d += 8) {
+                    uint4 v;
+                    v.x = at_pack(__uint_as_float(orr[d]) * inv, __uint_as_float(orr[d + 1]) * inv);
+                    v.y = at_pack(__uint_as_float(orr[d + 2]) * inv, __uint_as_float(orr[d + 3]) * inv);
+                    v.z = at_pack(__uint_as_float(orr[d + 4]) * inv, __uint_as_float(orr[d + 5]) * inv);
+                    v.w = at_pack(__uint_as_float(orr[d + 6]) * inv, __uint_as_float(orr[d + 7]) * inv);
+                    *reinterpret_cast<uint4*>(dst + d) = v;
                 }
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         if (failed) __nanosleep(200000);      // after a failed wait: let copies in flight land
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"(TMEM_COLS) : "memory");
@@ -324,7 +349,7 @@ VK_API int vk_attention_prefill_tcgen05(const void* q, const void* cache, const 
     CUtensorMap mq, mkv;
     if (!at_make_map(&mq, q, n_tokens, nh * hd, (long long)nh * hd, AT_BM)) return VK_BAD_SHAPE;
     if (!at_make_map(&mkv, cache, cache_rows, hd, hd, page_size < AT_BN ? page_size : AT_BN)) return VK_BAD_SHAPE;
-    const size_t smem = (size_t)AT_BM * 64 * 2 + 2 * AT_STAGES * AT_BN * 64 * 2 + 2 * AT_BM * AT_BN * 2 + 1024 + 128;
+    const size_t smem = (size_t)AT_BM * 64 * 2 + 2 * AT_STAGES * AT_BN * 64 * 2 + 2 * AT_BM * AT_BN * 2 + 1024 + 256;
     auto kern = attention_prefill_tcgen05_kernel<64>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
