@@ -17,19 +17,22 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// Bounded wait for the phase with the given parity.  False: gave up.
+// Bounded wait for the phase with the given parity.  False: gave up.  The waiting thread is suspended by the
+// hardware (up to the hint's 20 microseconds a try, woken as soon as the phase completes) instead of polling: polls of
+// waiting warps would take issue slots from the warps that work.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_u32(bar);
-    const long long start = clock64();
-    for (;;) {
+    long long start = 0;
+    for (int tries = 0;; tries++) {
         uint32_t done;
         asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, p;\n\t}"
             : "=r"(done)
-            : "r"(addr), "r"(parity)
+            : "r"(addr), "r"(parity), "r"(20000u)
             : "memory");
         if (done) return true;
-        if ((unsigned long long)(clock64() - start) > TC_WAIT_CYCLES) return false;
+        if (tries == 0) start = clock64();
+        else if ((unsigned long long)(clock64() - start) > TC_WAIT_CYCLES) return false;
     }
 }
 
