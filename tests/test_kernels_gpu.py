@@ -463,9 +463,38 @@ def test_attention_prefill_tiles(ops, nh, nkv, hd, ps, window):
     """Prompt portions on the tensor cores: a whole prompt of 150 tokens, a portion of 37 tokens in mid-request
     (positions 103..139, across a boundary of 64), a portion of 2 tokens far into a context, and a portion that
     starts exactly at a multiple of 64.  Sharp scores; against the plain attention and against attention_rows."""
+    _prefill_case(ops, ops.attention_prefill, 64, nh, nkv, hd, ps, window, [150, 140, 601, 128 + 70], [150, 37, 2, 70])
+
+
+@pytest.mark.parametrize("nh,nkv,ps,window", [(9, 3, 16, 0), (4, 4, 8, 0), (2, 1, 32, 0), (6, 2, 64, 0), (3, 1, 128, 0),
+                                              (3, 3, 16, 70), (2, 1, 8, 200)])
+def test_attention_prefill_tcgen05(ops, nh, nkv, ps, window):
+    """The same on the fifth-generation tensor cores (head size 64, tiles of up to 128 tokens): a whole prompt of 300
+    tokens, portions in mid-request across boundaries of 64 and 128, two tokens far into a context, a portion that
+    ends exactly at a multiple of 64, and pages of many sizes.  Unused slots of the pages hold 1000."""
+    _prefill_case(ops, ops.attention_prefill_tcgen05, 128, nh, nkv, 64, ps, window, [300, 140, 601, 128 + 70, 448], [300, 37, 2, 70, 200])
+
+
+def test_attention_prefill_tcgen05_refuses_what_it_does_not_take(ops):
+    """Pages of 4 slots (a TMA box must be a multiple of eight 128-byte rows) and head sizes other than 64 are refused
+    with a clear error; the dispatcher then takes the mma.sync kernel."""
+    q = torch.zeros(8, 2 * 64, dtype=torch.bfloat16, device="cuda")
+    tiles = dev(np.asarray([(0, 8, 0, 0)], np.int32))
+    bt = dev(np.zeros((1, 4), np.int32))
+    small_pages = torch.zeros(4, 2, 1, 4, 64, dtype=torch.bfloat16, device="cuda")
+    assert not ops.attention_prefill_tcgen05_takes(q, small_pages, 64)
+    with pytest.raises(ops.KernelError):
+        ops.attention_prefill_tcgen05(q, small_pages, bt, tiles, torch.empty_like(q), 2, 1, 64, 0.125, 0)
+    q32 = torch.zeros(8, 2 * 32, dtype=torch.bfloat16, device="cuda")
+    pages32 = torch.zeros(4, 2, 1, 16, 32, dtype=torch.bfloat16, device="cuda")
+    assert not ops.attention_prefill_tcgen05_takes(q32, pages32, 32)
+    with pytest.raises(ops.KernelError):
+        ops.attention_prefill_tcgen05(q32, pages32, bt, tiles, torch.empty_like(q32), 2, 1, 32, 0.125, 0)
+
+
+def _prefill_case(ops, kernel, tile_rows, nh, nkv, hd, ps, window, lens, news):
+    """lens: context after the step; news: tokens of this step."""
     rng = np.random.default_rng(6)
-    lens = [150, 140, 601, 128 + 70]         # context after the step
-    news = [150, 37, 2, 70]                  # tokens of this step
     dtype = torch.bfloat16
     pages = sum(-(-n // ps) for n in lens) + 7
     pool = torch.zeros(pages, 2, nkv, ps, hd, dtype=dtype) + 1000.0
@@ -488,13 +517,15 @@ def test_attention_prefill_tiles(ops, nh, nkv, hd, ps, window):
             pool[bt[s, p // ps], 1, :, p % ps] = vv[p]
         ref = P.causal_attention(q, k, v, window=window or None).reshape(n, nh * hd)
         start = len(q_all)
-        for o in range(0, new, 64):
-            tiles.append((start + o, min(64, new - o), n - new + o, s))
+        for o in range(0, new, tile_rows):
+            tiles.append((start + o, min(tile_rows, new - o), n - new + o, s))
         for p in range(n - new, n):
             q_all.append(q[p].reshape(-1)); seg.append(s); pos.append(p); want.append(ref[p])
     q_dev = torch.from_numpy(np.stack(q_all)).to(dtype).cuda()
     out = torch.empty_like(q_dev)
-    ops.attention_prefill(q_dev, pool.cuda(), dev(bt), dev(np.asarray(tiles, np.int32)), out, nh, nkv, hd, 1.0 / math.sqrt(hd), window)
+    kernel(q_dev, pool.cuda(), dev(bt), dev(np.asarray(tiles, np.int32)), out, nh, nkv, hd, 1.0 / math.sqrt(hd), window)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
     want = np.stack(want)
     got = out.float().cpu().numpy()
     assert np.isfinite(got).all()
