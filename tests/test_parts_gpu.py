@@ -1,6 +1,7 @@
 """Each part alone against the plain function of the same name; a decoder whose schedule names a layer
-twice and lets a layer read another layer's cache; and a toy mixer with state of its own, defined here,
-registered, built and stepped with no change to the framework's files."""
+twice and lets a layer read another layer's cache; and toy parts defined here, registered, built and stepped
+with no change to the framework's files: a mixer with state of its own, a feed-forward with routing and a
+position encoding that adds learned rows."""
 import json
 import math
 
@@ -267,3 +268,145 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     assert np.abs(a1 - a2).max() < 1e-5 and np.abs(b1 - b2).max() < 1e-5
     assert np.abs(c1 - a1).max() < 1e-5 and np.abs(c2 - a1).max() < 1e-5
     assert np.abs(a1[1:] - a1[:-1]).max() > 1e-3          # the state does change the output from token to token
+
+
+def test_toy_routed_feed_forward_and_learned_positions(tmp_path):
+    """A made-up architecture with two more kinds of parts defined here and nowhere in the framework: a position
+    encoding that adds a learned row per position to the embeddings (the attention then rotates nothing), and a
+    feed-forward with routing (a float32 router picks one of three SwiGLU experts per token and weighs it by its
+    softmax probability).  Whole prompts, cut prompts and decoding agree with a plain statement of the same model."""
+    from vitna_anchor_b200 import ops
+    from vitna_anchor_b200.config import Architecture, register_architecture
+    from vitna_anchor_b200.engine.loading import load_model, write_random_model
+    from vitna_anchor_b200.engine.runner import ModelRunner, StepEntry
+    from vitna_anchor_b200.models.decoder import DecoderModel, LayerRun
+    from vitna_anchor_b200.parts import FeedForward, PositionEncoding, make_part, register_part
+    from vitna_anchor_b200.parts.embedding import Embedding, LMHead
+    from vitna_anchor_b200.weights import WeightSpec
+
+    class LearnedPositions(PositionEncoding):
+        def __init__(self, table):
+            self.table = table                      # float32 [max_positions, hidden]
+
+        def tensors(self):
+            return [self.table]
+
+        def on_embeddings(self, x, ctx):
+            x += self.table[ctx.positions.long()]
+
+    class Top1Experts(FeedForward):
+        def __init__(self, hidden, inter, router, gate_up, down):
+            self.hidden, self.inter, self.router, self.gate_up, self.down = hidden, inter, router, gate_up, down
+
+        def tensors(self):
+            return [self.router] + self.gate_up + self.down
+
+        def forward(self, xn, ctx, residual, norm=None):
+            logits = xn.float() @ self.router.t()                       # router logits in float32
+            prob = torch.softmax(logits, dim=-1)
+            pick = torch.argmax(logits, dim=-1)                         # the lowest id among equal maxima
+            for e in range(len(self.gate_up)):
+                idx = torch.nonzero(pick == e).flatten()
+                if idx.numel() == 0:
+                    continue
+                xe = xn[idx].contiguous()
+                gu = torch.empty(idx.numel(), 2 * self.inter, dtype=xn.dtype, device=xn.device)
+                ops.linear(xe, self.gate_up[e], gu, ops.LINEAR_SAME)
+                act = torch.empty(idx.numel(), self.inter, dtype=xn.dtype, device=xn.device)
+                ops.silu_mul(gu, act)
+                y = torch.empty(idx.numel(), self.hidden, dtype=torch.float32, device=xn.device)
+                ops.linear(act, self.down[e], y, ops.LINEAR_F32)
+                residual.index_add_(0, idx, y * prob[idx, e][:, None])
+
+    register_part("position", "toy_learned", LearnedPositions)
+    register_part("feed_forward", "toy_top1_experts", Top1Experts)
+    E = 3
+
+    def parse(cj):
+        return dict(H=cj["hidden_size"], V=cj["vocab_size"], L=cj["num_hidden_layers"], I=cj["intermediate_size"],
+                    nh=cj["num_attention_heads"], nkv=cj["num_key_value_heads"], hd=cj["head_dim"], P=cj["max_position_embeddings"])
+
+    def manifest(c):
+        m = [WeightSpec("embed.weight", (c["V"], c["H"])), WeightSpec("positions.weight", (c["P"], c["H"])), WeightSpec("norm.weight", (c["H"],))]
+        for l in range(c["L"]):
+            p = f"layers.{l}."
+            m += [WeightSpec(p + "qkv.weight", ((c["nh"] + 2 * c["nkv"]) * c["hd"], c["H"])), WeightSpec(p + "o.weight", (c["H"], c["nh"] * c["hd"])),
+                  WeightSpec(p + "norm1.weight", (c["H"],)), WeightSpec(p + "norm2.weight", (c["H"],)), WeightSpec(p + "router.weight", (E, c["H"]))]
+            for e in range(E):
+                m += [WeightSpec(p + f"experts.{e}.gate_up.weight", (2 * c["I"], c["H"])), WeightSpec(p + f"experts.{e}.down.weight", (c["H"], c["I"]))]
+        return m
+
+    def build(c, w, dtype, device):
+        d = lambda n: w[n].to(device=device, dtype=dtype).contiguous()
+        f = lambda n: w[n].to(device=device, dtype=torch.float32)
+        position = make_part("position", "toy_learned", table=f("positions.weight"))
+        blocks = []
+        for l in range(c["L"]):
+            p = f"layers.{l}."
+            blocks.append(make_part(
+                "block", "pre_norm",
+                mixer_norm=make_part("norm", "rmsnorm", width=c["H"], eps=1e-5, weight=f(p + "norm1.weight")),
+                mixer=make_part("mixer", "attention", hidden=c["H"], num_heads=c["nh"], num_kv_heads=c["nkv"], head_dim=c["hd"],
+                                wqkv=d(p + "qkv.weight"), wo=d(p + "o.weight"), position=position),
+                ffn_norm=make_part("norm", "rmsnorm", width=c["H"], eps=1e-5, weight=f(p + "norm2.weight")),
+                ffn=make_part("feed_forward", "toy_top1_experts", hidden=c["H"], inter=c["I"], router=f(p + "router.weight"),
+                              gate_up=[d(p + f"experts.{e}.gate_up.weight") for e in range(E)],
+                              down=[d(p + f"experts.{e}.down.weight") for e in range(E)])))
+        emb = Embedding(c["V"], c["H"], d("embed.weight"))
+        return DecoderModel(embedding=emb, blocks=blocks, schedule=[LayerRun(l, l) for l in range(c["L"])],
+                            final_norm=make_part("norm", "rmsnorm", width=c["H"], eps=1e-5, weight=f("norm.weight")),
+                            lm_head=LMHead(c["V"], c["H"], emb.table), position=position, dtype=dtype, vocab_size=c["V"],
+                            max_positions=c["P"])
+
+    register_architecture(Architecture("ToyRoutedLM", parse, manifest, build, lambda n: "norm" in n), replace=True)
+    cj = dict(architectures=["ToyRoutedLM"], hidden_size=40, vocab_size=61, num_hidden_layers=2, intermediate_size=24,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=12, max_position_embeddings=64)
+    write_random_model(str(tmp_path / "toy"), cj, 11, std=0.25)
+    json.dump(cj, open(tmp_path / "toy" / "config.json", "w"))
+    model = load_model(str(tmp_path / "toy"), "float32")
+    ids = [3, 14, 15, 9, 26, 5, 35, 8, 9, 7, 9, 32, 38, 46, 26, 43, 38, 32, 7, 9, 50, 28, 8]
+
+    # the plain statement of this model, from the plain functions of the parts
+    W = {k: v.astype(np.float32) for k, v in P.read_safetensors(str(tmp_path / "toy" / "model.safetensors")).items()}
+    c = parse(cj)
+    x = P.embed(W["embed.weight"], ids) + W["positions.weight"][:len(ids)]
+    picks = []
+    for l in range(c["L"]):
+        p = f"layers.{l}."
+        xn = P.rms_norm(x, W[p + "norm1.weight"], 1e-5)
+        qkv = P.linear(xn, W[p + "qkv.weight"])
+        qd, kd = c["nh"] * c["hd"], c["nkv"] * c["hd"]
+        q = qkv[:, :qd].reshape(-1, c["nh"], c["hd"]); k = qkv[:, qd:qd + kd].reshape(-1, c["nkv"], c["hd"]); v = qkv[:, qd + kd:].reshape(-1, c["nkv"], c["hd"])
+        x = x + P.linear(P.causal_attention(q, k, v), W[p + "o.weight"])
+        xn = P.rms_norm(x, W[p + "norm2.weight"], 1e-5)
+        logits = P.linear(xn, W[p + "router.weight"])
+        prob = np.exp(logits - logits.max(-1, keepdims=True)); prob /= prob.sum(-1, keepdims=True)
+        pick = logits.argmax(-1)
+        picks.append(pick)
+        y = np.zeros_like(x)
+        for t in range(len(ids)):
+            e = int(pick[t])
+            gu = W[p + f"experts.{e}.gate_up.weight"]
+            y[t] = P.swiglu(xn[t:t + 1], gu[:c["I"]], gu[c["I"]:], W[p + f"experts.{e}.down.weight"])[0] * prob[t, e]
+        x = x + y
+    want = P.linear(P.rms_norm(x, W["norm.weight"], 1e-5), W["embed.weight"])
+    assert all(len(set(pk.tolist())) > 1 for pk in picks)              # the router does send tokens to different experts
+
+    def run(cuts):
+        runner = ModelRunner(model, page_size=4, num_pages=8, max_requests=2, max_batch_tokens=32, cuda_graphs=False)
+        runner.open("a")
+        rows, at = [], 0
+        for n in cuts:
+            rows.append(runner.step([StepEntry("a", ids[at:at + n], range(n))]).cpu().numpy())
+            at += n
+        return np.concatenate(rows)
+    whole = run([len(ids)])
+    cut = run([5, 2, 9, 1, 1, 1, 1, 1, 1, 1])
+    scale = max(1.0, np.abs(want).max())
+    assert np.abs(whole - want).max() <= 2e-5 * scale
+    assert np.abs(cut - want).max() <= 2e-5 * scale
+    # the same token at another position gives other logits: the learned rows are added
+    runner = ModelRunner(model, page_size=4, num_pages=8, max_requests=2, max_batch_tokens=32, cuda_graphs=False)
+    runner.open("b")
+    moved = runner.step([StepEntry("b", ids[1:2], [0])]).cpu().numpy()   # token ids[1] at position 0 instead of 1
+    assert np.abs(moved[0] - whole[1]).max() > 1e-3
