@@ -94,8 +94,10 @@ __device__ __forceinline__ uint32_t dm_pack(float x, float y) {
 }
 
 // Warp w asks for keys and values 32w .. 32w+31 of the split with cp.async: consecutive lanes take consecutive
-// 16-byte pieces, so a request covers whole 128-byte lines (the keys of a page lie one after the other).  Rows
-// that do not count are zeroed (never counted, p = 0, but 0 * garbage must not be NaN).  No commit.
+// 16-byte pieces, so a request covers whole 128-byte lines (the keys of a page lie one after the other).  The
+// pages of the warp's keys are read from the block table in one trip (lane p reads the p-th of them) and handed
+// round by shuffle: a trip to memory per copy was a third of the block's time.  Rows that do not count are zeroed
+// (never counted, p = 0, but 0 * garbage must not be NaN).  No commit.
 template <int HD>
 __device__ __forceinline__ void dm_copy_warp(const DmArgs& a, const DmItem& it, __nv_bfloat16* sk, __nv_bfloat16* sv) {
     typedef __nv_bfloat16 T;
@@ -103,17 +105,22 @@ __device__ __forceinline__ void dm_copy_warp(const DmArgs& a, const DmItem& it, 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t page_stride = (size_t)2 * a.nkv * a.page_size * HD;
     const size_t v_off = (size_t)a.nkv * a.page_size * HD;
+    const int wk0 = it.k0 + warp * 32;                  // the warp's first key
+    const int pg0 = a.page_shift >= 0 ? wk0 >> a.page_shift : wk0 / a.page_size;
+    const int pg_last = a.page_shift >= 0 ? it.pos >> a.page_shift : it.pos / a.page_size;     // the request has pages up to here
+    const int my_page = pg0 + lane <= pg_last ? it.bt[pg0 + lane] : 0;        // at most 32 pages hold 32 keys
 #pragma unroll
     for (int i = 0; i < CH; i++) {
         const int c = i * 32 + lane;
         const int kl = warp * 32 + c / CH, part = c % CH;
         const int key = it.k0 + kl;
+        const int pg = a.page_shift >= 0 ? key >> a.page_shift : key / a.page_size;
+        const int page = __shfl_sync(0xffffffffu, my_page, pg - pg0);
         T* dk = sk + kl * LD + part * 8;
         T* dv = sv + kl * LD + part * 8;
         if (kl < it.nkeys && key >= it.lo) {
-            const int pg = a.page_shift >= 0 ? key >> a.page_shift : key / a.page_size;
             const int off = key - pg * a.page_size;
-            const T* kr = a.cache + (size_t)it.bt[pg] * page_stride + ((size_t)it.kvh * a.page_size + off) * HD + part * 8;
+            const T* kr = a.cache + (size_t)page * page_stride + ((size_t)it.kvh * a.page_size + off) * HD + part * 8;
             dm_cp_async16(dk, kr);
             dm_cp_async16(dv, kr + v_off);
         } else {
@@ -315,17 +322,18 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 3 : 1) attention_decode
     }
 
     // ---- the last block of this (token, kv-head tile) combines ----------------------------------------------
-    __threadfence();
+    // The block's partial is written; the barrier orders it before thread 0's counting, which releases it to the
+    // other blocks and acquires theirs (one instruction instead of a fence in every thread).
     __syncthreads();
     int* counter = a.counters + (size_t)zi * a.counter_tiles + it.y;
     if (tid == 0) {
-        const int old = atomicAdd(counter, 1);
+        int old;
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(counter) : "memory");
         is_last = old == n_active - 1;
         if (is_last) *counter = 0;              // ready for the next launch
     }
     __syncthreads();
     if (!is_last) return;
-    __threadfence();
     float* mxs = wts + DM_ROWS * 128;           // [16][n_active] maxima of the splits
     for (int i = tid; i < gt * n_active; i += DM_THREADS) {
         const int h = i / n_active, sp = first_split + i % n_active;
