@@ -379,7 +379,10 @@ static int launch_mma(MmaParams p, cudaStream_t stream) {
     const int tiles = (units + 7) / 8;
     // Batch rows a block: all of them (in groups of eight), unless the weights make too few tiles to fill the
     // machine; then the rows are split over blocks too, and the weights come several times, from the second-level cache.
+    // Small weights (up to 16 MB) never get more than 16 rows a block: re-reading them from the second-level cache
+    // is cheap, and 16 rows are few enough for the norm to be fused.
     int mg = p.M <= 8 ? 1 : p.M <= 16 ? 2 : p.M <= 32 ? 4 : 8;
+    if (mg > 2 && (size_t)p.N * p.K * 2 <= ((size_t)16 << 20)) mg = 2;
     while (mg > 1 && tiles * ((p.M + 8 * mg - 1) / (8 * mg)) < 120) mg /= 2;
     const int ychunks = (p.M + 8 * mg - 1) / (8 * mg);
     const int nblk = p.K / 32;

@@ -360,11 +360,13 @@ SKINNY_MAX_ROWS = 64
 FUSED_NORM_MAX_ROWS = 16     # a block of the few-rows kernel norms every row it stages: beyond this many a norm kernel runs once
 
 
-def _mma_rows_per_block(M: int, N: int) -> int:
+def _mma_rows_per_block(M: int, N: int, K: int) -> int:
     """Batch rows a block of the tensor-core few-rows kernel stages (its launcher's rule): all of them in groups
-    of eight, fewer when the weights make too few tiles to fill the machine."""
+    of eight; at most 16 for weights of up to 16 MB; fewer when the weights make too few tiles to fill the machine."""
     tiles = ((N + 1) // 2 + 7) // 8
     mg = 1 if M <= 8 else 2 if M <= 16 else 4 if M <= 32 else 8
+    if mg > 2 and N * K * 2 <= (16 << 20):
+        mg = 2
     while mg > 1 and tiles * -(-M // (8 * mg)) < 120:
         mg //= 2
     return 8 * mg
@@ -372,7 +374,7 @@ def _mma_rows_per_block(M: int, N: int) -> int:
 
 def _mma_norm_smem(M: int, K: int, N: int) -> int:
     """Shared memory of the tensor-core few-rows kernel with the fused norm: a block's rows staged whole in float32."""
-    rows = _mma_rows_per_block(M, N)
+    rows = _mma_rows_per_block(M, N, K)
     return rows * (4 * K + 64) + 4 * K + 8 * (rows // 8) * 512
 
 
@@ -383,7 +385,7 @@ def fused_norm_takes(dtype: torch.dtype, M: int, K: int, N: int) -> bool:
         return False
     if dtype == torch.float32 or K % 32 != 0:
         return M <= FUSED_NORM_MAX_ROWS
-    return _mma_rows_per_block(M, N) <= FUSED_NORM_MAX_ROWS and _mma_norm_smem(M, K, N) <= 112 * 1024
+    return _mma_rows_per_block(M, N, K) <= FUSED_NORM_MAX_ROWS and _mma_norm_smem(M, K, N) <= 112 * 1024
 
 
 def skinny_takes(dtype: torch.dtype, M: int, K: int, N: int = 0) -> bool:
