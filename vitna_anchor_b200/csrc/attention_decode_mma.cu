@@ -149,15 +149,11 @@ __device__ __forceinline__ void dm_load_q(const DmArgs& a, const DmItem& it, uin
 
 // Shared memory of a block: keys [256][HD+8], values [256][HD+8], the warps' maxima and sums [8][16][2] and the
 // weights of the warps' parts [8][16].  A warp's unnormalised output [16][HD] float32 lies over its own 32 keys,
-// dead once it has its scores; the combine's weights and maxima (16 KB) lie over the values, dead once every
-// warp has its p * v.  74 KB at HD = 64: three blocks a multiprocessor.
+// dead once it has its scores.  74 KB at HD = 64: three blocks a multiprocessor.
 template <int HD> struct DmSmem {
     static constexpr int LD = HD + 8;
     static constexpr size_t KV_BYTES = (size_t)2 * DM_SPLIT * LD * 2;
-    static constexpr size_t W_NEED = (size_t)2 * DM_ROWS * 128 * 4;            // the combine's weights and maxima
-    static constexpr bool W_OVER_V = (size_t)DM_SPLIT * LD * 2 >= W_NEED;
-    static constexpr size_t W_BYTES = W_OVER_V ? 0 : W_NEED;
-    static constexpr size_t BYTES = KV_BYTES + W_BYTES + (8 * DM_ROWS * 2 + 8 * DM_ROWS) * 4;
+    static constexpr size_t BYTES = KV_BYTES + (8 * DM_ROWS * 2 + 8 * DM_ROWS) * 4;
 };
 
 // Every warp works alone on its 32 keys: copy, scores, softmax against its own maximum, p * v with the
@@ -172,9 +168,7 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 3 : 1) attention_decode
     extern __shared__ __align__(16) unsigned char smem_raw[];
     T* sk = reinterpret_cast<T*>(smem_raw);                 // [256][LD]
     T* sv = sk + DM_SPLIT * LD;                             // [256][LD]
-    float* wts = L::W_OVER_V ? reinterpret_cast<float*>(sv)   // [16][128] weights of the combine, then [16][128] maxima
-                             : reinterpret_cast<float*>(smem_raw + L::KV_BYTES);
-    float* wml = reinterpret_cast<float*>(smem_raw + L::KV_BYTES + L::W_BYTES);   // [8 warps][16 rows][2]: maximum, sum
+    float* wml = reinterpret_cast<float*>(smem_raw + L::KV_BYTES);   // [8 warps][16 rows][2]: maximum, sum
     float* wes = wml + 8 * DM_ROWS * 2;                     // [8 warps][16 rows]: weight of the warp's part
     __shared__ float row_m[DM_ROWS], row_l[DM_ROWS];
     __shared__ int is_last;
@@ -334,41 +328,38 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 3 : 1) attention_decode
     }
     __syncthreads();
     if (!is_last) return;
-    float* mxs = wts + DM_ROWS * 128;           // [16][n_active] maxima of the splits
-    for (int i = tid; i < gt * n_active; i += DM_THREADS) {
-        const int h = i / n_active, sp = first_split + i % n_active;
-        const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml + (((size_t)zi * nh + h0 + h) * max_splits + sp) * 2));
-        mxs[i] = ml.x;
-        wts[h * 128 + (sp - first_split)] = ml.y;
-    }
-    __syncthreads();
-    if (tid < gt) {
-        float mm = -INFINITY;
-        for (int j = 0; j < n_active; j++) mm = fmaxf(mm, mxs[tid * n_active + j]);
-        float l = 0.0f;
-        for (int j = 0; j < n_active; j++) {
-            const float e = expf(mxs[tid * n_active + j] - mm);
-            l += wts[tid * 128 + j] * e;
-            wts[tid * 128 + j] = e;
-        }
-        row_l[tid] = 1.0f / l;
-    }
-    __syncthreads();
+    // Every thread combines one output element on its own: the splits' maxima, sums and partial outputs are asked
+    // for eight splits at a time in one trip to the second-level cache, and folded into a running maximum, sum and
+    // output in split order (the same order whatever else is in the batch).
     for (int i = tid; i < gt * HD; i += DM_THREADS) {
         const int h = i / HD, d = i % HD;
+        const float2* ml = reinterpret_cast<const float2*>(a.part_ml) + ((size_t)zi * nh + h0 + h) * max_splits + first_split;
         const float* po = a.part_o + (((size_t)zi * nh + h0 + h) * max_splits + first_split) * HD + d;
-        float o = 0.0f;
-        int j = 0;
-        for (; j + 4 <= n_active; j += 4) {
-            const float a0 = __ldcg(po + (size_t)j * HD), a1 = __ldcg(po + (size_t)(j + 1) * HD);
-            const float a2 = __ldcg(po + (size_t)(j + 2) * HD), a3 = __ldcg(po + (size_t)(j + 3) * HD);
-            o += a0 * wts[h * 128 + j];
-            o += a1 * wts[h * 128 + j + 1];
-            o += a2 * wts[h * 128 + j + 2];
-            o += a3 * wts[h * 128 + j + 3];
+        float mm = -INFINITY, l = 0.0f, o = 0.0f;
+        for (int j0 = 0; j0 < n_active; j0 += 8) {
+            float2 st[8];
+            float pv[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const bool on = j0 + j < n_active;
+                st[j] = on ? __ldcg(ml + j0 + j) : make_float2(-INFINITY, 0.0f);
+                pv[j] = on ? __ldcg(po + (size_t)(j0 + j) * HD) : 0.0f;
+            }
+            float cm = mm;
+#pragma unroll
+            for (int j = 0; j < 8; j++) cm = fmaxf(cm, st[j].x);
+            const float keep = mm == -INFINITY ? 0.0f : expf(mm - cm);          // cm is finite: every split has a counted key
+            l *= keep;
+            o *= keep;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float e = st[j].x == -INFINITY ? 0.0f : expf(st[j].x - cm);
+                l += st[j].y * e;
+                o += pv[j] * e;
+            }
+            mm = cm;
         }
-        for (; j < n_active; j++) o += __ldcg(po + (size_t)j * HD) * wts[h * 128 + j];
-        a.out[((size_t)t * nh + h0 + h) * HD + d] = __float2bfloat16_rn(o * row_l[h]);
+        a.out[((size_t)t * nh + h0 + h) * HD + d] = __float2bfloat16_rn(o / l);
     }
 }
 
