@@ -147,13 +147,12 @@ __device__ __forceinline__ void dm_load_q(const DmArgs& a, const DmItem& it, uin
     }
 }
 
-// Shared memory of a block: keys [256][HD+8], values [256][HD+8], the warps' maxima and sums [8][16][2] and the
-// weights of the warps' parts [8][16].  A warp's unnormalised output [16][HD] float32 lies over its own 32 keys,
+// Shared memory of a block: keys [256][HD+8], values [256][HD+8] and the warps' maxima and sums [8][16][2].  A warp's unnormalised output [16][HD] float32 lies over its own 32 keys,
 // dead once it has its scores.  74 KB at HD = 64: three blocks a multiprocessor.
 template <int HD> struct DmSmem {
     static constexpr int LD = HD + 8;
     static constexpr size_t KV_BYTES = (size_t)2 * DM_SPLIT * LD * 2;
-    static constexpr size_t BYTES = KV_BYTES + (8 * DM_ROWS * 2 + 8 * DM_ROWS) * 4;
+    static constexpr size_t BYTES = KV_BYTES + 8 * DM_ROWS * 2 * 4;
 };
 
 // Every warp works alone on its 32 keys: copy, scores, softmax against its own maximum, p * v with the
@@ -169,8 +168,6 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 3 : 1) attention_decode
     T* sk = reinterpret_cast<T*>(smem_raw);                 // [256][LD]
     T* sv = sk + DM_SPLIT * LD;                             // [256][LD]
     float* wml = reinterpret_cast<float*>(smem_raw + L::KV_BYTES);   // [8 warps][16 rows][2]: maximum, sum
-    float* wes = wml + 8 * DM_ROWS * 2;                     // [8 warps][16 rows]: weight of the warp's part
-    __shared__ float row_m[DM_ROWS], row_l[DM_ROWS];
     __shared__ int is_last;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gq = lane >> 2, qd = lane & 3;
@@ -279,41 +276,34 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 3 : 1) attention_decode
     }
     __syncthreads();
 
-    // ---- the warps' parts meet: row maximum, weights, sum; thread (row, warp) for the statistics -------------
-    if (tid < DM_ROWS * 8) {
-        const int row = tid >> 3, w = tid & 7;
-        const float2 ml = *reinterpret_cast<const float2*>(wml + (w * DM_ROWS + row) * 2);
-        float m = ml.x;
-        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
-        const float e = ml.x == -INFINITY ? 0.0f : expf(ml.x - m);
-        float l = ml.y * e;
-        l += __shfl_xor_sync(0xffffffffu, l, 1);
-        l += __shfl_xor_sync(0xffffffffu, l, 2);
-        l += __shfl_xor_sync(0xffffffffu, l, 4);
-        wes[w * DM_ROWS + row] = e;
-        if (w == 0) { row_m[row] = m; row_l[row] = l; }
-    }
-    __syncthreads();
+    // ---- the warps' parts meet: every thread takes one output element and weighs the eight parts itself, in warp
+    // order (row maximum, weights exp(own maximum - row maximum), sum); the threads of a row's first column also
+    // leave the row's maximum and sum
     const bool single = n_active == 1;
     for (int i = tid; i < gt * HD; i += DM_THREADS) {
         const int row = i / HD, d = i % HD;
-        float acc = 0.0f;
+        float2 ml[8];
+#pragma unroll
+        for (int w = 0; w < 8; w++) ml[w] = *reinterpret_cast<const float2*>(wml + (w * DM_ROWS + row) * 2);
+        float m = ml[0].x;
+#pragma unroll
+        for (int w = 1; w < 8; w++) m = fmaxf(m, ml[w].x);
+        float l = 0.0f, acc = 0.0f;
 #pragma unroll
         for (int w = 0; w < 8; w++) {
-            const float e = wes[w * DM_ROWS + row];
-            if (e != 0.0f) acc += reinterpret_cast<const float*>(sk + w * 32 * LD)[row * HD + d] * e;
+            if (ml[w].x == -INFINITY) continue;     // a warp without a counted key left nothing
+            const float e = expf(ml[w].x - m);
+            l += ml[w].y * e;
+            acc += reinterpret_cast<const float*>(sk + w * 32 * LD)[row * HD + d] * e;
         }
-        if (single) a.out[((size_t)t * nh + h0 + row) * HD + d] = __float2bfloat16_rn(acc / row_l[row]);
-        else a.part_o[(((size_t)zi * nh + h0 + row) * max_splits + split) * HD + d] = acc;
+        if (single) {
+            a.out[((size_t)t * nh + h0 + row) * HD + d] = __float2bfloat16_rn(acc / l);
+        } else {
+            a.part_o[(((size_t)zi * nh + h0 + row) * max_splits + split) * HD + d] = acc;
+            if (d == 0) *reinterpret_cast<float2*>(a.part_ml + (((size_t)zi * nh + h0 + row) * max_splits + split) * 2) = make_float2(m, l);
+        }
     }
     if (single) return;
-    if (tid < gt) {
-        float* ml = a.part_ml + (((size_t)zi * nh + h0 + tid) * max_splits + split) * 2;
-        ml[0] = row_m[tid];
-        ml[1] = row_l[tid];
-    }
 
     // ---- the last block of this (token, kv-head tile) combines ----------------------------------------------
     // The block's partial is written; the barrier orders it before thread 0's counting, which releases it to the
