@@ -428,7 +428,7 @@ def test_linear_skinny_rope_store_matches_the_separate_kernels(ops, dtype, nh, n
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 64, 64), (128, 128, 576), (2048, 960, 576), (300, 576, 1536), (65, 200, 72), (1000, 3072, 576),
-                                   (257, 49152, 576), (130, 72, 200)])
+                                   (257, 49152, 576), (130, 72, 200), (700, 1100, 520), (1500, 2048, 2048)])   # the last three of the big ones: 128 x 256 tiles
 def test_linear_tcgen05(ops, M, N, K):
     """The tcgen05 product against float64, and against the CUDA-core kernel (same exact products, float32 sums)."""
     torch.manual_seed(M + N + K)
@@ -536,7 +536,7 @@ def _prefill_case(ops, kernel, tile_rows, nh, nkv, hd, ps, window, lens, news):
     assert (rows.float() - out.float()).abs().max() <= 3e-2 * max(1.0, np.abs(want).max())
 
 
-@pytest.mark.parametrize("M,I,K", [(128, 64, 64), (2048, 1536, 576), (300, 200, 72), (70, 8192, 2048)])
+@pytest.mark.parametrize("M,I,K", [(128, 64, 64), (2048, 1536, 576), (300, 200, 72), (70, 8192, 2048), (600, 1096, 520)])
 def test_linear_tcgen05_swiglu_matches_the_separate_kernels(ops, M, I, K):
     torch.manual_seed(M + I)
     x = torch.randn(M, K).to(torch.bfloat16).cuda()
@@ -555,7 +555,8 @@ def test_linear_tcgen05_swiglu_matches_the_separate_kernels(ops, M, I, K):
     assert (got.double() - ref).abs().max() <= 2e-2 * float(ref.abs().max())
 
 
-@pytest.mark.parametrize("nh,nkv,hd,ps,M,K", [(9, 3, 64, 16, 200, 576), (2, 1, 128, 8, 130, 96), (32, 32, 64, 16, 70, 2048)])
+@pytest.mark.parametrize("nh,nkv,hd,ps,M,K", [(9, 3, 64, 16, 200, 576), (2, 1, 128, 8, 130, 96), (32, 32, 64, 16, 70, 2048),
+                                              (15, 5, 64, 16, 600, 960), (6, 3, 128, 32, 520, 512)])   # the last two: 128 x 256 tiles
 def test_linear_tcgen05_rope_matches_the_separate_kernels(ops, nh, nkv, hd, ps, M, K):
     torch.manual_seed(nh + M)
     N = (nh + 2 * nkv) * hd

@@ -12,6 +12,8 @@
 //
 // Every wait on an mbarrier is bounded: after about a second a waiter sets *error (a word the host can
 // read), the block stops issuing work, lets its copies land, frees its tensor memory and returns.
+#include <cstdlib>
+
 #include "tcgen05_common.cuh"
 
 namespace vk {
@@ -301,6 +303,263 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The wide variant for large products: a block (one a multiprocessor, as many blocks as multiprocessors) walks over
+// output tiles of 128 x 256, and two accumulators in tensor memory (2 x 256 columns, all there is) let the four
+// epilogue warps drain one tile while the tensor core fills the next.  A 128 x 256 tile reads a quarter fewer bytes
+// a flop from the second-level cache than 128 x 128 (which that traffic bounded at about 60 % of the tensor peak),
+// and N = 256 instructions take the tensor core longer than they take their thread to issue.
+// SwiGLU: a tile is 128 gate rows and the 128 up rows of the same columns.
+constexpr int TW_BN = 256, TW_STAGES = 4;
+
+template <int EPI, int HD = 0>
+__global__ void __launch_bounds__(TC_THREADS, 1) linear_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                                         const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
+                                                                         int M, int N, int K, int* error, const TcExtra ex) {
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = TW_BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + TW_STAGES * STAGE_BYTES);
+    uint64_t* empty = full + TW_STAGES;
+    uint64_t* acc_full = empty + TW_STAGES;       // [2]
+    uint64_t* acc_empty = acc_full + 2;           // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    __shared__ int failed;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    const int tile_cols = EPI == TC_SWIGLU ? TW_BN / 2 : TW_BN;                // output columns of a tile
+    const int out_cols = EPI == TC_SWIGLU ? ex.inter : N;
+    const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (out_cols + tile_cols - 1) / tile_cols;
+    const int num_tiles = tiles_m * tiles_n;      // tile t: rows (t % tiles_m) * 128, columns (t / tiles_m) * tile_cols
+
+    if (threadIdx.x == 0) {
+        failed = 0;
+        for (int s = 0; s < TW_STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * TW_BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int kc = 0;                            // stages filled so far, over all of this block's tiles
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * tile_cols;
+                for (int kb = 0; kb < num_kb; kb++, kc++) {
+                    const int s = kc % TW_STAGES;
+                    if (kc >= TW_STAGES && !mbar_wait(&empty[s], ((kc / TW_STAGES) - 1) & 1)) { give_up(error, &failed, 31); ok = false; break; }
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    tma_load_2d(smem + s * STAGE_BYTES, &map_x, kb * TC_BK, m0, &full[s]);
+                    if (EPI == TC_SWIGLU) {        // the map's box is 128 rows: gate rows, then the same rows of up
+                        tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &map_w, kb * TC_BK, n0, &full[s]);
+                        tma_load_2d(smem + s * STAGE_BYTES + A_BYTES + B_BYTES / 2, &map_w, kb * TC_BK, ex.inter + n0, &full[s]);
+                    } else {
+                        tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &map_w, kb * TC_BK, n0, &full[s]);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_bf16(TC_BM, TW_BN);
+            int kc = 0, j = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, j++) {
+                const int b = j & 1;
+                if (j >= 2 && !mbar_wait(&acc_empty[b], ((j >> 1) - 1) & 1)) { give_up(error, &failed, 32); break; }
+                tc_fence_after();
+                for (int kb = 0; kb < num_kb; kb++, kc++) {
+                    const int s = kc % TW_STAGES;
+                    if (!mbar_wait(&full[s], (kc / TW_STAGES) & 1)) { give_up(error, &failed, 33); ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t a_desc = umma_desc_sw128(smem_u32(smem + s * STAGE_BYTES));
+                    const uint64_t b_desc = umma_desc_sw128(smem_u32(smem + s * STAGE_BYTES + A_BYTES));
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; k++) umma_bf16(tmem_base + b * TW_BN, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+                    umma_commit(&empty[s]);
+                }
+                if (ok) umma_commit(&acc_full[b]);
+            }
+        }
+    } else {
+        // epilogue: warp w reads lanes 32*(w%4) .. +31 of the accumulator, one output row per thread
+        const int quarter = warp & 3;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        int j = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, j++) {
+            const int b = j & 1;
+            const int row = (t % tiles_m) * TC_BM + quarter * 32 + lane, n0 = (t / tiles_m) * tile_cols;
+            if (ok && !__all_sync(0xffffffffu, mbar_wait(&acc_full[b], (j >> 1) & 1))) { if (lane == 0) give_up(error, &failed, 34); ok = false; }
+            if (ok) {
+                tc_fence_after();
+                const uint32_t acc = lane_base + b * TW_BN;
+                if (EPI == TC_SWIGLU) {
+#pragma unroll 1
+                    for (int c = 0; c < TW_BN / 2; c += 32) {
+                        uint32_t gr[32], ur[32];
+                        tmem_ld32_nowait(acc + c, gr);
+                        tmem_ld32_nowait(acc + TW_BN / 2 + c, ur);
+                        tmem_wait_ld();
+                        tmem_loaded(gr);
+                        tmem_loaded(ur);
+                        const int col = n0 + c;
+                        if (row < M && col < ex.inter) {
+                            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * ex.inter + col;
+                            uint32_t packed[16];
+#pragma unroll
+                            for (int q = 0; q < 32; q += 2) {
+                                float v[2];
+#pragma unroll
+                                for (int e = 0; e < 2; e++) {
+                                    const float gte = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gr[q + e])));
+                                    const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ur[q + e])));
+                                    v[e] = (gte / (1.0f + expf(-gte))) * up;
+                                }
+                                __nv_bfloat162 pk = __floats2bfloat162_rn(v[0], v[1]);
+                                packed[q / 2] = *reinterpret_cast<uint32_t*>(&pk);
+                            }
+                            if (col + 32 <= ex.inter && (ex.inter % 8 == 0)) {
+#pragma unroll
+                                for (int q = 0; q < 4; q++)
+                                    *reinterpret_cast<uint4*>(o + 8 * q) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                            } else {
+                                for (int q = 0; q < 32 && col + q < ex.inter; q++)
+                                    o[q] = __ushort_as_bfloat16((unsigned short)((packed[q / 2] >> ((q & 1) * 16)) & 0xffffu));
+                            }
+                        }
+                    }
+                } else if (EPI == TC_ROPE) {
+                    // the tile is 256 / HD heads: q heads, then k heads, then v heads (see the narrow kernel)
+                    constexpr int HDX = HD > 0 ? HD : 64, HALF = HDX / 2;
+                    const int sl = row < M ? ex.slot[row] : -1;
+                    const int p0 = row < M ? ex.positions[row] : 0;
+#pragma unroll 1
+                    for (int hh = 0; hh < TW_BN / HDX; hh++) {
+                        const int head = n0 / HDX + hh;
+                        if (head >= ex.nh + 2 * ex.nkv) break;          // the same for the whole warp
+                        const bool is_q = head < ex.nh, is_k = !is_q && head < ex.nh + ex.nkv;
+                        __nv_bfloat16* dst = nullptr;                   // where this row's head goes (null: nowhere)
+                        if (row < M) {
+                            if (is_q) dst = reinterpret_cast<__nv_bfloat16*>(out) + ((size_t)row * ex.nh + head) * HDX;
+                            else if (sl >= 0) {
+                                const int kvh = is_k ? head - ex.nh : head - ex.nh - ex.nkv;
+                                dst = ex.cache + (size_t)(sl / ex.page_size) * 2 * ex.nkv * ex.page_size * HDX +
+                                      (is_k ? 0 : (size_t)ex.nkv * ex.page_size * HDX) + ((size_t)kvh * ex.page_size + sl % ex.page_size) * HDX;
+                            }
+                        }
+#pragma unroll 1
+                        for (int c = 0; c < HALF; c += 32) {
+                            uint32_t ar[32], br[32];                    // columns c .. c+31 of the head and their partners HALF + c ..
+                            tmem_ld32_nowait(acc + hh * HDX + c, ar);
+                            tmem_ld32_nowait(acc + hh * HDX + HALF + c, br);
+                            tmem_wait_ld();
+                            tmem_loaded(ar);
+                            tmem_loaded(br);
+                            if (!dst) continue;
+                            const float4* cp = reinterpret_cast<const float4*>(ex.cos_t + (size_t)p0 * HALF + c);
+                            const float4* sp = reinterpret_cast<const float4*>(ex.sin_t + (size_t)p0 * HALF + c);
+                            uint32_t pa[16], pb[16];
+#pragma unroll
+                            for (int q = 0; q < 32; q += 4) {
+                                float4 c4 = make_float4(1.0f, 1.0f, 1.0f, 1.0f), s4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                                if (is_q || is_k) { c4 = cp[q / 4]; s4 = sp[q / 4]; }
+                                const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+                                float ra[4], rb[4];
+#pragma unroll
+                                for (int e = 0; e < 4; e++) {
+                                    const float a = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ar[q + e])));
+                                    const float b2 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(br[q + e])));
+                                    ra[e] = a * cs[e] - b2 * sn[e];
+                                    rb[e] = b2 * cs[e] + a * sn[e];
+                                }
+                                __nv_bfloat162 va0 = __floats2bfloat162_rn(ra[0], ra[1]), va1 = __floats2bfloat162_rn(ra[2], ra[3]);
+                                __nv_bfloat162 vb0 = __floats2bfloat162_rn(rb[0], rb[1]), vb1 = __floats2bfloat162_rn(rb[2], rb[3]);
+                                pa[q / 2] = *reinterpret_cast<uint32_t*>(&va0); pa[q / 2 + 1] = *reinterpret_cast<uint32_t*>(&va1);
+                                pb[q / 2] = *reinterpret_cast<uint32_t*>(&vb0); pb[q / 2 + 1] = *reinterpret_cast<uint32_t*>(&vb1);
+                            }
+#pragma unroll
+                            for (int q = 0; q < 4; q++) {
+                                *reinterpret_cast<uint4*>(dst + c + 8 * q) = make_uint4(pa[4 * q], pa[4 * q + 1], pa[4 * q + 2], pa[4 * q + 3]);
+                                *reinterpret_cast<uint4*>(dst + HALF + c + 8 * q) = make_uint4(pb[4 * q], pb[4 * q + 1], pb[4 * q + 2], pb[4 * q + 3]);
+                            }
+                        }
+                    }
+                } else {
+#pragma unroll 1
+                    for (int c = 0; c < TW_BN; c += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(acc + c, r);
+                        tmem_loaded(r);
+                        const int col = n0 + c;
+                        if (row >= M || col >= N) continue;
+                        const bool whole = col + 32 <= N;
+                        if (EPI == TC_SAME) {
+                            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + col;
+                            if (whole && (N % 8 == 0)) {
+#pragma unroll
+                                for (int q = 0; q < 32; q += 8) {
+                                    uint4 v;
+                                    __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[q]), __uint_as_float(r[q + 1]));
+                                    __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[q + 2]), __uint_as_float(r[q + 3]));
+                                    __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[q + 4]), __uint_as_float(r[q + 5]));
+                                    __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[q + 6]), __uint_as_float(r[q + 7]));
+                                    v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
+                                    v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
+                                    *reinterpret_cast<uint4*>(o + q) = v;
+                                }
+                            } else {
+                                for (int q = 0; q < 32 && col + q < N; q++) o[q] = __float2bfloat16_rn(__uint_as_float(r[q]));
+                            }
+                        } else {
+                            float* o = reinterpret_cast<float*>(out) + (size_t)row * N + col;
+                            if (whole && (N % 4 == 0)) {
+                                float4 prev[8];
+                                if (EPI == TC_ACC) {           // all eight reads are issued before any is used
+#pragma unroll
+                                    for (int q = 0; q < 8; q++) prev[q] = *reinterpret_cast<const float4*>(o + 4 * q);
+                                }
+#pragma unroll
+                                for (int q = 0; q < 8; q++) {
+                                    float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
+                                                           __uint_as_float(r[4 * q + 3]));
+                                    if (EPI == TC_ACC) { v.x += prev[q].x; v.y += prev[q].y; v.z += prev[q].z; v.w += prev[q].w; }
+                                    *reinterpret_cast<float4*>(o + 4 * q) = v;
+                                }
+                            } else {
+                                for (int q = 0; q < 32 && col + q < N; q++) {
+                                    if (EPI == TC_ACC) o[q] += __uint_as_float(r[q]);
+                                    else o[q] = __uint_as_float(r[q]);
+                                }
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive_plain(&acc_empty[b]);      // kept even after a failed wait: nobody waits for this warp without a limit
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (failed) __nanosleep(200000);      // after a failed wait: let copies in flight land
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * TW_BN) : "memory");
+    }
+}
+
 // A [rows, cols] bfloat16 matrix with row stride ld (elements), read in boxes of box_rows x 64 columns.
 static bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
     EncodeTiledFn enc = encode_tiled();
@@ -326,6 +585,46 @@ static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, void* out, in
     return launch_plain(kern, grid, dim3(TC_THREADS), smem, stream, mx, mw, out, M, N, K, error, ex);
 }
 
+static int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+// Whether the wide variant takes a product.  Measured at M = 2,048: it wins where a block gets more than one tile
+// (the epilogue of one hides behind the main loop of the next) or where K is long enough that the main loop is nearly
+// all of a tile's time; with one short tile a block the narrow kernel's two blocks a multiprocessor do better.
+// tile_cols: output columns of a wide tile.  VITNA_TCGEN05_WIDE=0 or 1 overrides (for measurements).
+static bool wide_takes(int M, int out_cols, int K, int tile_cols = TW_BN) {
+    static int forced = -1;
+    if (forced < 0) {
+        const char* e = getenv("VITNA_TCGEN05_WIDE");
+        forced = e ? (e[0] == '1' ? 1 : 0) : 2;
+    }
+    if (forced != 2) return forced == 1;
+    if (M < 512 || out_cols < 1024 || K < 512) return false;
+    const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((out_cols + tile_cols - 1) / tile_cols);
+    return K >= 2048 || (K >= 768 && tiles * 4 >= (long long)sm_count() * 5);    // at K = 576 a tile's epilogue outlasts its main loop
+}
+
+template <int EPI, int HD = 0>
+static int launch_wide(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int M, int N, int K, int* error, cudaStream_t stream,
+                       const TcExtra& ex = TcExtra{}) {
+    const size_t smem = (size_t)TW_STAGES * (TC_BM * TC_BK * 2 + TW_BN * TC_BK * 2) + 1024 + 128;
+    auto kern = linear_tcgen05_wide_kernel<EPI, HD>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    const int tile_cols = EPI == TC_SWIGLU ? TW_BN / 2 : TW_BN;
+    const int cols = EPI == TC_SWIGLU ? ex.inter : N;
+    const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((cols + tile_cols - 1) / tile_cols);
+    const int grid = tiles < sm_count() ? (int)tiles : sm_count();
+    return launch_plain(kern, dim3(grid), dim3(TC_THREADS), smem, stream, mx, mw, out, M, N, K, error, ex);
+}
+
 }  // namespace vk
 
 using namespace vk;
@@ -340,6 +639,13 @@ VK_API int vk_linear_tcgen05(const void* x, const void* w, void* out, int M, int
     if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)out % 16)) return VK_BAD_ALIGNMENT;
     const int bn = N >= 2048 ? 128 : 64;
     if ((M + TC_BM - 1) / TC_BM > 65535) return VK_TOO_LARGE;
+    if (wide_takes(M, N, K)) {
+        CUtensorMap wx, ww;
+        if (!make_map(&wx, x, M, K, ldx, TC_BM) || !make_map(&ww, w, N, K, K, TW_BN)) return VK_BAD_SHAPE;
+        if (mode == 0) return launch_wide<TC_SAME>(wx, ww, out, M, N, K, error, stream);
+        if (mode == 1) return launch_wide<TC_F32>(wx, ww, out, M, N, K, error, stream);
+        return launch_wide<TC_ACC>(wx, ww, out, M, N, K, error, stream);
+    }
     CUtensorMap mx, mw;
     if (!make_map(&mx, x, M, K, ldx, TC_BM) || !make_map(&mw, w, N, K, K, bn)) return VK_BAD_SHAPE;
 #define GO(BN, EPI) return launch_tc<BN, EPI>(mx, mw, out, M, N, K, error, stream)
@@ -363,9 +669,13 @@ VK_API int vk_linear_tcgen05_swiglu(const void* x, const void* w, void* out, int
     if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)out % 16)) return VK_BAD_ALIGNMENT;
     if ((M + TC_BM - 1) / TC_BM > 65535) return VK_TOO_LARGE;
     CUtensorMap mx, mw;
-    if (!make_map(&mx, x, M, K, ldx, TC_BM) || !make_map(&mw, w, 2 * inter, K, K, 64)) return VK_BAD_SHAPE;
     TcExtra ex{};
     ex.inter = inter;
+    if (wide_takes(M, inter, K, TW_BN / 2)) {
+        if (!make_map(&mx, x, M, K, ldx, TC_BM) || !make_map(&mw, w, 2 * inter, K, K, TW_BN / 2)) return VK_BAD_SHAPE;
+        return launch_wide<TC_SWIGLU>(mx, mw, out, M, 2 * inter, K, error, stream, ex);
+    }
+    if (!make_map(&mx, x, M, K, ldx, TC_BM) || !make_map(&mw, w, 2 * inter, K, K, 64)) return VK_BAD_SHAPE;
     return launch_tc<128, TC_SWIGLU>(mx, mw, out, M, 2 * inter, K, error, stream, ex);
 }
 
@@ -388,6 +698,11 @@ VK_API int vk_linear_tcgen05_rope(const void* x, const void* w, void* q_out, int
     TcExtra ex{};
     ex.positions = positions; ex.cos_t = cos_t; ex.sin_t = sin_t; ex.slot = slot; ex.cache = (__nv_bfloat16*)cache;
     ex.nh = nh; ex.nkv = nkv; ex.hd = hd; ex.page_size = page_size;
+    if (wide_takes(M, N, K)) {
+        if (!make_map(&mw, w, N, K, K, TW_BN)) return VK_BAD_SHAPE;
+        if (hd == 64) return launch_wide<TC_ROPE, 64>(mx, mw, q_out, M, N, K, error, stream, ex);
+        return launch_wide<TC_ROPE, 128>(mx, mw, q_out, M, N, K, error, stream, ex);
+    }
     if (hd == 64) return launch_tc<64, TC_ROPE>(mx, mw, q_out, M, N, K, error, stream, ex);
     return launch_tc<128, TC_ROPE>(mx, mw, q_out, M, N, K, error, stream, ex);
 }
