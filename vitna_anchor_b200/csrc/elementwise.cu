@@ -20,6 +20,19 @@ __global__ void embed_rows_kernel(const T* __restrict__ table, const int32_t* __
 }
 
 // y_i = (x_i * (1 / sqrt(sum(x^2)/n + eps))) * w_i    (engine/src/kernels.c:94-111)
+// Four consecutive values in one store (the address is aligned to four values).
+template <typename T> __device__ __forceinline__ void store4(T* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 v;
+    v.x = *reinterpret_cast<uint32_t*>(&lo);
+    v.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = v;
+}
+
 // A warp per output row (eight rows a block): 16-byte loads when the rows allow, the 32 partial sums meet in a
 // fixed shuffle tree.  `rows` (optional) names the input row of each output row.
 template <typename T>
@@ -35,6 +48,30 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
     const bool vec = (n % 4 == 0) && (reinterpret_cast<uintptr_t>(in) % 16 == 0) && (reinterpret_cast<uintptr_t>(w) % 16 == 0) &&
                      (reinterpret_cast<uintptr_t>(out) % (4 * sizeof(T)) == 0);
     float ss = 0.0f;
+    constexpr int KEEP = 16;                       // rows of up to 128 * KEEP values stay in registers between the two passes
+    if (vec && n <= 128 * KEEP) {
+        float4 v[KEEP];
+#pragma unroll
+        for (int j = 0; j < KEEP; j++) {
+            const int i = lane * 4 + j * 128;
+            v[j] = i < n ? *reinterpret_cast<const float4*>(in + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+#pragma unroll
+        for (int j = 0; j < KEEP; j++) {           // the same order of sums as the loop below
+            if (lane * 4 + j * 128 < n) { ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss); ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss); }
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+#pragma unroll
+        for (int j = 0; j < KEEP; j++) {
+            const int i = lane * 4 + j * 128;
+            if (i < n) {
+                const float4 g = *reinterpret_cast<const float4*>(w + i);
+                store4<T>(out + i, (v[j].x * inv) * g.x, (v[j].y * inv) * g.y, (v[j].z * inv) * g.z, (v[j].w * inv) * g.w);
+            }
+        }
+        return;
+    }
     if (vec) {
 #pragma unroll 4
         for (int i = lane * 4; i < n; i += 128) {
@@ -51,10 +88,7 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
         for (int i = lane * 4; i < n; i += 128) {
             const float4 v = *reinterpret_cast<const float4*>(in + i);
             const float4 g = *reinterpret_cast<const float4*>(w + i);
-            out[i] = from_f32<T>((v.x * inv) * g.x);
-            out[i + 1] = from_f32<T>((v.y * inv) * g.y);
-            out[i + 2] = from_f32<T>((v.z * inv) * g.z);
-            out[i + 3] = from_f32<T>((v.w * inv) * g.w);
+            store4<T>(out + i, (v.x * inv) * g.x, (v.y * inv) * g.y, (v.z * inv) * g.z, (v.w * inv) * g.w);
         }
     } else {
         for (int i = lane; i < n; i += 32) out[i] = from_f32<T>((in[i] * inv) * w[i]);
