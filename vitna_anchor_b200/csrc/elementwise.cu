@@ -216,8 +216,8 @@ VK_API int vk_rmsnorm_rows(const float* x, const float* w, const int32_t* rows, 
     if (out_rows <= 0) return VK_OK;
     if (n <= 0) return VK_BAD_SHAPE;
     const dim3 grid((out_rows + 7) / 8);
-    if (dtype == 0) return launch_plain(rmsnorm_rows_kernel<float>, grid, dim3(256), 0, stream, x, w, rows, (float*)y, out_rows, n, eps);
-    return launch_plain(rmsnorm_rows_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, x, w, rows, (__nv_bfloat16*)y, out_rows, n, eps);
+    if (dtype == 0) return launch_dependent(rmsnorm_rows_kernel<float>, grid, dim3(256), 0, stream, x, w, rows, (float*)y, out_rows, n, eps);
+    return launch_dependent(rmsnorm_rows_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, x, w, rows, (__nv_bfloat16*)y, out_rows, n, eps);
 }
 
 VK_API int vk_rope_store(const void* qkv, const int32_t* positions, const float* cos_t, const float* sin_t,

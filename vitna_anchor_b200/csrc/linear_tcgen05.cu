@@ -582,7 +582,7 @@ static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, void* out, in
     const int tile_cols = EPI == TC_SWIGLU ? BN / 2 : BN;
     const int cols = EPI == TC_SWIGLU ? ex.inter : N;
     dim3 grid((cols + tile_cols - 1) / tile_cols, (M + TC_BM - 1) / TC_BM);
-    return launch_plain(kern, grid, dim3(TC_THREADS), smem, stream, mx, mw, out, M, N, K, error, ex);
+    return launch_dependent(kern, grid, dim3(TC_THREADS), smem, stream, mx, mw, out, M, N, K, error, ex);
 }
 
 static int sm_count() {
