@@ -412,8 +412,10 @@ static int launch_mma(MmaParams p, cudaStream_t stream) {
     if (smem > 220 * 1024) return VK_TOO_LARGE;
     // a block stages x (and computes the norm) for itself, so there are no more blocks than are resident at once
     // (two a multiprocessor, one if the staged rows are large); each takes every gridDim.x-th tile
+    // (the row chunks share them)
     const int resident = 148 * (smem + 1024 <= 113 * 1024 ? 2 : 1);
-    const int blocks = tiles < resident ? tiles : resident;
+    const int per_chunk = resident / ychunks > 0 ? resident / ychunks : 1;
+    const int blocks = tiles < per_chunk ? tiles : per_chunk;
     p.tpb = (tiles + blocks - 1) / blocks;
     const bool pipe = nblk / ks > 4;                    // more than one batch of four runs a warp
 #define LAUNCH(MGV)                                                                                                         \
