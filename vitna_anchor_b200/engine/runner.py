@@ -256,7 +256,7 @@ class ModelRunner:
         return logits
 
     # -- decoding through CUDA graphs -----------------------------------------------------------
-    def _decode_context(self, entries: Sequence[StepEntry], B: int, views: bool = True):
+    def _decode_context(self, entries: Sequence[StepEntry], B: int, views: bool = True, reach: int = 0):
         """The context of a batch of single tokens, padded to B segments, at fixed offsets in the
         metadata buffer so that a captured graph finds every array where it was at capture.  A padding
         segment has one token at position 0 that writes nothing (slot -1) and reads page 0."""
@@ -311,7 +311,7 @@ class ModelRunner:
             token_seg=dev[o_seg:o_seg + B], seg_starts=dev[o_starts:o_starts + B + 1], seg_context=dev[o_ctx:o_ctx + B],
             seg_slots=dev[o_slots:o_slots + B], groups=groups, caches=self.cache.views, workspace=self.workspace,
             host_seg_lens=[1] * B, host_seg_first_pos=first + [0] * (B - S), host_seg_slots=[rc.slot for rc in rcs] + [0] * (B - S),
-            max_seg_len=1, max_context=self.max_model_len, decode_only=True, num_dec=B)
+            max_seg_len=1, max_context=reach or self.max_model_len, decode_only=True, num_dec=B)
         return ctx, dev[o_rows:o_rows + B]
 
     def _decode_step(self, entries: Sequence[StepEntry], token_source=None) -> torch.Tensor:
@@ -320,8 +320,13 @@ class ModelRunner:
         while B < S:
             B *= 2
         B = min(B, self.max_segments) if S <= self.max_segments else S
-        held = self._graphs.get(B)
-        ctx, rows = self._decode_context(entries, B, views=held is None)
+        # the longest context, rounded up to 512 positions, bounds the grid of the decode attention: a graph per
+        # batch bucket and context bucket, so that a short context does not launch the blocks of a long one
+        longest = max(self.cache.tables.get(e.request_id).length for e in entries) + 1
+        reach = min(self.max_model_len, -(-longest // 512) * 512)
+        key = (B, reach)
+        held = self._graphs.get(key)
+        ctx, rows = self._decode_context(entries, B, views=held is None, reach=reach)
         if token_source is not None:
             ids, src = token_source
             if self._src_dev is None:
@@ -343,7 +348,7 @@ class ModelRunner:
                 static_logits = self.model.forward(ctx, rows)
             kernels = ops.launch_count() - before
             ops.add_launches(-kernels)            # capture does not run the kernels; `logits` above is this step's result
-            self._graphs[B] = (graph, static_logits, kernels)
+            self._graphs[key] = (graph, static_logits, kernels)
             return logits[:S]
         graph, static_logits, kernels = held
         graph.replay()
