@@ -22,6 +22,14 @@ import numpy as np
 F32 = np.float32
 
 
+def bf16_round(x):
+    """x rounded to the nearest bfloat16 (ties to even) and widened back to float32: the value a tensor has after
+    it has been stored in 16 bits (the upper half of a float32, engine/src/ops.c:25-30 read the other way)."""
+    u = np.ascontiguousarray(x, dtype=F32).view(np.uint32)
+    r = (u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) & np.uint32(0xFFFF0000)
+    return r.view(F32).reshape(np.shape(x))
+
+
 # ----------------------------------------------------------------------------
 # Reading a model folder
 # ----------------------------------------------------------------------------
@@ -134,56 +142,77 @@ def linear(x, w):
     return (x.astype(F32) @ w.astype(F32).T).astype(F32)
 
 
-def swiglu(xn, w_gate, w_up, w_down):
+def swiglu(xn, w_gate, w_up, w_down, rnd=None):
     """act_i = (g_i / (1 + exp(-g_i))) * u_i; y = W_down act
-    (engine/src/model.c:966-971, engine/src/ops.c:283-288)."""
-    g = linear(xn, w_gate)
-    u = linear(xn, w_up)
-    act = (g / (F32(1.0) + np.exp(-g, dtype=F32))) * u
+    (engine/src/model.c:966-971, engine/src/ops.c:283-288).  rnd: applied to what a 16-bit engine stores (the gate
+    and up products, then the activation)."""
+    rnd = rnd or (lambda a: a)
+    g = rnd(linear(xn, w_gate))
+    u = rnd(linear(xn, w_up))
+    act = rnd((g / (F32(1.0) + np.exp(-g, dtype=F32))) * u)
     return linear(act.astype(F32), w_down)
 
 
-def attention_block(x, W, prefix, cfg, positions, window=None):
+def attention_block(x, W, prefix, cfg, positions, window=None, kv=None, return_kv=False, rnd=None):
     """RMSNorm, q/k/v, rotation of q and k, attention, output projection,
-    residual sum (engine/src/model.c:912-959)."""
+    residual sum (engine/src/model.c:912-959).  kv: rotated keys and values of
+    another run to attend over instead of this one's own.  rnd: applied to every tensor that a 16-bit engine
+    stores between two kernels (normed activations; q, k, v before and after the rotation, so the cache too; the
+    attention's output); the residual stream and all sums stay float32."""
+    rnd = rnd or (lambda a: a)
     T = x.shape[0]
-    xn = rms_norm(x, W[prefix + "input_layernorm.weight"], cfg["eps"])
-    q = linear(xn, W[prefix + "self_attn.q_proj.weight"]).reshape(T, cfg["nh"], cfg["hd"])
-    k = linear(xn, W[prefix + "self_attn.k_proj.weight"]).reshape(T, cfg["nkv"], cfg["hd"])
-    v = linear(xn, W[prefix + "self_attn.v_proj.weight"]).reshape(T, cfg["nkv"], cfg["hd"])
+    xn = rnd(rms_norm(x, W[prefix + "input_layernorm.weight"], cfg["eps"]))
+    q = rnd(linear(xn, W[prefix + "self_attn.q_proj.weight"])).reshape(T, cfg["nh"], cfg["hd"])
+    k = rnd(linear(xn, W[prefix + "self_attn.k_proj.weight"])).reshape(T, cfg["nkv"], cfg["hd"])
+    v = rnd(linear(xn, W[prefix + "self_attn.v_proj.weight"])).reshape(T, cfg["nkv"], cfg["hd"])
     cos, sin = rope_tables(positions, cfg["hd"], cfg["theta"])
-    q, k = rope_half(q, cos, sin), rope_half(k, cos, sin)
-    att = causal_attention(q, k, v, window)
-    return (x + linear(att, W[prefix + "self_attn.o_proj.weight"])).astype(F32)
+    q, k = rnd(rope_half(q, cos, sin)), rnd(rope_half(k, cos, sin))
+    if kv is not None:
+        k, v = kv
+    att = rnd(causal_attention(q, k, v, window))
+    y = (x + linear(att, W[prefix + "self_attn.o_proj.weight"])).astype(F32)
+    return (y, (k, v)) if return_kv else y
 
 
-def mlp_block(x, W, prefix, cfg):
+def mlp_block(x, W, prefix, cfg, rnd=None):
     """RMSNorm, SwiGLU, residual sum (engine/src/model.c:962-972)."""
-    xn = rms_norm(x, W[prefix + "post_attention_layernorm.weight"], cfg["eps"])
+    rnd = rnd or (lambda a: a)
+    xn = rnd(rms_norm(x, W[prefix + "post_attention_layernorm.weight"], cfg["eps"]))
     return (x + swiglu(xn, W[prefix + "mlp.gate_proj.weight"], W[prefix + "mlp.up_proj.weight"],
-                       W[prefix + "mlp.down_proj.weight"])).astype(F32)
+                       W[prefix + "mlp.down_proj.weight"], rnd)).astype(F32)
 
 
-def lm_head(x, W, cfg):
+def lm_head(x, W, cfg, rnd=None):
     """Final RMSNorm and the output matrix; the embedding stands in for a
     missing lm_head.weight when the two are tied (engine/src/model.c:315-321,
     975-978)."""
-    xn = rms_norm(x, W["model.norm.weight"], cfg["eps"])
+    rnd = rnd or (lambda a: a)
+    xn = rnd(rms_norm(x, W["model.norm.weight"], cfg["eps"]))
     head = W["lm_head.weight"] if "lm_head.weight" in W else W["model.embed_tokens.weight"]
     return linear(xn, head)
 
 
-def forward(cfg, W, ids, layer_order=None):
+def forward(cfg, W, ids, layer_order=None, reads=None, bf16=False):
     """Logits [len(ids), V] of one whole sequence starting at position 0.
     `layer_order` names the layers to run, in order (default: 0..L-1,
-    engine/src/model.c:906-972)."""
+    engine/src/model.c:906-972).  reads[i] = j: run i attends over the keys and
+    values that run j (an earlier one) made, and makes none of its own.
+    bf16: the same computation with the matrices and every tensor between two kernels rounded to bfloat16 where a
+    16-bit engine stores them (norm weights, the residual stream, softmax and every sum stay float32): what the
+    bfloat16 path is held to, more tightly than to the unrounded computation."""
+    rnd = bf16_round if bf16 else None
+    if bf16:
+        W = {k: (v if v.ndim < 2 else bf16_round(v)) for k, v in W.items()}
     positions = np.arange(len(ids))
     x = embed(W["model.embed_tokens.weight"], ids)
-    for l in (range(cfg["L"]) if layer_order is None else layer_order):
+    order = list(range(cfg["L"]) if layer_order is None else layer_order)
+    made = {}
+    for i, l in enumerate(order):
         p = f"model.layers.{l}."
-        x = attention_block(x, W, p, cfg, positions)
-        x = mlp_block(x, W, p, cfg)
-    return lm_head(x, W, cfg)
+        src = None if reads is None else reads.get(i)
+        x, made[i] = attention_block(x, W, p, cfg, positions, kv=None if src is None else made[src], return_kv=True, rnd=rnd)
+        x = mlp_block(x, W, p, cfg, rnd)
+    return lm_head(x, W, cfg, rnd)
 
 
 # ----------------------------------------------------------------------------

@@ -14,10 +14,18 @@ class Replay:
     """One trace_run process.  run(steps) feeds steps one by one, waiting for `done <step>` after each,
     and returns {(request id, position): logits row}."""
 
-    def __init__(self, model_dir, dtype, out_dir, max_tokens):
+    def __init__(self, model_dir, dtype, out_dir, max_tokens, kv_block=None, max_requests=None, plugins=None):
         self.out_dir = str(out_dir)
-        self.proc = subprocess.Popen([sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", self.out_dir,
-                                      "--max-tokens", str(max_tokens)], stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+        cmd = [sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", self.out_dir, "--max-tokens", str(max_tokens)]
+        if kv_block is not None:
+            cmd += ["--kv-block", str(kv_block)]
+        if max_requests is not None:
+            cmd += ["--max-requests", str(max_requests)]
+        env = dict(os.environ)
+        if plugins:          # architectures defined under tests/: the child imports them by name
+            env["VITNA_ANCHOR_PLUGINS"] = plugins
+            env["PYTHONPATH"] = os.path.dirname(os.path.abspath(__file__)) + os.pathsep + env.get("PYTHONPATH", "")
+        self.proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env=env)
         self.next_step = 0
         self.position = {}
 
@@ -83,13 +91,16 @@ def changing_portions(rid, ids, sizes=(7, 2, 13, 3, 2, 29, 5, 2, 64, 11)):
     return steps
 
 
-def mixed(requests, prompt_part, rng, live_max=4):
-    """requests: {id: ids}; the first prompt_part[id] tokens go in portions of 2..11, the rest one by one.
-    Up to live_max requests are live; a live request is sometimes left out of a step."""
+def mixed(requests, prompt_part, rng, live_max=4, portions=(2, 12), one_prompt_at_a_time=False):
+    """requests: {id: ids}; the first prompt_part[id] tokens go in portions of portions[0]..portions[1]-1 tokens
+    (2..11 unless given), the rest one by one.  Up to live_max requests are live; a live request is sometimes
+    left out of a step.  one_prompt_at_a_time: a request is let in only when every live one is past its prompt
+    part, so that its portions run beside the decoded tokens of the others."""
     waiting = list(requests)
     live, pos, steps = [], {}, []
     while waiting or live:
-        while waiting and len(live) < live_max:
+        while (waiting and len(live) < live_max
+               and not (one_prompt_at_a_time and any(pos[r] < prompt_part[r] for r in live))):
             rid = waiting.pop(0)
             live.append(rid)
             pos[rid] = 0
@@ -100,7 +111,7 @@ def mixed(requests, prompt_part, rng, live_max=4):
                 continue
             p = pos[rid]
             if p < prompt_part[rid]:
-                n = min(int(rng.integers(2, 12)), prompt_part[rid] - p)
+                n = min(int(rng.integers(portions[0], portions[1])), prompt_part[rid] - p)
                 if prompt_part[rid] - p - n == 1:
                     n += 1
             else:

@@ -8,6 +8,7 @@ import sys
 
 import numpy as np
 import pytest
+import torch
 
 import plain_llama as P
 from tiny_configs import TINIES, write_tiny
@@ -215,3 +216,103 @@ def test_decoding_a_step_ahead_of_the_host_gives_the_same_tokens(sharp_dirs):
             assert eng.runner.graph_replays > 10
     assert outs[(True, False)] == outs[(False, False)]
     assert outs[(True, True)] == outs[(False, True)]
+
+
+def test_logits_handed_out_by_the_entry_point_do_not_change_with_later_steps(sharp_dirs):
+    """The step function's result is valid until the next step (replayed graphs share one logits buffer); what
+    the entry point hands out is a copy: rows kept across many later steps of the same shape stay as they were."""
+    from vitna_anchor_b200.engine.engine import Engine
+    from vitna_anchor_b200.engine.runner import StepEntry
+    cfg, W = P.read_model(sharp_dirs["tinyA"])
+    eng = Engine(sharp_dirs["tinyA"], dtype="float32", kv_block=4, parallel=2)
+    ids = [int(t) for t in np.random.default_rng(1).integers(0, cfg["V"], 40)]
+    rows = eng.logits(ids, piece=1)                     # 40 single-token steps: from the second on they are replays
+    kept = rows.clone()
+    eng.logits(ids[::-1], piece=1)                      # later steps of the same shape
+    assert torch.equal(rows, kept)
+    assert np.abs(rows.cpu().numpy() - P.forward(cfg, W, ids)).max() <= 2e-5 * 5
+    # the raw step function does reuse the buffer, as its docstring says
+    runner = eng.runner
+    runner.open("x")
+    first = runner.step([StepEntry("x", ids[:1], [0])])
+    second = runner.step([StepEntry("x", ids[1:2], [0])])
+    third = runner.step([StepEntry("x", ids[2:3], [0])])
+    assert second.data_ptr() == third.data_ptr()
+    runner.close("x")
+
+
+@pytest.mark.parametrize("family,cuts", [("linear_tcgen05", [100]), ("attention_prefill_tcgen05", [200])])
+def test_a_kernel_that_gives_up_a_wait_fails_the_step_and_the_engine_goes_on(family, cuts, tmp_path):
+    """A wait inside a tcgen05 kernel runs out (the test's hook makes the producer leave one stage unarmed; the limit
+    of a wait is set to 5 ms): the kernel returns by itself, the step function reports it, the request is back
+    where it was, and the same step again gives the right logits."""
+    from vitna_anchor_b200 import ops
+    from vitna_anchor_b200.engine.loading import load_model, write_random_model
+    from vitna_anchor_b200.engine.runner import DeviceStepFailed, ModelRunner, StepEntry
+    cfg_json = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_act="silu", rms_norm_eps=1e-5,
+                    tie_word_embeddings=True, max_position_embeddings=1024, num_hidden_layers=2, hidden_size=128,
+                    intermediate_size=256, num_attention_heads=2, num_key_value_heads=1, head_dim=64, vocab_size=320,
+                    rope_theta=10000.0)
+    write_random_model(str(tmp_path / "m"), cfg_json, seed=3, std=0.1)
+    cfg, W = P.read_model(str(tmp_path / "m"))
+    ids = [int(t) for t in np.random.default_rng(5).integers(0, cfg["V"], 260)]
+    plain = P.forward(cfg, W, ids)
+    runner = ModelRunner(load_model(str(tmp_path / "m"), "bfloat16"), page_size=16, num_pages=64, max_requests=2, max_batch_tokens=256)
+    runner.open("r")
+    n = cuts[0]
+    good = runner.step([StepEntry("r", ids[:40], [39])]).float().cpu().numpy()
+    runner.check(sync=True)
+    free_before = runner.cache.free_pages()
+    ops.set_wait_limit_ms(5.0)
+    try:
+        ops.skip_stage_once(family, 0)
+        bad = runner.step([StepEntry("r", ids[40:40 + n], [n - 1])])
+        with pytest.raises(DeviceStepFailed) as e:
+            runner.check(sync=True)
+        assert e.value.request_ids == ["r"]
+    finally:
+        ops.set_wait_limit_ms(0)
+    assert runner.length("r") == 40 and runner.cache.free_pages() == free_before
+    assert ops.device_error_code() == 0
+    again = runner.step([StepEntry("r", ids[40:40 + n], [n - 1])]).float().cpu().numpy()
+    runner.check(sync=True)
+    scale = max(1.0, float(np.abs(plain).max()))
+    assert np.abs(good[0] - plain[39]).max() <= 8e-2 * scale
+    assert np.abs(again[0] - plain[40 + n - 1]).max() <= 8e-2 * scale
+    runner.cache.check()
+
+
+def test_a_kernel_that_gives_up_ends_the_requests_of_that_step_only(tmp_path):
+    """Through the entry point: two requests are in the step that meets the failed wait (one decoding, one with its
+    prompt): both end with an error and keep what they had.  A third that was still waiting is admitted afterwards
+    and gets the tokens it gets alone."""
+    from vitna_anchor_b200 import ops
+    from vitna_anchor_b200.engine.engine import Engine
+    from vitna_anchor_b200.engine.loading import write_random_model
+    cfg_json = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_act="silu", rms_norm_eps=1e-5,
+                    tie_word_embeddings=True, max_position_embeddings=1024, num_hidden_layers=2, hidden_size=128,
+                    intermediate_size=256, num_attention_heads=2, num_key_value_heads=1, head_dim=64, vocab_size=320,
+                    rope_theta=10000.0)
+    write_random_model(str(tmp_path / "m"), cfg_json, seed=3, std=0.1)
+    rng = np.random.default_rng(9)
+    short, long_ = [int(t) for t in rng.integers(0, 320, 12)], [int(t) for t in rng.integers(0, 320, 150)]
+    eng = Engine(str(tmp_path / "m"), dtype="bfloat16", parallel=2, max_batch_tokens=256)
+    want = eng.generate(short, max_new=20)
+    a = eng.add_request(short, max_new=20)
+    for _ in range(4):
+        eng.step()                                  # a is decoding
+    eng.flush()
+    b = eng.add_request(long_, max_new=5)
+    c = eng.add_request(short, max_new=20)          # waits: both slots are taken
+    ops.set_wait_limit_ms(5.0)
+    try:
+        ops.skip_stage_once("linear_tcgen05", 0)    # the next prompt-sized product: b's portion beside a's token
+        done = eng.step()
+        done += eng.flush()
+    finally:
+        ops.set_wait_limit_ms(0)
+    assert b.finish_reason == "error" and a.finish_reason == "error" and set(map(id, done)) == {id(a), id(b)}
+    assert a.output == want[:len(a.output)] and len(a.output) >= 4 and b.output == []
+    finished = eng.run()
+    assert [id(r) for r in finished] == [id(c)] and c.output == want and c.finish_reason == "length"
+    assert eng.runner.cache.free_pages() == [eng.runner.cache.tables.pools[0].num_pages]

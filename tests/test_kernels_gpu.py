@@ -581,3 +581,43 @@ def test_linear_tcgen05_rope_matches_the_separate_kernels(ops, nh, nkv, hd, ps, 
     assert (q_a.float() - q_b.float()).abs().max() <= t
     assert (cache_a.float() - cache_b.float()).abs().max() <= t
     assert torch.equal(cache_a == 7.0, cache_b == 7.0)
+
+
+@pytest.mark.parametrize("family,M,N,K,stage", [("linear_tcgen05", 300, 200, 576, 0), ("linear_tcgen05", 300, 200, 576, 5),
+                                                ("linear_tcgen05_wide", 1024, 2048, 2048, 1), ("linear_tcgen05_wide", 2048, 4096, 2048, 40)])
+def test_linear_tcgen05_gives_up_a_wait_and_says_so(ops, family, M, N, K, stage):
+    """The producer leaves one stage unarmed (a hook for this test; nothing faults): the waits on it run out after the
+    5 ms set here, every block returns by itself with its tensor memory freed, the error word is set, and the next
+    launch of the same kernel is right."""
+    torch.manual_seed(1)
+    x = torch.randn(M, K).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K) / math.sqrt(K)).to(torch.bfloat16).cuda()
+    want = x.double() @ w.double().T
+    out = torch.zeros(M, N, device="cuda")
+    ops.set_wait_limit_ms(5.0)
+    try:
+        ops.skip_stage_once(family, stage)
+        ops.linear_tcgen05(x, w, out, ops.LINEAR_F32)
+        torch.cuda.synchronize()
+        with pytest.raises(ops.KernelGaveUp):
+            ops.check_device_errors()
+    finally:
+        ops.set_wait_limit_ms(0)
+    ops.linear_tcgen05(x, w, out, ops.LINEAR_F32)          # the hook was for one launch
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    assert (out.double() - want).abs().max() <= 2e-5 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("stage", [0, 2])
+def test_attention_prefill_tcgen05_gives_up_a_wait_and_says_so(ops, stage):
+    """The same for the prompt attention: one step's keys never arrive; the tensor-core lane, the softmax warps and the
+    producer each give up within the limit, keep their appointments, and the block returns."""
+    ops.set_wait_limit_ms(5.0)
+    try:
+        ops.skip_stage_once("attention_prefill_tcgen05", stage)
+        with pytest.raises(ops.KernelGaveUp):
+            _prefill_case(ops, ops.attention_prefill_tcgen05, 128, 4, 2, 64, 16, 0, [300, 448], [300, 200])
+    finally:
+        ops.set_wait_limit_ms(0)
+    _prefill_case(ops, ops.attention_prefill_tcgen05, 128, 4, 2, 64, 16, 0, [300, 448], [300, 200])

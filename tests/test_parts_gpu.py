@@ -1,7 +1,8 @@
 """Each part alone against the plain function of the same name; a decoder whose schedule names a layer
-twice and lets a layer read another layer's cache; and toy parts defined here, registered, built and stepped
-with no change to the framework's files: a mixer with state of its own, a feed-forward with routing and a
-position encoding that adds learned rows."""
+twice and lets a layer read another layer's cache; and toy parts defined under tests/ (toy_archs.py), registered,
+built and stepped with no change to the framework's files: a mixer with state of its own, a feed-forward with
+routing and a position encoding that adds learned rows; through the step function, the Python entry point and
+the replay program, with the engine's default settings."""
 import json
 import math
 
@@ -15,37 +16,23 @@ pytestmark = pytest.mark.gpu
 
 
 def make_ctx(model_like_specs, segments, page_size=4, dtype=torch.float32, num_pages=64):
-    """A cache manager and the StepContext of one batch: segments = [(request id, first position, n tokens)]."""
+    """A cache manager and the StepContext of one batch, made by the step function's own builder:
+    segments = [(request id, first position, n tokens)].  ctx.extra["builder"] builds further batches on the same cache."""
     from vitna_anchor_b200.cache import CacheManager
-    from vitna_anchor_b200.parts.base import GroupMeta, StepContext, Workspace
+    from vitna_anchor_b200.engine.context import ContextBuilder
+    from vitna_anchor_b200.parts.base import Workspace
     cache = CacheManager(model_like_specs, page_size=page_size, num_pages=num_pages, max_requests=8, dtype=dtype, device="cuda")
-    T = sum(n for _, _, n in segments)
-    pos, seg, plan = [], [], []
-    for s, (rid, first, n) in enumerate(segments):
+    builder = ContextBuilder(cache, dtype, Workspace(torch.device("cuda"), 64), max_batch_tokens=64, max_segments=8,
+                             max_model_len=page_size * num_pages, device="cuda")
+    plan = []
+    for rid, first, n in segments:
         cache.open(rid)
         if first:
             cache.reserve_step([(rid, first)]); cache.commit_step([(rid, first)])
         plan.append((rid, n))
-        pos += list(range(first, first + n)); seg += [s] * n
     cache.reserve_step(plan)
-    maxb = max(len(cache.tables.get(rid).tables[0].blocks) for rid, _, _ in segments) if cache.groups else 1
-    groups = []
-    for g in range(len(cache.groups)):
-        bt = np.zeros((len(segments), maxb), np.int32)
-        sm = []
-        for s, (rid, first, n) in enumerate(segments):
-            blocks = cache.tables.get(rid).tables[g].blocks
-            bt[s, :len(blocks)] = blocks
-            sm += [blocks[p // page_size] * page_size + p % page_size for p in range(first, first + n)]
-        groups.append(GroupMeta(torch.tensor(sm, dtype=torch.int32, device="cuda"), torch.from_numpy(bt).cuda(), maxb))
-    starts = np.cumsum([0] + [n for _, _, n in segments]).astype(np.int32)
-    i32 = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device="cuda")
-    ctx = StepContext(num_tokens=T, num_segments=len(segments), dtype=dtype, tokens=i32([0] * T), positions=i32(pos),
-                      token_seg=i32(seg), seg_starts=i32(starts), seg_context=i32([f + n for _, f, n in segments]),
-                      seg_slots=i32([cache.slot(rid) for rid, _, _ in segments]), groups=groups, caches=cache.views,
-                      workspace=Workspace(torch.device("cuda"), 64), host_seg_lens=[n for _, _, n in segments],
-                      host_seg_first_pos=[f for _, f, _ in segments], host_seg_slots=[cache.slot(rid) for rid, _, _ in segments],
-                      max_seg_len=max(n for _, _, n in segments), max_context=max(f + n for _, f, n in segments))
+    ctx, _ = builder.build([(rid, [0] * n, []) for rid, _, n in segments])
+    ctx.extra["builder"] = builder
     return cache, ctx
 
 
@@ -109,19 +96,10 @@ def test_attention_part_in_two_steps(dtype, window):
     out1 = torch.zeros(9, H, device="cuda")
     part.forward(xa[:9].to(dtype).cuda(), ctx, ctx.caches[0], out1)
     cache.commit_step([("a", 9)])
-    # second step: build its context by hand on the same cache
-    from vitna_anchor_b200.parts.base import GroupMeta
+    # second step: five more tokens of "a" beside the seven of a new request, on the same cache
     cache.open("b")
     cache.reserve_step([("a", 5), ("b", 7)])
-    ps = cache.page_size
-    ta, tb = cache.tables.get("a").tables[0].blocks, cache.tables.get("b").tables[0].blocks
-    maxb = max(len(ta), len(tb))
-    bt = np.zeros((2, maxb), np.int32); bt[0, :len(ta)] = np.maximum(ta, 0); bt[1, :len(tb)] = tb
-    sm = [ta[p // ps] * ps + p % ps for p in range(9, 14)] + [tb[p // ps] * ps + p % ps for p in range(7)]
-    i32 = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device="cuda")
-    ctx.num_tokens, ctx.num_segments = 12, 2
-    ctx.positions, ctx.token_seg = i32(list(range(9, 14)) + list(range(7))), i32([0] * 5 + [1] * 7)
-    ctx.groups = [GroupMeta(i32(sm), torch.from_numpy(bt).cuda(), maxb)]
+    ctx, _ = ctx.extra["builder"].build([("a", [0] * 5, []), ("b", [0] * 7, [])])
     out2 = torch.zeros(12, H, device="cuda")
     part.forward(torch.cat([xa[9:], xb]).to(dtype).cuda(), ctx, ctx.caches[0], out2)
     got_a = torch.cat([out1, out2[:5]]).cpu().numpy()
@@ -141,7 +119,7 @@ def _tiny_llama_weights(model_dir):
 def test_schedule_names_a_layer_twice_and_shares_a_cache(tiny_dirs):
     """Blocks 0, 1, 0 of tinyA run in that order, each run with a cache of its own: against the plain
     implementation told the same order.  Then a schedule whose last run reads the first run's cache
-    without writing it is built and stepped (it has no plain counterpart; it must differ from the other)."""
+    without writing it, whole and in two steps: against the plain implementation told the same."""
     from vitna_anchor_b200.models.decoder import DecoderModel, LayerRun
     from vitna_anchor_b200.models.llama import build_llama
     from vitna_anchor_b200.engine.runner import ModelRunner, StepEntry
@@ -167,88 +145,38 @@ def test_schedule_names_a_layer_twice_and_shares_a_cache(tiny_dirs):
     runner2 = ModelRunner(shared, page_size=4, num_pages=32, max_requests=2, max_batch_tokens=32)
     runner2.open("r")
     c = runner2.step([StepEntry("r", ids, range(len(ids)))]).cpu().numpy()
-    assert np.isfinite(c).all() and np.abs(c - want).max() > 1e-3
+    want_shared = P.forward(pc, pw, ids, layer_order=[0, 1, 0], reads={2: 0})
+    assert np.abs(want_shared - want).max() > 1e-3            # sharing the cache does change the logits
+    assert np.abs(c - want_shared).max() <= 2e-5 * max(1.0, np.abs(want_shared).max())
+    runner2.open("s")
+    d = np.concatenate([runner2.step([StepEntry("s", ids[:4], range(4))]).cpu().numpy(),
+                        runner2.step([StepEntry("s", ids[4:], range(7))]).cpu().numpy()])
+    assert np.abs(d - want_shared).max() <= 2e-5 * max(1.0, np.abs(want_shared).max())
     with pytest.raises(ValueError):
         with_schedule([LayerRun(0, 0), LayerRun(1, 0)])          # two writers of one cache layer
 
 
 def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     """A made-up architecture whose mixer keeps a running mean of its inputs per request in the request's
-    state slot.  Everything it needs is defined here; the framework's files are not touched."""
-    from vitna_anchor_b200 import ops
-    from vitna_anchor_b200.cache import StateSpec
-    from vitna_anchor_b200.config import Architecture, register_architecture
-    from vitna_anchor_b200.engine.loading import load_model, write_random_model
-    from vitna_anchor_b200.engine.runner import ModelRunner, StepEntry
-    from vitna_anchor_b200.models.decoder import DecoderModel, LayerRun
-    from vitna_anchor_b200.parts import Mixer, make_part, register_part
-    from vitna_anchor_b200.parts.embedding import Embedding, LMHead
-    from vitna_anchor_b200.weights import WeightSpec
-
-    class RunningMean(Mixer):
-        """state = (sum of inputs so far [H], count); output_t = W (sum_t / count_t)."""
-
-        def __init__(self, hidden, w):
-            self.hidden, self.w = hidden, w
-
-        def tensors(self):
-            return [self.w]
-
-        def cache_spec(self):
-            return StateSpec((self.hidden + 1,), torch.float32)
-
-        def forward(self, xn, ctx, cache, residual, write_cache=True):
-            start = 0
-            outs = []
-            for n, slot in zip(ctx.host_seg_lens, ctx.host_seg_slots):
-                st = cache.state[slot]
-                x = xn[start:start + n].float()
-                sums = st[:self.hidden] + torch.cumsum(x, 0)
-                counts = st[self.hidden] + torch.arange(1, n + 1, device=x.device)
-                outs.append(sums / counts[:, None])
-                st[:self.hidden] = sums[-1]; st[self.hidden] = counts[-1]
-                start += n
-            mean = torch.cat(outs).to(xn.dtype).contiguous()
-            ops.linear(mean, self.w, residual, ops.LINEAR_ACC_F32)
-
-    register_part("mixer", "toy_running_mean", RunningMean)
-
-    def parse(cj):
-        return dict(H=cj["hidden_size"], V=cj["vocab_size"], L=cj["num_hidden_layers"], I=cj["intermediate_size"])
-
-    def manifest(c):
-        m = [WeightSpec("embed.weight", (c["V"], c["H"])), WeightSpec("norm.weight", (c["H"],))]
-        for l in range(c["L"]):
-            m += [WeightSpec(f"layers.{l}.mix.weight", (c["H"], c["H"])), WeightSpec(f"layers.{l}.norm1.weight", (c["H"],)),
-                  WeightSpec(f"layers.{l}.norm2.weight", (c["H"],)), WeightSpec(f"layers.{l}.gate_up.weight", (2 * c["I"], c["H"])),
-                  WeightSpec(f"layers.{l}.down.weight", (c["H"], c["I"]))]
-        return m
-
-    def build(c, w, dtype, device):
-        d = lambda n: w[n].to(device=device, dtype=dtype)
-        f = lambda n: w[n].to(device=device, dtype=torch.float32)
-        blocks = [make_part("block", "pre_norm",
-                            mixer_norm=make_part("norm", "rmsnorm", width=c["H"], eps=1e-5, weight=f(f"layers.{l}.norm1.weight")),
-                            mixer=make_part("mixer", "toy_running_mean", hidden=c["H"], w=d(f"layers.{l}.mix.weight")),
-                            ffn_norm=make_part("norm", "rmsnorm", width=c["H"], eps=1e-5, weight=f(f"layers.{l}.norm2.weight")),
-                            ffn=make_part("feed_forward", "swiglu", hidden=c["H"], intermediate=c["I"],
-                                          w_gate_up=d(f"layers.{l}.gate_up.weight"), w_down=d(f"layers.{l}.down.weight")))
-                  for l in range(c["L"])]
-        emb = Embedding(c["V"], c["H"], d("embed.weight"))
-        return DecoderModel(embedding=emb, blocks=blocks, schedule=[LayerRun(l, l) for l in range(c["L"])],
-                            final_norm=make_part("norm", "rmsnorm", width=c["H"], eps=1e-5, weight=f("norm.weight")),
-                            lm_head=LMHead(c["V"], c["H"], emb.table), position=None, dtype=dtype, vocab_size=c["V"], max_positions=512)
-
-    register_architecture(Architecture("ToyRunningMeanLM", parse, manifest, build, lambda n: "norm" in n), replace=True)
-    cj = dict(architectures=["ToyRunningMeanLM"], hidden_size=24, vocab_size=50, num_hidden_layers=2, intermediate_size=40)
-    write_random_model(str(tmp_path / "toy"), cj, 3, std=0.3)
-    json.dump(cj, open(tmp_path / "toy" / "config.json", "w"))
-    model = load_model(str(tmp_path / "toy"), "float32")
+    state slot (tests/toy_archs.py; the framework's files are not touched).  With the engine's default settings:
+    the model says it is not capture-safe, so nothing is captured; cut and batched in different ways, and with
+    steps repeated many times, the logits are those of the plain statement; a slot that is taken again starts
+    from zero; a step that fails after the mixer wrote its state leaves no trace; the state cannot be truncated."""
+    import toy_archs as T
+    from vitna_anchor_b200.cache import CacheError, StateSpec
+    from vitna_anchor_b200.engine.loading import load_model
+    from vitna_anchor_b200.engine.runner import ModelRunner, StepEntry, StepFailed
+    model_dir = T.write_toy(str(tmp_path / "toy"), T.RUNNING_MEAN_CONFIG, 3, 0.3)
+    model = load_model(model_dir, "float32")
     assert model.cache_specs() == [StateSpec((25,), torch.float32)] * 2
+    assert not model.capture_safe
+    a, b = [3, 1, 4, 1, 5, 9, 2, 6, 5, 3, 5, 8, 9, 7, 9, 3, 2, 3, 8, 4, 6, 2], [2, 7, 1, 8, 2, 8, 1, 8, 2, 8, 4, 5]
+    want_a, want_b = T.plain_running_mean(model_dir, a), T.plain_running_mean(model_dir, b)
+    tol = 2e-5 * max(1.0, np.abs(want_a).max(), np.abs(want_b).max())
 
     def run(cuts_a, cuts_b):
-        runner = ModelRunner(model, page_size=4, num_pages=4, max_requests=2, max_batch_tokens=32, cuda_graphs=False)
-        a, b = [3, 1, 4, 1, 5, 9, 2, 6, 5, 3], [2, 7, 1, 8, 2, 8]
+        runner = ModelRunner(model, page_size=4, num_pages=4, max_requests=2, max_batch_tokens=32)
+        assert not runner.cuda_graphs
         runner.open("a"); runner.open("b")
         rows = {"a": [], "b": []}
         pa = pb = 0
@@ -263,137 +191,90 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
         runner.open("c")                       # takes a's slot: the state must start from zero again
         c = runner.step([StepEntry("c", a, range(len(a)))]).cpu().numpy()
         return np.concatenate(rows["a"]), np.concatenate(rows["b"]), c
-    a1, b1, c1 = run([10, 0], [0, 6])
-    a2, b2, c2 = run([3, 2, 5], [1, 3, 2])
-    assert np.abs(a1 - a2).max() < 1e-5 and np.abs(b1 - b2).max() < 1e-5
-    assert np.abs(c1 - a1).max() < 1e-5 and np.abs(c2 - a1).max() < 1e-5
+    a1, b1, c1 = run([22, 0], [0, 12])
+    # portions, then the same counts step after step (what a captured graph would replay)
+    a2, b2, c2 = run([3, 2, 5] + [1] * 12, [1, 3, 2] + [1] * 6 + [0] * 6)
+    for got_a, got_b, got_c in ((a1, b1, c1), (a2, b2, c2)):
+        assert np.abs(got_a - want_a).max() <= tol and np.abs(got_b - want_b).max() <= tol and np.abs(got_c - want_a).max() <= tol
     assert np.abs(a1[1:] - a1[:-1]).max() > 1e-3          # the state does change the output from token to token
+
+    # a step that raises after the first layer's mixer wrote its state: the state is put back, and the same
+    # step again gives what it gives without the failure
+    runner = ModelRunner(model, page_size=4, num_pages=4, max_requests=2, max_batch_tokens=32)
+    runner.open("a")
+    first = runner.step([StepEntry("a", a[:6], range(6))]).cpu().numpy()
+    runner.fail_after_run_once(0)
+    with pytest.raises(StepFailed):
+        runner.step([StepEntry("a", a[6:11], range(5))])
+    assert runner.length("a") == 6
+    again = runner.step([StepEntry("a", a[6:11], range(5))]).cpu().numpy()
+    assert np.abs(np.concatenate([first, again]) - want_a[:11]).max() <= tol
+    with pytest.raises(CacheError):
+        runner.cache.truncate("a", 4)                     # a running mean cannot be taken back
+
+
+def test_toy_architectures_through_the_entry_point_and_the_replay_program(tmp_path, monkeypatch):
+    """The state mixer and the learned positions through Engine.generate (default settings) and through bin/trace_run
+    as a child process that learns the architectures from VITNA_ANCHOR_PLUGINS: greedy tokens and logits against
+    the plain statements.  The capture-safe toy is replayed from graphs; the other is never captured."""
+    import toy_archs as T
+    from replay_util import Replay, changing_portions, tail_one_by_one, whole
+    from vitna_anchor_b200.engine.engine import Engine
+    rm_dir = T.write_toy(str(tmp_path / "rm"), T.RUNNING_MEAN_CONFIG, 3, 0.3)
+    lp_dir = T.write_toy(str(tmp_path / "lp"), dict(T.LEARNED_CONFIG, architectures=["ToyLearnedLM"]), 11, 0.25)
+    rng = np.random.default_rng(8)
+
+    def plain_greedy(fn, prompt, n):
+        ids, rows = list(prompt), []
+        for _ in range(n):
+            rows.append(fn(ids)[-1]); ids.append(int(np.argmax(rows[-1])))
+        return ids[len(prompt):], np.stack(rows)
+
+    for model_dir, fn, vocab, captured in ((rm_dir, lambda ids: T.plain_running_mean(rm_dir, ids), 50, False),
+                                           (lp_dir, lambda ids: T.plain_learned(lp_dir, ids, False)[0], 61, True)):
+        prompts = [[int(t) for t in rng.integers(0, vocab, n)] for n in (7, 19, 3)]
+        eng = Engine(model_dir, dtype="float32", kv_block=4, parallel=3, max_batch_tokens=16)
+        assert eng.runner.cuda_graphs == captured
+        out_file = str(tmp_path / "rows.f32")
+        got = eng.generate(prompts, max_new=24, logits_out=out_file)
+        want0, rows0 = plain_greedy(fn, prompts[0], 24)
+        mine = np.fromfile(out_file, "<f4").reshape(24, vocab)
+        assert got[0] == want0 and np.abs(mine - rows0).max() <= 2e-5 * max(1.0, np.abs(rows0).max())
+        for p, g in zip(prompts[1:], got[1:]):
+            assert g == plain_greedy(fn, p, 24)[0]
+        assert (eng.runner.graph_replays > 10) == captured
+        # the replay program, as a child process
+        ids = [int(t) for t in rng.integers(0, vocab, 60)]
+        want = fn(ids)
+        replay = Replay(model_dir, "float32", tmp_path / f"out{int(captured)}", 128, kv_block=4, plugins="toy_archs")
+        try:
+            for steps in (whole("w", ids), tail_one_by_one("t", ids), changing_portions("c", ids)):
+                got_rows = replay.run(steps, vocab)
+                assert len(got_rows) == len(ids)
+                worst = max(float(np.abs(row - want[pos]).max()) for (_, pos), row in got_rows.items())
+                assert worst <= 2e-5 * max(1.0, np.abs(want).max())
+        finally:
+            replay.close()
 
 
 def test_toy_routed_feed_forward_and_learned_positions(tmp_path):
-    """A made-up architecture with two more kinds of parts defined here and nowhere in the framework: a position
-    encoding that adds a learned row per position to the embeddings (the attention then rotates nothing), and a
-    feed-forward with routing (a float32 router picks one of three SwiGLU experts per token and weighs it by its
-    softmax probability).  Whole prompts, cut prompts and decoding agree with a plain statement of the same model."""
-    from vitna_anchor_b200 import ops
-    from vitna_anchor_b200.config import Architecture, register_architecture
-    from vitna_anchor_b200.engine.loading import load_model, write_random_model
+    """A made-up architecture with two more kinds of parts defined under tests/ and nowhere in the framework: a
+    position encoding that adds a learned row per position to the embeddings (the attention then rotates nothing),
+    and a feed-forward with routing (a float32 router picks one of three SwiGLU experts per token and weighs it by its
+    softmax probability).  Whole prompts, cut prompts and decoding, with the engine's default settings, agree with a
+    plain statement of the same model."""
+    import toy_archs as T
+    from vitna_anchor_b200.engine.loading import load_model
     from vitna_anchor_b200.engine.runner import ModelRunner, StepEntry
-    from vitna_anchor_b200.models.decoder import DecoderModel, LayerRun
-    from vitna_anchor_b200.parts import FeedForward, PositionEncoding, make_part, register_part
-    from vitna_anchor_b200.parts.embedding import Embedding, LMHead
-    from vitna_anchor_b200.weights import WeightSpec
-
-    class LearnedPositions(PositionEncoding):
-        def __init__(self, table):
-            self.table = table                      # float32 [max_positions, hidden]
-
-        def tensors(self):
-            return [self.table]
-
-        def on_embeddings(self, x, ctx):
-            x += self.table[ctx.positions.long()]
-
-    class Top1Experts(FeedForward):
-        def __init__(self, hidden, inter, router, gate_up, down):
-            self.hidden, self.inter, self.router, self.gate_up, self.down = hidden, inter, router, gate_up, down
-
-        def tensors(self):
-            return [self.router] + self.gate_up + self.down
-
-        def forward(self, xn, ctx, residual, norm=None):
-            logits = xn.float() @ self.router.t()                       # router logits in float32
-            prob = torch.softmax(logits, dim=-1)
-            pick = torch.argmax(logits, dim=-1)                         # the lowest id among equal maxima
-            for e in range(len(self.gate_up)):
-                idx = torch.nonzero(pick == e).flatten()
-                if idx.numel() == 0:
-                    continue
-                xe = xn[idx].contiguous()
-                gu = torch.empty(idx.numel(), 2 * self.inter, dtype=xn.dtype, device=xn.device)
-                ops.linear(xe, self.gate_up[e], gu, ops.LINEAR_SAME)
-                act = torch.empty(idx.numel(), self.inter, dtype=xn.dtype, device=xn.device)
-                ops.silu_mul(gu, act)
-                y = torch.empty(idx.numel(), self.hidden, dtype=torch.float32, device=xn.device)
-                ops.linear(act, self.down[e], y, ops.LINEAR_F32)
-                residual.index_add_(0, idx, y * prob[idx, e][:, None])
-
-    register_part("position", "toy_learned", LearnedPositions)
-    register_part("feed_forward", "toy_top1_experts", Top1Experts)
-    E = 3
-
-    def parse(cj):
-        return dict(H=cj["hidden_size"], V=cj["vocab_size"], L=cj["num_hidden_layers"], I=cj["intermediate_size"],
-                    nh=cj["num_attention_heads"], nkv=cj["num_key_value_heads"], hd=cj["head_dim"], P=cj["max_position_embeddings"])
-
-    def manifest(c):
-        m = [WeightSpec("embed.weight", (c["V"], c["H"])), WeightSpec("positions.weight", (c["P"], c["H"])), WeightSpec("norm.weight", (c["H"],))]
-        for l in range(c["L"]):
-            p = f"layers.{l}."
-            m += [WeightSpec(p + "qkv.weight", ((c["nh"] + 2 * c["nkv"]) * c["hd"], c["H"])), WeightSpec(p + "o.weight", (c["H"], c["nh"] * c["hd"])),
-                  WeightSpec(p + "norm1.weight", (c["H"],)), WeightSpec(p + "norm2.weight", (c["H"],)), WeightSpec(p + "router.weight", (E, c["H"]))]
-            for e in range(E):
-                m += [WeightSpec(p + f"experts.{e}.gate_up.weight", (2 * c["I"], c["H"])), WeightSpec(p + f"experts.{e}.down.weight", (c["H"], c["I"]))]
-        return m
-
-    def build(c, w, dtype, device):
-        d = lambda n: w[n].to(device=device, dtype=dtype).contiguous()
-        f = lambda n: w[n].to(device=device, dtype=torch.float32)
-        position = make_part("position", "toy_learned", table=f("positions.weight"))
-        blocks = []
-        for l in range(c["L"]):
-            p = f"layers.{l}."
-            blocks.append(make_part(
-                "block", "pre_norm",
-                mixer_norm=make_part("norm", "rmsnorm", width=c["H"], eps=1e-5, weight=f(p + "norm1.weight")),
-                mixer=make_part("mixer", "attention", hidden=c["H"], num_heads=c["nh"], num_kv_heads=c["nkv"], head_dim=c["hd"],
-                                wqkv=d(p + "qkv.weight"), wo=d(p + "o.weight"), position=position),
-                ffn_norm=make_part("norm", "rmsnorm", width=c["H"], eps=1e-5, weight=f(p + "norm2.weight")),
-                ffn=make_part("feed_forward", "toy_top1_experts", hidden=c["H"], inter=c["I"], router=f(p + "router.weight"),
-                              gate_up=[d(p + f"experts.{e}.gate_up.weight") for e in range(E)],
-                              down=[d(p + f"experts.{e}.down.weight") for e in range(E)])))
-        emb = Embedding(c["V"], c["H"], d("embed.weight"))
-        return DecoderModel(embedding=emb, blocks=blocks, schedule=[LayerRun(l, l) for l in range(c["L"])],
-                            final_norm=make_part("norm", "rmsnorm", width=c["H"], eps=1e-5, weight=f("norm.weight")),
-                            lm_head=LMHead(c["V"], c["H"], emb.table), position=position, dtype=dtype, vocab_size=c["V"],
-                            max_positions=c["P"])
-
-    register_architecture(Architecture("ToyRoutedLM", parse, manifest, build, lambda n: "norm" in n), replace=True)
-    cj = dict(architectures=["ToyRoutedLM"], hidden_size=40, vocab_size=61, num_hidden_layers=2, intermediate_size=24,
-              num_attention_heads=4, num_key_value_heads=2, head_dim=12, max_position_embeddings=64)
-    write_random_model(str(tmp_path / "toy"), cj, 11, std=0.25)
-    json.dump(cj, open(tmp_path / "toy" / "config.json", "w"))
-    model = load_model(str(tmp_path / "toy"), "float32")
+    model_dir = T.write_toy(str(tmp_path / "toy"), dict(T.LEARNED_CONFIG, architectures=["ToyRoutedLM"]), 11, 0.25)
+    model = load_model(model_dir, "float32")
+    assert not model.capture_safe                                      # the routing reads its picks on the host
     ids = [3, 14, 15, 9, 26, 5, 35, 8, 9, 7, 9, 32, 38, 46, 26, 43, 38, 32, 7, 9, 50, 28, 8]
-
-    # the plain statement of this model, from the plain functions of the parts
-    W = {k: v.astype(np.float32) for k, v in P.read_safetensors(str(tmp_path / "toy" / "model.safetensors")).items()}
-    c = parse(cj)
-    x = P.embed(W["embed.weight"], ids) + W["positions.weight"][:len(ids)]
-    picks = []
-    for l in range(c["L"]):
-        p = f"layers.{l}."
-        xn = P.rms_norm(x, W[p + "norm1.weight"], 1e-5)
-        qkv = P.linear(xn, W[p + "qkv.weight"])
-        qd, kd = c["nh"] * c["hd"], c["nkv"] * c["hd"]
-        q = qkv[:, :qd].reshape(-1, c["nh"], c["hd"]); k = qkv[:, qd:qd + kd].reshape(-1, c["nkv"], c["hd"]); v = qkv[:, qd + kd:].reshape(-1, c["nkv"], c["hd"])
-        x = x + P.linear(P.causal_attention(q, k, v), W[p + "o.weight"])
-        xn = P.rms_norm(x, W[p + "norm2.weight"], 1e-5)
-        logits = P.linear(xn, W[p + "router.weight"])
-        prob = np.exp(logits - logits.max(-1, keepdims=True)); prob /= prob.sum(-1, keepdims=True)
-        pick = logits.argmax(-1)
-        picks.append(pick)
-        y = np.zeros_like(x)
-        for t in range(len(ids)):
-            e = int(pick[t])
-            gu = W[p + f"experts.{e}.gate_up.weight"]
-            y[t] = P.swiglu(xn[t:t + 1], gu[:c["I"]], gu[c["I"]:], W[p + f"experts.{e}.down.weight"])[0] * prob[t, e]
-        x = x + y
-    want = P.linear(P.rms_norm(x, W["norm.weight"], 1e-5), W["embed.weight"])
+    want, picks = T.plain_learned(model_dir, ids, True)
     assert all(len(set(pk.tolist())) > 1 for pk in picks)              # the router does send tokens to different experts
 
     def run(cuts):
-        runner = ModelRunner(model, page_size=4, num_pages=8, max_requests=2, max_batch_tokens=32, cuda_graphs=False)
+        runner = ModelRunner(model, page_size=4, num_pages=8, max_requests=2, max_batch_tokens=32)
         runner.open("a")
         rows, at = [], 0
         for n in cuts:
@@ -406,7 +287,7 @@ def test_toy_routed_feed_forward_and_learned_positions(tmp_path):
     assert np.abs(whole - want).max() <= 2e-5 * scale
     assert np.abs(cut - want).max() <= 2e-5 * scale
     # the same token at another position gives other logits: the learned rows are added
-    runner = ModelRunner(model, page_size=4, num_pages=8, max_requests=2, max_batch_tokens=32, cuda_graphs=False)
+    runner = ModelRunner(model, page_size=4, num_pages=8, max_requests=2, max_batch_tokens=32)
     runner.open("b")
     moved = runner.step([StepEntry("b", ids[1:2], [0])]).cpu().numpy()   # token ids[1] at position 0 instead of 1
     assert np.abs(moved[0] - whole[1]).max() > 1e-3

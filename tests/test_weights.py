@@ -64,6 +64,22 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path, tiny_dirs
     assert "missing tensors (2)" in msg and "unexpected tensors (1)" in msg and "wrong shapes (1)" in msg
 
 
+def test_extra_tensors_alone_load_with_a_warning(tmp_path, tiny_dirs):
+    """The reference binds by name and ignores the rest (engine/src/model.c:265-283): an old export's
+    rotary_emb.inv_freq buffer must not refuse the checkpoint."""
+    src = SafetensorsFile(os.path.join(tiny_dirs["tinyB"], "model.safetensors"))
+    tensors = {n: src.read(n) for n in src.names()}
+    src.close()
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(16)
+    d = tmp_path / "extra"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(TINY_B["config"]))
+    write_safetensors(str(d / "model.safetensors"), tensors)
+    with pytest.warns(UserWarning, match="rotary_emb.inv_freq"):
+        got = load_weights(str(d), _manifest(str(d)))
+    assert "model.layers.0.self_attn.rotary_emb.inv_freq" not in got and len(got) == len(tensors) - 1
+
+
 def test_malformed_files_are_refused(tmp_path):
     p = tmp_path / "model.safetensors"
     p.write_bytes(b"\x01\x02")

@@ -10,4 +10,18 @@ from .config import registry as _registry
 
 _registry._register_builtin()
 
+
+def _load_plugins() -> None:
+    """Modules named in VITNA_ANCHOR_PLUGINS (comma-separated, importable names) are imported once the built-in
+    parts and architectures are registered.  A module registers its own parts and architectures when imported
+    (register_part, register_architecture), which is how the command line and the replay program come to know
+    an architecture that is defined outside this package."""
+    import importlib
+    import os
+    for name in filter(None, (n.strip() for n in os.environ.get("VITNA_ANCHOR_PLUGINS", "").split(","))):
+        importlib.import_module(name)
+
+
+_load_plugins()
+
 __version__ = "0.1.0"

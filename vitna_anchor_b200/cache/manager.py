@@ -134,7 +134,35 @@ class CacheManager:
             self.tables.rollback(rid)
 
     def truncate(self, request_id: Hashable, length: int) -> None:
+        """Forget positions >= length.  A fixed-size state cannot be taken back to an earlier position (it has to
+        be computed again from the start), so a model with such a state refuses anything but the current length."""
+        if self.has_state and length != self.length(request_id):
+            raise CacheError("a request with a fixed-size state cannot be truncated; close it and run it again")
         self.tables.truncate(request_id, length)
+
+    def rewind(self, request_id: Hashable, length: int) -> None:
+        """truncate() for the step function's own undoing of steps, which restores the states itself."""
+        self.tables.truncate(request_id, length)
+
+    # -- fixed-size states across a step --------------------------------------------------------
+    @property
+    def has_state(self) -> bool:
+        return any(v.state is not None for v in self.views)
+
+    def save_states(self, request_ids: Sequence[Hashable]):
+        """Copies of the state rows of these requests (None when no cache layer has a state): what restore_states
+        needs to undo a step that wrote them."""
+        if not self.has_state:
+            return None
+        slots = torch.tensor([self.tables.get(r).slot for r in request_ids], dtype=torch.long, device=self.device)
+        return slots, [(cid, v.state.index_select(0, slots)) for cid, v in enumerate(self.views) if v.state is not None]
+
+    def restore_states(self, saved) -> None:
+        if saved is None:
+            return
+        slots, rows = saved
+        for cid, copy in rows:
+            self.views[cid].state.index_copy_(0, slots, copy)
 
     def free_pages(self) -> List[int]:
         return [p.free_pages for p in self.tables.pools]

@@ -3,6 +3,7 @@
     vitna-anchor generate --model <dir> (--ids a,b,... | --ids-file f) [--max-new n] [--greedy |
                  --temperature t [--top-k k] [--top-p p] [--seed s]] [--logits-out file] [--timing]
                  [--ctx n] [--parallel n] [--stop-at-special] [--device cuda] [--dtype bfloat16|float32]
+                 [--kv-block n] [--num-pages n] [--max-batch-tokens n] [--max-prompt-portion n]
     vitna-anchor logits   --model <dir> (--ids ... | --ids-file f) --out file [--ctx n] [--dtype ...]
     vitna-anchor random-model --config file.json --seed s --out <dir> [--std x] [--norm-noise x] [--weights-dtype ...]
     vitna-anchor info     --model <dir>
@@ -20,7 +21,7 @@ from typing import List, Optional
 
 VALUE_OPTIONS = {"--model", "--ids", "--ids-file", "--max-new", "--temperature", "--top-k", "--top-p", "--seed", "--logits-out",
                  "--out", "--ctx", "--device", "--dtype", "--parallel", "--kv-block", "--num-pages", "--max-batch-tokens",
-                 "--config", "--std", "--norm-noise", "--weights-dtype"}
+                 "--max-prompt-portion", "--config", "--std", "--norm-noise", "--weights-dtype"}
 FLAG_OPTIONS = {"--greedy", "--timing", "--stop-at-special"}
 COMMANDS = ("generate", "logits", "random-model", "info")
 
@@ -46,7 +47,7 @@ def parse_args(argv: List[str]) -> dict:
         else:
             raise UsageError(f"Unknown or incomplete option: {k}")
     try:
-        for key in ("max_new", "top_k", "seed", "ctx", "parallel", "kv_block", "num_pages", "max_batch_tokens"):
+        for key in ("max_new", "top_k", "seed", "ctx", "parallel", "kv_block", "num_pages", "max_batch_tokens", "max_prompt_portion"):
             if key in a:
                 a[key] = int(a[key])
         for key in ("temperature", "top_p", "std", "norm_noise"):
@@ -84,7 +85,7 @@ def make_engine(a: dict):
         raise UsageError(f"--device is cuda; this engine has no path for {a['device']}")
     kw = {}
     for key, name in (("ctx", "ctx"), ("parallel", "parallel"), ("kv_block", "kv_block"), ("num_pages", "num_pages"),
-                      ("max_batch_tokens", "max_batch_tokens")):
+                      ("max_batch_tokens", "max_batch_tokens"), ("max_prompt_portion", "max_prompt_portion")):
         if key in a:
             kw[name] = a[key]
     kw.setdefault("parallel", 1)

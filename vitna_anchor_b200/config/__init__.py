@@ -1,2 +1,3 @@
-from .llama import ConfigError, LlamaConfig, read_config_json  # noqa: F401
+from .errors import ConfigError  # noqa: F401
+from .llama import LlamaConfig, read_config_json  # noqa: F401
 from .registry import Architecture, architectures, register_architecture, resolve  # noqa: F401

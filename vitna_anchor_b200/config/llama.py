@@ -16,9 +16,7 @@ import os
 from dataclasses import dataclass, asdict
 from typing import Any, Mapping, Optional
 
-
-class ConfigError(ValueError):
-    """config.json is missing, malformed, or asks for what the engine lacks."""
+from .errors import ConfigError
 
 
 def _size(cfg: Mapping[str, Any], key: str, required: bool, default: Optional[int] = None) -> Optional[int]:

@@ -11,7 +11,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any, Callable, Dict, List, Mapping
 
-from .llama import ConfigError
+from .errors import ConfigError
 
 
 @dataclass(frozen=True)

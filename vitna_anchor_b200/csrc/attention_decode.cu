@@ -56,7 +56,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
 
     const int pos = positions[t];
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int first_split = lo / DEC_SPLIT, last_split = pos / DEC_SPLIT;
+    // A position beyond the grid's reach (the caller broke its promise on grid_context) loses its far keys, but the
+    // count below then still names launched blocks only, so the counters return to zero and no later launch is hurt.
+    const int first_split = lo / DEC_SPLIT, last_split = min(pos / DEC_SPLIT, (int)gridDim.x - 1);
     if (split < first_split || split > last_split) return;
     const int n_active = last_split - first_split + 1;
     const int k0 = split * DEC_SPLIT;

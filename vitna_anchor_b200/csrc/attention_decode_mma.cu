@@ -75,7 +75,7 @@ __device__ __forceinline__ DmItem dm_item(const DmArgs& a, int zi, int y, int sp
     it.pos = a.positions[it.t];
     it.lo = (a.window > 0 && it.pos - a.window + 1 > 0) ? it.pos - a.window + 1 : 0;
     it.first_split = it.lo / DM_SPLIT;
-    it.last_split = it.pos / DM_SPLIT;
+    it.last_split = min(it.pos / DM_SPLIT, (int)gridDim.x - 1);     // see attention_decode.cu: only launched blocks are counted
     it.active = split >= it.first_split && split <= it.last_split;
     it.n_active = it.last_split - it.first_split + 1;
     it.k0 = split * DM_SPLIT;

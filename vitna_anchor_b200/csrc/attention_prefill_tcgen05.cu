@@ -23,8 +23,8 @@
 // A row's result does not depend on what else is in the batch: its keys are walked in 64s from absolute position
 // 0 (or the window's first tile), and every decision above is the row's own.
 //
-// Every wait on an mbarrier is bounded: after about a second the waiter sets *error (a word the host reads),
-// the block stops, and its tensor memory is freed.
+// Every wait on an mbarrier is bounded: after the launch's limit (about a second unless the host set another) the
+// waiter sets *error (a word the host reads), the block stops, and its tensor memory is freed.
 //
 // tiles [n_tiles][4] int32: first token (flat index), rows (1..128), position of the first token, segment.
 #include "tcgen05_common.cuh"
@@ -50,7 +50,7 @@ template <int HD>
 __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const int32_t* __restrict__ block_tables,
     const int32_t* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int max_blocks, float scale,
-    int window, int* error) {
+    int window, const WaitCtl wc) {
     static_assert(HD == 64, "one 128-byte row per key");
     constexpr int STAGES = AT_STAGES;
     constexpr uint32_t Q_BYTES = AT_BM * HD * 2, KV_BYTES = AT_BN * HD * 2, P_BYTES = AT_BM * AT_BN * 2;
@@ -125,15 +125,17 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
             const int off = (key0 + lane * box_rows) % page_size;
             const uint32_t dst = s * KV_BYTES + lane * box_rows * (HD * 2);
             if (i >= STAGES) {
-                const bool ok = mbar_wait(&k_empty[s], ((i / STAGES) - 1) & 1);
-                if (!__all_sync(0xffffffffu, ok)) { if (lane == 0) give_up(error, &failed, 11); break; }
+                const bool ok = mbar_wait(&k_empty[s], ((i / STAGES) - 1) & 1, wc.cycles);
+                if (!__all_sync(0xffffffffu, ok)) { if (lane == 0) give_up(wc.error, &failed, 11); break; }
             }
-            if (lane == 0) mbar_expect_tx(&k_full[s], (uint32_t)nb * box_rows * HD * 2);
-            __syncwarp();
-            if (lane < nb) tma_load_2d(smem + K_OFF + dst, &map_kv, 0, (page * 2 * nkv + kvh) * page_size + off, &k_full[s]);
+            if (i != wc.skip_stage) {          // (a step named by wc.skip_stage gets no keys: a test of the give-up path)
+                if (lane == 0) mbar_expect_tx(&k_full[s], (uint32_t)nb * box_rows * HD * 2);
+                __syncwarp();
+                if (lane < nb) tma_load_2d(smem + K_OFF + dst, &map_kv, 0, (page * 2 * nkv + kvh) * page_size + off, &k_full[s]);
+            }
             if (i >= STAGES) {
-                const bool ok = mbar_wait(&v_empty[s], ((i / STAGES) - 1) & 1);
-                if (!__all_sync(0xffffffffu, ok)) { if (lane == 0) give_up(error, &failed, 19); break; }
+                const bool ok = mbar_wait(&v_empty[s], ((i / STAGES) - 1) & 1, wc.cycles);
+                if (!__all_sync(0xffffffffu, ok)) { if (lane == 0) give_up(wc.error, &failed, 19); break; }
             }
             if (lane == 0) mbar_expect_tx(&v_full[s], (uint32_t)nb * box_rows * HD * 2);
             __syncwarp();
@@ -148,7 +150,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
             const uint32_t q_addr = smem_u32(smem), ph_addr = smem_u32(smem + PH_OFF), pl_addr = smem_u32(smem + PL_OFF);
             auto scores = [&](int i) -> bool {        // S[i & 1] = Q K_i^T
                 const int s = i % STAGES;
-                if (!mbar_wait(&k_full[s], (i / STAGES) & 1)) { give_up(error, &failed, 13); return false; }
+                if (!mbar_wait(&k_full[s], (i / STAGES) & 1, wc.cycles)) { give_up(wc.error, &failed, 13); return false; }
                 tc_fence_after();
                 const uint32_t k_addr = smem_u32(smem + K_OFF + s * KV_BYTES);
 #pragma unroll
@@ -158,14 +160,14 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
                 umma_commit(&k_empty[s]);               // the keys' stage is free once these instructions have read it
                 return true;
             };
-            bool ok = mbar_wait(q_full, 0);
-            if (!ok) give_up(error, &failed, 12);
+            bool ok = mbar_wait(q_full, 0, wc.cycles);
+            if (!ok) give_up(wc.error, &failed, 12);
             ok = ok && scores(0);
             for (int i = 0; i < n_it && ok; i++) {
                 // the next step's scores go into the other buffer while the softmax warps work on this step's
                 if (i + 1 < n_it && !scores(i + 1)) break;
-                if (!mbar_wait(&v_full[i % STAGES], (i / STAGES) & 1)) { give_up(error, &failed, 20); break; }
-                if (!mbar_wait(p_full, i & 1)) { give_up(error, &failed, 14); break; }
+                if (!mbar_wait(&v_full[i % STAGES], (i / STAGES) & 1, wc.cycles)) { give_up(wc.error, &failed, 20); break; }
+                if (!mbar_wait(p_full, i & 1, wc.cycles)) { give_up(wc.error, &failed, 14); break; }
                 tc_fence_after();
                 const uint32_t v_addr = smem_u32(smem + V_OFF + (i % STAGES) * KV_BYTES);
                 // 16 keys an instruction: two groups of eight 128-byte rows of the values
@@ -199,7 +201,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
             const int key0 = (kt0 + i) * AT_BN + half * 32;
             uint32_t sr[32];
             float mx = -INFINITY;
-            if (ok && !__all_sync(0xffffffffu, mbar_wait(&s_full[i & 1], (i >> 1) & 1))) { if (lane == 0) give_up(error, &failed, 15); ok = false; }
+            if (ok && !__all_sync(0xffffffffu, mbar_wait(&s_full[i & 1], (i >> 1) & 1, wc.cycles))) { if (lane == 0) give_up(wc.error, &failed, 15); ok = false; }
             if (ok) {
                 tc_fence_after();
                 tmem_ld32(tmem_s + (i & 1) * AT_BN + half * 32 + lane_off, sr);
@@ -227,7 +229,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
                 const bool raise = mx > m + RAISE;  // also the first counted key after none (m = -inf)
                 if (__any_sync(0xffffffffu, raise)) {
                     // scale this warp's part of O (and the sums) to the new maxima; every earlier P V must have landed
-                    if (!__all_sync(0xffffffffu, mbar_wait(pv_done, (i - 1) & 1))) { if (lane == 0) give_up(error, &failed, 16); ok = false; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(pv_done, (i - 1) & 1, wc.cycles))) { if (lane == 0) give_up(wc.error, &failed, 16); ok = false; }
                     pv_waited = true;
                     if (ok) {
                         tc_fence_after();
@@ -247,7 +249,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
             const float m_use = m == -INFINITY ? 0.0f : m;
             // the probabilities may only replace the last step's once its P V has read them
             if (ok && i > 0 && !pv_waited) {
-                if (!__all_sync(0xffffffffu, mbar_wait(pv_done, (i - 1) & 1))) { if (lane == 0) give_up(error, &failed, 17); ok = false; }
+                if (!__all_sync(0xffffffffu, mbar_wait(pv_done, (i - 1) & 1, wc.cycles))) { if (lane == 0) give_up(wc.error, &failed, 17); ok = false; }
             }
             if (ok) {
                 float sum = 0.0f;
@@ -271,7 +273,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
                 // the values' rows beyond the last position (pages not loaded, slots not yet written): never counted,
                 // but 0 * garbage must not be NaN
                 if (kt0 + i == kt1 && (last_pos & (AT_BN - 1)) != AT_BN - 1 &&
-                    __all_sync(0xffffffffu, mbar_wait(&v_full[i % STAGES], (i / STAGES) & 1))) {      // the values have landed
+                    __all_sync(0xffffffffu, mbar_wait(&v_full[i % STAGES], (i / STAGES) & 1, wc.cycles))) {      // the values have landed
                     const int z0 = (last_pos & (AT_BN - 1)) + 1;
                     uint8_t* vs = smem + V_OFF + (i % STAGES) * KV_BYTES;
                     for (int idx = half * AT_BM + r; idx < (AT_BN - z0) * 8; idx += 2 * AT_BM)
@@ -286,7 +288,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
         xmax[half * AT_BM + r] = l;
         asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
         l += xmax[(half ^ 1) * AT_BM + r];
-        if (ok && !__all_sync(0xffffffffu, mbar_wait(pv_done, (n_it - 1) & 1))) { if (lane == 0) give_up(error, &failed, 18); ok = false; }
+        if (ok && !__all_sync(0xffffffffu, mbar_wait(pv_done, (n_it - 1) & 1, wc.cycles))) { if (lane == 0) give_up(wc.error, &failed, 18); ok = false; }
         if (ok) {
             tc_fence_after();
             const float inv = 1.0f / l;
@@ -354,5 +356,5 @@ VK_API int vk_attention_prefill_tcgen05(const void* q, const void* cache, const 
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     return launch_plain(kern, dim3(n_tiles, nh), dim3(AT_THREADS), smem, stream, mq, mkv, block_tables, tiles, (__nv_bfloat16*)out, nh,
-                        nkv, page_size, max_blocks, scale, window, error);
+                        nkv, page_size, max_blocks, scale, window, wait_ctl(error, WAIT_FAMILY_ATTENTION_PREFILL));
 }

@@ -10,8 +10,9 @@
 // tiles.  Each output element's sum runs over K in the same order whatever M is, so a row's result does
 // not depend on the batch.
 //
-// Every wait on an mbarrier is bounded: after about a second a waiter sets *error (a word the host can
-// read), the block stops issuing work, lets its copies land, frees its tensor memory and returns.
+// Every wait on an mbarrier is bounded: after the launch's limit (about a second unless the host set another) a
+// waiter sets *error (a word the host can read), the block stops issuing work, lets its copies land, frees its
+// tensor memory and returns.
 #include <cstdlib>
 
 #include "tcgen05_common.cuh"
@@ -42,7 +43,7 @@ struct TcExtra {
 template <int BN, int EPI>
 __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                     const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
-                                                                    int M, int N, int K, int* error, const TcExtra ex) {
+                                                                    int M, int N, int K, const WaitCtl wc, const TcExtra ex) {
     constexpr int TC_STAGES = TcStages<BN>::N;
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
     extern __shared__ uint8_t smem_raw[];
@@ -87,16 +88,20 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
                     tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &map_w, kb * TC_BK, n0, &full[s]);
                 }
             };
+            // (a stage named by wc.skip_stage is left unarmed and unfilled: a test of the give-up path)
             const int early = num_kb < TC_STAGES ? num_kb : TC_STAGES;
             for (int kb = 0; kb < early; kb++) {
+                if (kb == wc.skip_stage) continue;
                 mbar_expect_tx(&full[kb], STAGE_BYTES);
                 load_w(kb, kb);
             }
             dependency_wait();
-            for (int kb = 0; kb < early; kb++) tma_load_2d(smem + kb * STAGE_BYTES, &map_x, kb * TC_BK, m0, &full[kb]);
+            for (int kb = 0; kb < early; kb++)
+                if (kb != wc.skip_stage) tma_load_2d(smem + kb * STAGE_BYTES, &map_x, kb * TC_BK, m0, &full[kb]);
             for (int kb = early; kb < num_kb; kb++) {
                 const int s = kb % TC_STAGES;
-                if (!mbar_wait(&empty[s], ((kb / TC_STAGES) & 1) ^ 1)) { give_up(error, &failed, 1); break; }
+                if (!mbar_wait(&empty[s], ((kb / TC_STAGES) & 1) ^ 1, wc.cycles)) { give_up(wc.error, &failed, 1); break; }
+                if (kb == wc.skip_stage) continue;
                 mbar_expect_tx(&full[s], STAGE_BYTES);
                 tma_load_2d(smem + s * STAGE_BYTES, &map_x, kb * TC_BK, m0, &full[s]);
                 load_w(kb, s);
@@ -108,7 +113,7 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
             bool ok = true;
             for (int kb = 0; kb < num_kb && ok; kb++) {
                 const int s = kb % TC_STAGES;
-                if (!mbar_wait(&full[s], (kb / TC_STAGES) & 1)) { give_up(error, &failed, 2); ok = false; break; }
+                if (!mbar_wait(&full[s], (kb / TC_STAGES) & 1, wc.cycles)) { give_up(wc.error, &failed, 2); ok = false; break; }
                 tc_fence_after();
                 const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
 #pragma unroll
@@ -147,8 +152,8 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
 #pragma unroll
             for (int j = 0; j < BN / 8; j++) { rc[j] = cp[j]; rs[j] = sp[j]; }
         }
-        if (!mbar_wait(acc_full, 0)) {
-            if (lane == 0) give_up(error, &failed, 3);
+        if (!mbar_wait(acc_full, 0, wc.cycles)) {
+            if (lane == 0) give_up(wc.error, &failed, 3);
         } else if (EPI == TC_SWIGLU) {
             tc_fence_after();
             const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
@@ -315,7 +320,7 @@ constexpr int TW_BN = 256, TW_STAGES = 4;
 template <int EPI, int HD = 0>
 __global__ void __launch_bounds__(TC_THREADS, 1) linear_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                          const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
-                                                                         int M, int N, int K, int* error, const TcExtra ex) {
+                                                                         int M, int N, int K, const WaitCtl wc, const TcExtra ex) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = TW_BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -357,7 +362,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tcgen05_wide_kernel(cons
                 const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * tile_cols;
                 for (int kb = 0; kb < num_kb; kb++, kc++) {
                     const int s = kc % TW_STAGES;
-                    if (kc >= TW_STAGES && !mbar_wait(&empty[s], ((kc / TW_STAGES) - 1) & 1)) { give_up(error, &failed, 31); ok = false; break; }
+                    if (kc >= TW_STAGES && !mbar_wait(&empty[s], ((kc / TW_STAGES) - 1) & 1, wc.cycles)) { give_up(wc.error, &failed, 31); ok = false; break; }
+                    if (kc == wc.skip_stage) continue;      // left unarmed and unfilled: a test of the give-up path
                     mbar_expect_tx(&full[s], STAGE_BYTES);
                     tma_load_2d(smem + s * STAGE_BYTES, &map_x, kb * TC_BK, m0, &full[s]);
                     if (EPI == TC_SWIGLU) {        // the map's box is 128 rows: gate rows, then the same rows of up
@@ -376,11 +382,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tcgen05_wide_kernel(cons
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, j++) {
                 const int b = j & 1;
-                if (j >= 2 && !mbar_wait(&acc_empty[b], ((j >> 1) - 1) & 1)) { give_up(error, &failed, 32); break; }
+                if (j >= 2 && !mbar_wait(&acc_empty[b], ((j >> 1) - 1) & 1, wc.cycles)) { give_up(wc.error, &failed, 32); break; }
                 tc_fence_after();
                 for (int kb = 0; kb < num_kb; kb++, kc++) {
                     const int s = kc % TW_STAGES;
-                    if (!mbar_wait(&full[s], (kc / TW_STAGES) & 1)) { give_up(error, &failed, 33); ok = false; break; }
+                    if (!mbar_wait(&full[s], (kc / TW_STAGES) & 1, wc.cycles)) { give_up(wc.error, &failed, 33); ok = false; break; }
                     tc_fence_after();
                     const uint64_t a_desc = umma_desc_sw128(smem_u32(smem + s * STAGE_BYTES));
                     const uint64_t b_desc = umma_desc_sw128(smem_u32(smem + s * STAGE_BYTES + A_BYTES));
@@ -400,7 +406,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tcgen05_wide_kernel(cons
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, j++) {
             const int b = j & 1;
             const int row = (t % tiles_m) * TC_BM + quarter * 32 + lane, n0 = (t / tiles_m) * tile_cols;
-            if (ok && !__all_sync(0xffffffffu, mbar_wait(&acc_full[b], (j >> 1) & 1))) { if (lane == 0) give_up(error, &failed, 34); ok = false; }
+            if (ok && !__all_sync(0xffffffffu, mbar_wait(&acc_full[b], (j >> 1) & 1, wc.cycles))) { if (lane == 0) give_up(wc.error, &failed, 34); ok = false; }
             if (ok) {
                 tc_fence_after();
                 const uint32_t acc = lane_base + b * TW_BN;
@@ -575,6 +581,7 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int
 template <int BN, int EPI>
 static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int M, int N, int K, int* error, cudaStream_t stream,
                      const TcExtra& ex = TcExtra{}) {
+    const WaitCtl wc = wait_ctl(error, WAIT_FAMILY_LINEAR);
     const size_t smem = (size_t)TcStages<BN>::N * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + 128;
     auto kern = linear_tcgen05_kernel<BN, EPI>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -582,7 +589,7 @@ static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, void* out, in
     const int tile_cols = EPI == TC_SWIGLU ? BN / 2 : BN;
     const int cols = EPI == TC_SWIGLU ? ex.inter : N;
     dim3 grid((cols + tile_cols - 1) / tile_cols, (M + TC_BM - 1) / TC_BM);
-    return launch_dependent(kern, grid, dim3(TC_THREADS), smem, stream, mx, mw, out, M, N, K, error, ex);
+    return launch_dependent(kern, grid, dim3(TC_THREADS), smem, stream, mx, mw, out, M, N, K, wc, ex);
 }
 
 static int sm_count() {
@@ -614,6 +621,7 @@ static bool wide_takes(int M, int out_cols, int K, int tile_cols = TW_BN) {
 template <int EPI, int HD = 0>
 static int launch_wide(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int M, int N, int K, int* error, cudaStream_t stream,
                        const TcExtra& ex = TcExtra{}) {
+    const WaitCtl wc = wait_ctl(error, WAIT_FAMILY_LINEAR_WIDE);
     const size_t smem = (size_t)TW_STAGES * (TC_BM * TC_BK * 2 + TW_BN * TC_BK * 2) + 1024 + 128;
     auto kern = linear_tcgen05_wide_kernel<EPI, HD>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -622,7 +630,7 @@ static int launch_wide(const CUtensorMap& mx, const CUtensorMap& mw, void* out, 
     const int cols = EPI == TC_SWIGLU ? ex.inter : N;
     const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((cols + tile_cols - 1) / tile_cols);
     const int grid = tiles < sm_count() ? (int)tiles : sm_count();
-    return launch_plain(kern, dim3(grid), dim3(TC_THREADS), smem, stream, mx, mw, out, M, N, K, error, ex);
+    return launch_plain(kern, dim3(grid), dim3(TC_THREADS), smem, stream, mx, mw, out, M, N, K, wc, ex);
 }
 
 }  // namespace vk

@@ -7,7 +7,21 @@
 
 namespace vk {
 
-constexpr unsigned long long TC_WAIT_CYCLES = 2000000000ull;
+constexpr unsigned long long TC_WAIT_CYCLES = 2000000000ull;      // the default limit of a wait: about a second
+
+// What a kernel with bounded waits gets from its launcher: the word it sets when a wait runs out (the host can
+// read it), the limit of one wait in clock cycles, and, for tests of the give-up path only, the number of the
+// stage that the producer leaves unarmed (-1: none), so that its consumer's wait runs out.
+struct WaitCtl {
+    int* error;
+    unsigned long long cycles;
+    int skip_stage;
+};
+
+enum { WAIT_FAMILY_LINEAR = 1, WAIT_FAMILY_LINEAR_WIDE = 2, WAIT_FAMILY_ATTENTION_PREFILL = 3 };
+
+// Defined in runtime.cu: the limit in force and the one-shot test fault of a kernel family (taken by the next launch of it).
+WaitCtl wait_ctl(int* error, int family);
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -23,7 +37,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 // Bounded wait for the phase with the given parity.  False: gave up.  The waiting thread is suspended by the
 // hardware (up to the hint's 20 microseconds a try, woken as soon as the phase completes) instead of polling: polls of
 // waiting warps would take issue slots from the warps that work.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit) {
     const uint32_t addr = smem_u32(bar);
     long long start = 0;
     for (int tries = 0;; tries++) {
@@ -35,7 +49,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
             : "memory");
         if (done) return true;
         if (tries == 0) start = clock64();
-        else if ((unsigned long long)(clock64() - start) > TC_WAIT_CYCLES) return false;
+        else if ((unsigned long long)(clock64() - start) > limit) return false;
     }
 }
 

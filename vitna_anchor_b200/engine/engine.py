@@ -5,7 +5,9 @@ Options carry the names and meanings of the reference's command line
 request, default min(model maximum, 4096), engine/src/model.c:377-378),
 parallel (requests at once), max_new (default 64), temperature / top_k /
 top_p / seed (greedy when temperature is 0, the default), logits_out.
-Ours in addition: dtype, kv_block, num_pages, max_batch_tokens.
+Ours in addition: dtype, kv_block, num_pages, max_batch_tokens, max_prompt_portion (the most prompt tokens of
+one request in a step; the reference runs a prompt in pieces of 512 between decode rounds when others are decoding,
+engine/src/api.c:48-49, 2216-2224).
 """
 from __future__ import annotations
 
@@ -18,33 +20,37 @@ import torch
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .loading import load_model
-from .runner import ModelRunner, StepEntry, StepFailed
+from .runner import DeviceStepFailed, ModelRunner, StepEntry, StepFailed
 from .scheduler import PENDING, Planned, Request, RequestRefused, Scheduler  # noqa: F401
 
 
 class Engine:
-    def __init__(self, model: str, *, dtype: str = "bfloat16", ctx: Optional[int] = None, parallel: int = 8,
+    def __init__(self, model, *, dtype: str = "bfloat16", ctx: Optional[int] = None, parallel: int = 8,
                  kv_block: int = 16, num_pages: Optional[int] = None, max_batch_tokens: int = 2048,
-                 device: str = "cuda", cuda_graphs: bool = True, pipeline: bool = True):
+                 max_prompt_portion: int = 0, device: str = "cuda", cuda_graphs: bool = True, pipeline: bool = True):
         if str(device) not in ("cuda", "cuda:0"):
             raise ValueError(f"--device is cuda; this engine has no path for {device}")
         if not torch.cuda.is_available():
             raise RuntimeError("no CUDA device is usable, and the engine has no CPU path")
         if not (1 <= parallel <= 64):
             raise ValueError("--parallel is between 1 and 64")        # engine/src/main.c:30
-        self.model = load_model(model, dtype, "cuda")
+        # a folder with config.json and model.safetensors, or a model that is already built on the device
+        self.model = load_model(model, dtype, "cuda") if isinstance(model, (str, bytes)) or hasattr(model, "__fspath__") else model
         max_pos = self.model.max_positions
         self.ctx = min(ctx or min(max_pos, 4096), max_pos)
         self.runner = ModelRunner(self.model, page_size=kv_block, num_pages=num_pages, max_requests=parallel,
                                   max_batch_tokens=max_batch_tokens, max_model_len=self.ctx, device="cuda",
                                   cuda_graphs=cuda_graphs)
-        self.scheduler = Scheduler(self.runner.cache, max_batch_tokens=max_batch_tokens, max_model_len=self.ctx)
+        if max_prompt_portion < 0:
+            raise ValueError("--max-prompt-portion is 0 (no limit below the step's token budget) or a number of tokens")
+        self.scheduler = Scheduler(self.runner.cache, max_batch_tokens=max_batch_tokens, max_model_len=self.ctx,
+                                   max_prompt_portion=max_prompt_portion)
         self.sampler = Sampler(self.model.vocab_size, parallel, "cuda")
         self._next_id = 0
         self.last_timing: Dict[str, float] = {}
         # Decoding one step ahead of the host: the ids a step samples stay on the device and become the next step's
         # tokens there, while the host reads them a step later (see step()).
-        self.pipeline = pipeline and cuda_graphs
+        self.pipeline = pipeline and self.runner.cuda_graphs
         self._inflight = None            # (requests, index of the pending token in each request's output, host ids, event)
         self._ids_host = [torch.empty(parallel, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._ids_turn = 0
@@ -91,46 +97,72 @@ class Engine:
                         e.tokens = [0]           # replaced on the device
                 token_source = (self.sampler.last_ids(), src)
             else:
-                self._resolve()
+                try:
+                    self._resolve()
+                except DeviceStepFailed as e:
+                    return self._device_failure(e)
                 for p, e in zip(plan, entries):
                     p.refresh()
                     e.tokens = p.tokens
         try:
             logits = self.runner.step(entries, token_source)
+            if token_source is not None:
+                self._resolve()                  # the step before: its ids have been on their way for a whole step
+            tokens: List[int] = []
+            if sampling:
+                if logits_sink is not None:
+                    logits_sink(sampling, logits)
+                if can_feed:
+                    ids = self.sampler.sample_async(logits, [r.sampling for r in sampling], [r.rng for r in sampling])
+                    host = self._ids_host[self._ids_turn]
+                    self._ids_turn ^= 1
+                    host[:len(sampling)].copy_(ids, non_blocking=True)
+                    event = torch.cuda.Event()
+                    event.record()
+                    done = self.scheduler.update(plan, [PENDING] * len(sampling))
+                    self._inflight = (sampling, [len(r.output) - 1 for r in sampling], host, event)
+                    self._held += done
+                    return self._release()
+                tokens = self.sampler.sample(logits, [r.sampling for r in sampling], [r.rng for r in sampling])
+                self.runner.check(sync=False)    # the ids have arrived, so every kernel of the step is done
+        except DeviceStepFailed as e:
+            return self._device_failure(e, plan)
         except StepFailed:
             # the step computed nothing: its requests end with an error and keep what they had
-            self._resolve()
             failed = [p.request for p in plan]
+            try:
+                self._resolve()
+            except DeviceStepFailed as e:
+                return self._device_failure(e, plan)
             for req in failed:
                 self.scheduler.fail(req)
             return failed + self._release()
-        if token_source is not None:
-            self._resolve()                      # the step before: its ids have been on their way for a whole step
-        tokens: List[int] = []
-        if sampling:
-            if logits_sink is not None:
-                logits_sink(sampling, logits)
-            if can_feed:
-                ids = self.sampler.sample_async(logits, [r.sampling for r in sampling], [r.rng for r in sampling])
-                host = self._ids_host[self._ids_turn]
-                self._ids_turn ^= 1
-                host[:len(sampling)].copy_(ids, non_blocking=True)
-                event = torch.cuda.Event()
-                event.record()
-                done = self.scheduler.update(plan, [PENDING] * len(sampling))
-                self._inflight = (sampling, [len(r.output) - 1 for r in sampling], host, event)
-                self._held += done
-                return self._release()
-            tokens = self.sampler.sample(logits, [r.sampling for r in sampling], [r.rng for r in sampling])
         return self.scheduler.update(plan, tokens) + self._release()
+
+    def _device_failure(self, e: DeviceStepFailed, plan=()) -> List[Request]:
+        """A kernel gave up a wait: the requests of the steps that were in flight end with an error; a token that was still on its way is dropped, as the reference does not keep the
+        token of a failed step (engine/src/api.c:1777-1782).  The other requests go on."""
+        self._inflight = None
+        hit = set(e.request_ids)
+        failed = [r for r in list(self.scheduler.running) + self._held if r.request_id in hit]
+        self._held = [r for r in self._held if r.request_id not in hit]
+        for req in failed:
+            while req.output and req.output[-1] == PENDING:
+                req.output.pop()
+            if req.state != "finished":
+                self.scheduler.fail(req)
+            else:
+                req.finish_reason = "error"
+        return failed + self._release()
 
     def _resolve(self) -> None:
         """Wait for the ids of the step in flight and put them where PENDING stands."""
         if self._inflight is None:
             return
         reqs, places, host, event = self._inflight
-        self._inflight = None
         event.synchronize()
+        self.runner.check(sync=False)            # raises DeviceStepFailed when a kernel of that step gave up
+        self._inflight = None
         for r, place, tok in zip(reqs, places, host[:len(reqs)].tolist()):
             r.output[place] = int(tok)
 
@@ -141,8 +173,13 @@ class Engine:
         return ready
 
     def flush(self) -> List[Request]:
-        """Wait for whatever is still on its way; returns the finished requests that were held back for it."""
-        self._resolve()
+        """Wait for whatever is still on its way; returns the finished requests that were held back for it
+        (and those that a kernel's failure ended)."""
+        try:
+            self._resolve()
+            self.runner.check(sync=True)
+        except DeviceStepFailed as e:
+            return self._device_failure(e)
         return self._release()
 
     def run(self, logits_sink=None) -> List[Request]:
@@ -206,6 +243,8 @@ class Engine:
             for p in range(0, len(ids), piece):
                 chunk = [int(t) for t in ids[p:p + piece]]
                 rows.append(self.runner.step([StepEntry(rid, chunk, range(len(chunk)))]).clone())
+            self.runner.check(sync=True)         # no logits leave before every kernel is known to have finished its waits
         finally:
-            self.runner.close(rid)
+            if self.runner.cache.is_open(rid):
+                self.runner.close(rid)
         return torch.cat(rows, dim=0)

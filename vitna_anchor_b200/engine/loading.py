@@ -39,3 +39,24 @@ def write_random_model(model_dir: str, config_json: Mapping[str, Any], seed: int
                              matrix_dtype=matrix_dtype, norm_dtype=norm_dtype)
     out_json = cfg.to_dict() if hasattr(cfg, "to_dict") else dict(config_json)
     write_model_folder(model_dir, out_json, tensors)
+
+
+def random_model_on_device(config_json: Mapping[str, Any], seed: int, dtype="bfloat16", device="cuda", std: float = 0.02):
+    """A model of the architecture config_json names with weights drawn on the device by torch's generator
+    (matrices N(0, std), norm weights 1): for throughput measurements of sizes whose checkpoint would take a
+    minute to write and read.  No folder is made, and the bits are torch's, not those of write_random_model."""
+    arch = resolve(config_json)
+    cfg = arch.parse_config(config_json)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    weights = {}
+    for w in arch.manifest(cfg):
+        if w.optional:
+            continue
+        if arch.is_norm_weight(w.name):
+            weights[w.name] = torch.ones(w.shape, dtype=torch.float32, device=device)
+        else:
+            t = torch.empty(w.shape, dtype=torch.float32 if len(w.shape) < 2 else torch.bfloat16, device=device)
+            t.normal_(0.0, std, generator=gen)
+            weights[w.name] = t
+    return arch.build(cfg, weights, compute_dtype(dtype), device)

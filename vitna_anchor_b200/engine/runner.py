@@ -7,7 +7,14 @@ checks the tokens and the room, and holds pages for the new positions; if the
 pools cannot give them it raises OutOfPages and nothing has changed.  A
 request's length advances only when the step has been issued in full.
 
-The reference has three calls for this (one token, engine/src/model.c:866;
+A step is issued, not waited for.  Kernels with bounded waits (the tcgen05 ones) report a wait that ran out
+through a word the host can read; `check()` (after the caller's synchronisation, or with sync=True) and the
+start of every later step read it.  When it is set, every step issued since the last clean check is undone
+(lengths, pages, fixed-size states) and DeviceStepFailed names the requests: their logits were not valid.  The
+reference checks every device call and turns a failure into a failed step whose position does not advance
+(engine/src/model_cuda.cu:3537-3548, engine/src/model.c:868-883, engine/include/model.h:212-213).
+
+The reference has three calls for a step (one token, engine/src/model.c:866;
 a run of one sequence's tokens, model.c:982-1040; one token of each of
 several sequences, model.c:1149-1172) and never mixes a prompt piece with
 decode rows in one pass (engine/src/api.c:2216-2225).  Here they are one call.
@@ -15,17 +22,18 @@ decode rows in one pass (engine/src/api.c:2216-2225).  Here they are one call.
 from __future__ import annotations
 
 import os
-from dataclasses import dataclass, field
+from collections import OrderedDict
+from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
-import numpy as np
 import torch
 
 from .. import ops
-from ..cache.manager import CacheManager, KVSpec
-from ..cache.pages import OutOfPages, UNMAPPED
+from ..cache.manager import CacheManager
+from ..cache.pages import CacheError, OutOfPages  # noqa: F401
 from ..models.decoder import DecoderModel
-from ..parts.base import GroupMeta, StepContext, Workspace
+from ..parts.base import Workspace
+from .context import ContextBuilder, MetaOverflow
 
 
 class StepError(RuntimeError):
@@ -33,8 +41,16 @@ class StepError(RuntimeError):
 
 
 class StepFailed(RuntimeError):
-    """The step failed as a test asked it to; nothing ran and nothing changed
-    (cf. vitna_llama_fail_step_once, engine/src/model.c:471-493)."""
+    """The step failed; nothing of it is kept (cf. vitna_llama_fail_step_once, engine/src/model.c:471-493)."""
+
+
+class DeviceStepFailed(StepFailed):
+    """A kernel gave up a bounded wait.  `request_ids`: the requests of every step issued since the last clean
+    check; they are back at the lengths they had before those steps (or closed, when that was not possible)."""
+
+    def __init__(self, message: str, request_ids: Sequence[Hashable]):
+        super().__init__(message)
+        self.request_ids = list(request_ids)
 
 
 @dataclass
@@ -44,13 +60,15 @@ class StepEntry:
     want: Sequence[int] = ()      # places among `tokens` whose logits are returned
 
 
-class _Staging:
-    """A pinned host buffer and the event that tells when its last copy to the device is done."""
+@dataclass
+class _Issued:
+    """A step whose kernels may still be running."""
+    before: List[Tuple[Hashable, int]]     # (request, its length before the step)
+    states: object                         # what CacheManager.save_states returned, or None
+    event: torch.cuda.Event
 
-    def __init__(self, n: int, pinned: bool):
-        self.host = torch.empty(n, dtype=torch.int32, pin_memory=pinned)
-        self.np = self.host.numpy()
-        self.event: Optional[torch.cuda.Event] = None
+
+GRAPH_LOGIT_ROWS = 64      # steps with up to this many wanted rows may run from a captured graph
 
 
 class ModelRunner:
@@ -72,25 +90,28 @@ class ModelRunner:
         self.max_blocks = -(-self.max_model_len // page_size)
         self.workspace = Workspace(self.device, max_batch_tokens, max_requests, self.max_model_len)
         self.max_segments = max_requests
-        n_groups = len(self.cache.groups)
-        most = max(max_batch_tokens, self.max_segments)
-        self._meta_len = 6 * most + 64 + 7 * self.max_segments + most // 16 + 1 + n_groups * (most + self.max_segments * self.max_blocks)
-        self._staging = [_Staging(self._meta_len, True) for _ in range(4)]
-        self._stage_i = 0
-        self._meta_dev = torch.zeros(self._meta_len, dtype=torch.int32, device=self.device)
+        self.builder = ContextBuilder(self.cache, model.dtype, self.workspace, max_batch_tokens=max_batch_tokens,
+                                      max_segments=max_requests, max_model_len=self.max_model_len, device=self.device)
+        self._meta_dev = self.builder.meta_dev
         self._fail_at: Optional[int] = None
+        self._fail_after_run: Optional[int] = None
         env = os.environ.get("VITNA_TEST_FAIL_STEP")
         if env is not None:
             self._fail_at = int(env) if env.strip() else 0
         self.steps_run = 0
-        self.cuda_graphs = cuda_graphs
-        self._graphs: Dict[object, tuple] = {}   # decode batch bucket, or the counts of a mixed step -> (graph, logits, kernels)
+        # A model is run from captured graphs only if every part of it says that a capture replays it faithfully.
+        self.cuda_graphs = bool(cuda_graphs) and model.capture_safe
+        self._decode_graphs: "OrderedDict[tuple, tuple]" = OrderedDict()    # (batch bucket, context bucket) -> (graph, kernels)
+        self._mixed_graphs: Dict[tuple, tuple] = {}                          # the counts of a mixed step -> (graph, logits, kernels)
         self._seen_shapes: Dict[tuple, int] = {}
         self.graph_mixed_steps = True            # steps with prompt portions are captured too, once their counts repeat
-        self.max_graphs = 48
+        self.max_decode_graphs = 32              # least recently used goes first
+        self.max_mixed_graphs = 48
+        self._graph_logits: Optional[torch.Tensor] = None      # [GRAPH_LOGIT_ROWS, vocab]: where every graph leaves its logits
         self._src_dev = None
         self._src_host = None
         self.graph_replays = 0
+        self._issued: List[_Issued] = []
 
     # -- requests ---------------------------------------------------------------------------
     def open(self, request_id: Hashable) -> int:
@@ -106,9 +127,61 @@ class ModelRunner:
         """The next step that would compute `position` of any request raises StepFailed instead."""
         self._fail_at = position
 
+    def fail_after_run_once(self, run: int) -> None:
+        """For tests: the next step raises StepFailed on the host after run `run` of the model's schedule has been
+        issued (its kernels may have written caches and states; the step must leave no trace of that)."""
+        self._fail_after_run = run
+
     def decode_graph_takes(self, entries: Sequence[StepEntry]) -> bool:
         """Whether the batch is single tokens, each wanted: the decode graph's case."""
-        return self.cuda_graphs and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries)
+        return (self.cuda_graphs and len(entries) <= GRAPH_LOGIT_ROWS
+                and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries))
+
+    # -- device errors ------------------------------------------------------------------------
+    def check(self, sync: bool = True) -> None:
+        """Whether a kernel of the steps issued so far gave up a wait.  sync=True waits for them first (call it with
+        sync=False right after a synchronisation of your own).  Clean: returns.  Otherwise every step issued
+        since the last clean check is undone and DeviceStepFailed is raised."""
+        if sync:
+            torch.cuda.current_stream(self.device).synchronize()
+        code = ops.device_error_code()
+        if code == 0:
+            if sync:
+                self._issued.clear()
+            else:
+                while self._issued and self._issued[0].event.query():
+                    if ops.device_error_code() != 0:       # set between the two reads: handled below
+                        return self.check(sync=True)
+                    self._issued.pop(0)
+            return
+        if not sync:
+            torch.cuda.current_stream(self.device).synchronize()
+        try:
+            ops.check_device_errors()                       # clears the word
+        except ops.KernelGaveUp as e:
+            message = str(e)
+        undone = self._undo_issued()
+        raise DeviceStepFailed(f"{message}; {len(undone)} request(s) were put back to where they were before", undone)
+
+    def _undo_issued(self) -> List[Hashable]:
+        """Put every request of the issued steps back to its length before the oldest of them."""
+        first_len: Dict[Hashable, int] = {}
+        for item in self._issued:
+            for rid, n in item.before:
+                first_len.setdefault(rid, n)
+        for item in reversed(self._issued):                 # the oldest snapshot of a slot is restored last
+            if item.states is not None:
+                self.cache.restore_states(item.states)
+        self._issued.clear()
+        for rid, n in first_len.items():
+            if not self.cache.is_open(rid):
+                continue
+            try:
+                if self.cache.length(rid) > n:
+                    self.cache.rewind(rid, n)
+            except CacheError:
+                self.cache.close(rid)                       # a window has given pages back: nothing to return to
+        return list(first_len)
 
     # -- the step ---------------------------------------------------------------------------
     def _validate(self, entries: Sequence[StepEntry]) -> Tuple[int, int]:
@@ -142,93 +215,17 @@ class ModelRunner:
             raise StepError(f"{T} tokens in a step; the limit is {self.max_batch_tokens}")
         return T, R
 
-    def _build_context(self, entries: Sequence[StepEntry], T: int, R: int, fixed_blocks: Optional[int] = None,
-                       for_graph: bool = False) -> Tuple[StepContext, Optional[torch.Tensor]]:
-        """The batch's arrays in one staging buffer and one copy.  Where each array lies depends only on the
-        counts (tokens, segments, wanted rows, single-token segments, prompt tiles, width of the block tables),
-        so a graph captured for one batch finds the arrays of any batch with the same counts."""
-        S = len(entries)
-        ps = self.page_size
-        tables = self.cache.tables
-        lens = [len(e.tokens) for e in entries]
-        first = [tables.get(e.request_id).length for e in entries]
-        slots = [tables.get(e.request_id).slot for e in entries]
-        context = [f + n for f, n in zip(first, lens)]
-        maxb = fixed_blocks or max(1, max(-(-c // ps) for c in context))
-
-        st = self._staging[self._stage_i]
-        self._stage_i = (self._stage_i + 1) % len(self._staging)
-        if st.event is not None:
-            st.event.synchronize()
-        buf = st.np
-        off = 0
-
-        def put(values, count) -> slice:
-            nonlocal off
-            sl = slice(off, off + count)
-            buf[sl] = values
-            off += count
-            return sl
-
-        seg_starts = np.zeros(S + 1, dtype=np.int32)
-        np.cumsum(lens, out=seg_starts[1:])
-        s_tokens = put(np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries]), T)
-        s_pos = put(np.concatenate([np.arange(f, f + n, dtype=np.int32) for f, n in zip(first, lens)]), T)
-        s_seg = put(np.repeat(np.arange(S, dtype=np.int32), lens), T)
-        s_starts = put(seg_starts, S + 1)
-        s_ctx = put(np.asarray(context, dtype=np.int32), S)
-        s_slots = put(np.asarray(slots, dtype=np.int32), S)
-        rows = [int(seg_starts[i]) + int(w) for i, e in enumerate(entries) for w in e.want]
-        s_rows = put(np.asarray(rows, dtype=np.int32), R) if R else slice(off, off)
-        dec = [int(seg_starts[i]) for i in range(S) if lens[i] == 1]
-        pre = [t for i in range(S) if lens[i] > 1 for t in range(int(seg_starts[i]), int(seg_starts[i + 1]))]
-        s_dec = put(np.asarray(dec, dtype=np.int32), len(dec)) if dec else None
-        s_pre = put(np.asarray(pre, dtype=np.int32), len(pre)) if pre and dec else None
-        tiles = [(int(seg_starts[i]) + o, min(64, lens[i] - o), first[i] + o, i)
-                 for i in range(S) if lens[i] > 1 for o in range(0, lens[i], 64)]
-        off = (off + 3) & ~3                                   # 16-byte alignment for what follows
-        s_tiles = put(np.asarray(tiles, dtype=np.int32).reshape(-1), 4 * len(tiles)) if tiles else None
-        big = [(int(seg_starts[i]) + o, min(128, lens[i] - o), first[i] + o, i)
-               for i in range(S) if lens[i] > 1 for o in range(0, lens[i], 128)]
-        s_big = put(np.asarray(big, dtype=np.int32).reshape(-1), 4 * len(big)) if big else None
-        group_slices = []
-        for g in range(len(self.cache.groups)):
-            bt = np.zeros((S, maxb), dtype=np.int32)
-            sm = np.empty(T, dtype=np.int32)
-            for i, e in enumerate(entries):
-                blocks = tables.get(e.request_id).tables[g].blocks
-                row = np.asarray(blocks[:maxb], dtype=np.int32)
-                pos = np.arange(first[i], first[i] + lens[i])
-                sm[seg_starts[i]:seg_starts[i + 1]] = row[pos // ps] * ps + pos % ps
-                row = np.where(row == UNMAPPED, 0, row)      # pages behind a window are never read
-                bt[i, :len(row)] = row
-            group_slices.append((put(sm, T), put(bt.reshape(-1), S * maxb)))
-
-        dev = self._meta_dev
-        dev[:off].copy_(st.host[:off], non_blocking=True)
-        st.event = torch.cuda.Event()
-        st.event.record()
-
-        groups = [GroupMeta(dev[a], dev[b].view(S, maxb), maxb) for a, b in group_slices]
-        ctx = StepContext(
-            num_tokens=T, num_segments=S, dtype=self.model.dtype, tokens=dev[s_tokens], positions=dev[s_pos],
-            token_seg=dev[s_seg], seg_starts=dev[s_starts], seg_context=dev[s_ctx], seg_slots=dev[s_slots], groups=groups,
-            caches=self.cache.views, workspace=self.workspace, host_seg_lens=lens, host_seg_first_pos=first,
-            host_seg_slots=slots, max_seg_len=max(lens), max_context=self.max_model_len if for_graph else max(context),
-            decode_only=all(n == 1 for n in lens),
-            num_dec=len(dec), dec_tokens=None if (s_dec is None or not pre) else dev[s_dec],
-            num_pre=len(pre), pre_tokens=None if s_pre is None else dev[s_pre],
-            pre_tiles=None if s_tiles is None else dev[s_tiles].view(-1, 4),
-            pre_tiles_big=None if s_big is None else dev[s_big].view(-1, 4))
-        return ctx, (dev[s_rows] if R else None)
-
     def step(self, entries: Sequence[StepEntry], token_source: Optional[Tuple[torch.Tensor, Sequence[int]]] = None) -> Optional[torch.Tensor]:
         """Run the batch.  Returns float32 logits [wanted places, vocab] on the device, in the order of the
         entries and of each entry's `want`, or None when nothing is wanted.
 
+        The result is valid until the next step() of this runner: steps that are replayed from a captured graph
+        all leave their logits in the same buffer.  Copy what is to be kept (Engine.logits does).
+
         token_source = (ids, src): only for a batch of single tokens that goes through the decode graph; entry i
         with src[i] >= 0 takes its token from the device tensor ids[src[i]] (what an earlier step's sampling left
         there) instead of from entries[i].tokens, so the host need not wait for that step."""
+        self.check(sync=False)                # a wait that ran out in an earlier step ends here, before anything new is issued
         T, R = self._validate(entries)
         plan = [(e.request_id, len(e.tokens)) for e in entries]
         if self._fail_at is not None:
@@ -237,153 +234,135 @@ class ModelRunner:
                 if lo <= self._fail_at < lo + len(e.tokens):
                     self._fail_at = None
                     raise StepFailed(f"the step that computes position {lo} failed as the test asked")
+        before = [(e.request_id, self.cache.length(e.request_id)) for e in entries]
         self.cache.reserve_step(plan)         # OutOfPages leaves everything as it was
+        states = None
         try:
-            if self.decode_graph_takes(entries):
+            states = self.cache.save_states([e.request_id for e in entries])
+            if self._fail_after_run is not None:
+                logits = self._eager_step(entries)
+            elif self.decode_graph_takes(entries):
                 logits = self._decode_step(entries, token_source)
             elif token_source is not None:
                 raise StepError("tokens can be taken from the device only by a batch of single tokens")
-            elif self.cuda_graphs and self.graph_mixed_steps and 0 < R <= 64:
+            elif self.cuda_graphs and self.graph_mixed_steps and R <= GRAPH_LOGIT_ROWS:
                 logits = self._graphed_step(entries, T, R)
             else:
-                ctx, rows = self._build_context(entries, T, R)
-                logits = self.model.forward(ctx, rows)
-        except BaseException:
+                logits = self._eager_step(entries)
+        except BaseException as exc:
             self.cache.rollback_step(plan)
+            if states is not None:
+                self.cache.restore_states(states)
+            if isinstance(exc, MetaOverflow):
+                raise StepError(str(exc)) from None
             raise
         self.cache.commit_step(plan)
         self.steps_run += 1
+        event = torch.cuda.Event()
+        event.record()
+        self._issued.append(_Issued(before, states, event))
         return logits
 
-    # -- decoding through CUDA graphs -----------------------------------------------------------
-    def _decode_context(self, entries: Sequence[StepEntry], B: int, views: bool = True, reach: int = 0):
-        """The context of a batch of single tokens, padded to B segments, at fixed offsets in the
-        metadata buffer so that a captured graph finds every array where it was at capture.  A padding
-        segment has one token at position 0 that writes nothing (slot -1) and reads page 0."""
-        S, ps, maxb = len(entries), self.page_size, self.max_blocks
-        tables = self.cache.tables
-        st = self._staging[self._stage_i]
-        self._stage_i = (self._stage_i + 1) % len(self._staging)
-        if st.event is not None:
-            st.event.synchronize()
-        buf = st.np
-        n_groups = len(self.cache.groups)
-        total = 7 * B + 1 + n_groups * (B + B * maxb)
-        buf[:total] = 0
-        o_tok, o_pos, o_seg, o_starts = 0, B, 2 * B, 3 * B
-        o_ctx, o_slots, o_rows = 4 * B + 1, 5 * B + 1, 6 * B + 1
-        o_groups = 7 * B + 1
-        ar = np.arange(B + 1, dtype=np.int32)
-        buf[o_seg:o_seg + B] = ar[:B]
-        buf[o_starts:o_starts + B + 1] = ar
-        buf[o_rows:o_rows + B] = ar[:B]
-        buf[o_ctx:o_ctx + B] = 1
-        rcs = [tables.get(e.request_id) for e in entries]
-        first = [rc.length for rc in rcs]
-        buf[o_tok:o_tok + S] = [int(e.tokens[0]) for e in entries]
-        buf[o_pos:o_pos + S] = first
-        buf[o_ctx:o_ctx + S] = [f + 1 for f in first]
-        buf[o_slots:o_slots + S] = [rc.slot for rc in rcs]
-        for g in range(n_groups):
-            o_sm = o_groups + g * (B + B * maxb)
-            o_bt = o_sm + B
-            buf[o_sm:o_sm + B] = -1
-            bt = buf[o_bt:o_bt + B * maxb].reshape(B, maxb)
-            for i, rc in enumerate(rcs):
-                blocks = rc.tables[g].blocks
-                row = np.asarray(blocks, dtype=np.int32)
-                buf[o_sm + i] = row[first[i] // ps] * ps + first[i] % ps
-                np.maximum(row, 0, out=row)
-                bt[i, :len(row)] = row
-        dev = self._meta_dev
-        dev[:total].copy_(st.host[:total], non_blocking=True)
-        if st.event is None:
-            st.event = torch.cuda.Event()
-        st.event.record()
-        if not views:               # a replay needs the arrays in place, not their description
-            return None, None
-        groups = []
-        for g in range(n_groups):
-            o_sm = o_groups + g * (B + B * maxb)
-            groups.append(GroupMeta(dev[o_sm:o_sm + B], dev[o_sm + B:o_sm + B + B * maxb].view(B, maxb), maxb))
-        ctx = StepContext(
-            num_tokens=B, num_segments=B, dtype=self.model.dtype, tokens=dev[o_tok:o_tok + B], positions=dev[o_pos:o_pos + B],
-            token_seg=dev[o_seg:o_seg + B], seg_starts=dev[o_starts:o_starts + B + 1], seg_context=dev[o_ctx:o_ctx + B],
-            seg_slots=dev[o_slots:o_slots + B], groups=groups, caches=self.cache.views, workspace=self.workspace,
-            host_seg_lens=[1] * B, host_seg_first_pos=first + [0] * (B - S), host_seg_slots=[rc.slot for rc in rcs] + [0] * (B - S),
-            max_seg_len=1, max_context=reach or self.max_model_len, decode_only=True, num_dec=B)
-        return ctx, dev[o_rows:o_rows + B]
+    def _eager_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        ctx, rows = self.builder.build([(e.request_id, e.tokens, e.want) for e in entries])
+        if self._fail_after_run is not None:
+            fail_at, self._fail_after_run = self._fail_after_run, None
+
+            def after_run(i: int) -> None:
+                if i == fail_at:
+                    raise StepFailed(f"the step failed after run {i} of the schedule as the test asked")
+            ctx.after_run = after_run
+        return self.model.forward(ctx, rows)
+
+    # -- replaying captured graphs ----------------------------------------------------------------
+    def _logits_buffer(self) -> torch.Tensor:
+        if self._graph_logits is None:
+            self._graph_logits = torch.empty((GRAPH_LOGIT_ROWS, self.model.vocab_size), dtype=torch.float32, device=self.device)
+        return self._graph_logits
+
+    def _capture(self, ctx, rows, n_rows: int):
+        """Capture the step's launches (the step has just run eagerly, so every workspace buffer exists)."""
+        out = self._logits_buffer()[:n_rows] if n_rows else None
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
+        with torch.cuda.graph(graph):
+            self.model.forward(ctx, rows, out=out)
+        kernels = ops.launch_count() - before
+        ops.add_launches(-kernels)            # capture does not run the kernels
+        return graph, kernels
+
+    @staticmethod
+    def context_bucket(longest: int, limit: int) -> int:
+        """The bound on positions a decode graph is captured for: steps of 512 up to 4,096, of 1,024 up to 8,192,
+        of 2,048 beyond, so that a long context does not mean hundreds of graphs."""
+        step = 512 if longest <= 4096 else 1024 if longest <= 8192 else 2048
+        return min(limit, -(-longest // step) * step)
 
     def _decode_step(self, entries: Sequence[StepEntry], token_source=None) -> torch.Tensor:
         S = len(entries)
         B = 1
         while B < S:
             B *= 2
-        B = min(B, self.max_segments) if S <= self.max_segments else S
-        # the longest context, rounded up to 512 positions, bounds the grid of the decode attention: a graph per
-        # batch bucket and context bucket, so that a short context does not launch the blocks of a long one
+        B = min(B, self.max_segments, GRAPH_LOGIT_ROWS)
+        # the longest context, rounded up, bounds the grid of the decode attention: a graph per batch bucket and
+        # context bucket, so that a short context does not launch the blocks of a long one.  The first batch of a
+        # bucket runs eagerly and is then captured (a stall of about two steps, once per bucket).
         longest = max(self.cache.tables.get(e.request_id).length for e in entries) + 1
-        reach = min(self.max_model_len, -(-longest // 512) * 512)
+        reach = self.context_bucket(longest, self.max_model_len)
         key = (B, reach)
-        held = self._graphs.get(key)
-        ctx, rows = self._decode_context(entries, B, views=held is None, reach=reach)
+        held = self._decode_graphs.get(key)
+        ctx, rows = self.builder.build_decode([e.request_id for e in entries], [e.tokens[0] for e in entries], B,
+                                              views=held is None, reach=reach)
         if token_source is not None:
             ids, src = token_source
             if self._src_dev is None:
                 self._src_dev = torch.empty(self.max_segments, dtype=torch.int32, device=self.device)
                 self._src_host = [torch.empty(self.max_segments, dtype=torch.int32).pin_memory() for _ in range(4)]
-            host = self._src_host[self._stage_i]
+            host = self._src_host[self.builder.turn]
             host[:B] = -1
             host[:S] = torch.as_tensor(list(src), dtype=torch.int32)
             self._src_dev[:B].copy_(host[:B], non_blocking=True)
             ops.take_tokens(self._meta_dev[:B], ids, self._src_dev[:B])      # the tokens are the first B words of the metadata
+        out = self._logits_buffer()[:B]
         if held is None:
-            # the first batch of this size runs eagerly (it also makes the workspace buffers), then the
-            # same launches are captured; the captured graph is replayed from the next step on
-            logits = self.model.forward(ctx, rows)
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            before = ops.launch_count()
-            with torch.cuda.graph(graph):
-                static_logits = self.model.forward(ctx, rows)
-            kernels = ops.launch_count() - before
-            ops.add_launches(-kernels)            # capture does not run the kernels; `logits` above is this step's result
-            self._graphs[key] = (graph, static_logits, kernels)
-            return logits[:S]
-        graph, static_logits, kernels = held
+            self.model.forward(ctx, rows, out=out)
+            graph, kernels = self._capture(ctx, rows, B)
+            self._decode_graphs[key] = (graph, kernels)
+            while len(self._decode_graphs) > self.max_decode_graphs:
+                self._decode_graphs.popitem(last=False)
+            return out[:S]
+        self._decode_graphs.move_to_end(key)
+        graph, kernels = held
         graph.replay()
         ops.add_launches(kernels)
         self.graph_replays += 1
-        return static_logits[:S]
+        return out[:S]
 
-    def _graphed_step(self, entries: Sequence[StepEntry], T: int, R: int) -> torch.Tensor:
+    def _graphed_step(self, entries: Sequence[StepEntry], T: int, R: int) -> Optional[torch.Tensor]:
         """A step with prompt portions.  Issuing its few hundred launches from the host takes longer than the GPU
         needs for them, so once the same counts come a second time the step's launches are captured and from then
-        on replayed.  Everything that differs between two such steps (tokens, positions, block tables, which rows
-        are wanted) is in the metadata buffer, at places that depend on the counts alone."""
+        on replayed.  Everything that differs between two such steps (tokens, positions, slots, block tables, which
+        rows are wanted) is in the metadata buffer, at places that depend on the counts alone; a part that reads
+        anything else of a batch must say so (Part.capture_safe)."""
         lens = [len(e.tokens) for e in entries]
         n_dec = sum(1 for n in lens if n == 1)
         n_tiles = sum(-(-n // 64) for n in lens if n > 1)
         n_big = sum(-(-n // 128) for n in lens if n > 1)
         key = ("mixed", T, len(entries), R, n_dec, n_tiles, n_big)
-        ctx, rows = self._build_context(entries, T, R, fixed_blocks=self.max_blocks, for_graph=True)
-        held = self._graphs.get(key)
+        ctx, rows = self.builder.build([(e.request_id, e.tokens, e.want) for e in entries], fixed_blocks=self.max_blocks,
+                                       for_graph=True)
+        out = self._logits_buffer()[:R] if R else None
+        held = self._mixed_graphs.get(key)
         if held is not None:
-            graph, static_logits, kernels = held
+            graph, kernels = held
             graph.replay()
             ops.add_launches(kernels)
             self.graph_replays += 1
-            return static_logits
-        logits = self.model.forward(ctx, rows)
+            return out
+        logits = self.model.forward(ctx, rows, out=out)
         seen = self._seen_shapes.get(key, 0) + 1
         self._seen_shapes[key] = seen
-        if seen >= 2 and len(self._graphs) < self.max_graphs:
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            before = ops.launch_count()
-            with torch.cuda.graph(graph):
-                static_logits = self.model.forward(ctx, rows)
-            kernels = ops.launch_count() - before
-            ops.add_launches(-kernels)            # capture does not run the kernels; `logits` above is this step's result
-            self._graphs[key] = (graph, static_logits, kernels)
+        if seen >= 2 and len(self._mixed_graphs) < self.max_mixed_graphs:
+            self._mixed_graphs[key] = self._capture(ctx, rows, R)
         return logits

@@ -59,17 +59,29 @@ class DecoderModel:
         per_block = [b.weight_bytes() for b in self.blocks]
         return sum(per_block[r.block] for r in self.schedule) + self.final_norm.weight_bytes() + self.lm_head.weight_bytes()
 
-    def forward(self, ctx: StepContext, logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
-        """Run the batch; float32 logits [len(logit_rows), vocab] for the flat token indices in logit_rows."""
+    @property
+    def capture_safe(self) -> bool:
+        """Whether every part says that a captured CUDA graph replays it faithfully (Part.capture_safe)."""
+        def safe(part) -> bool:
+            if not getattr(part, "capture_safe", True):
+                return False
+            return all(safe(sub) for sub in vars(part).values() if isinstance(sub, Part))
+        return all(safe(p) for p in self.parts() if p is not None) and (self.position is None or safe(self.position))
+
+    def forward(self, ctx: StepContext, logit_rows: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """Run the batch; float32 logits [len(logit_rows), vocab] for the flat token indices in logit_rows
+        (written into `out` when given, else into a new tensor)."""
         x = self.embedding.forward(ctx)
         if self.position is not None:
             self.position.on_embeddings(x, ctx)
-        for run in self.schedule:
+        for i, run in enumerate(self.schedule):
             cache = ctx.caches[run.cache] if run.cache >= 0 else None
             self.blocks[run.block].forward(x, ctx, cache, run.write_cache)
+            if ctx.after_run is not None:
+                ctx.after_run(i)
         if logit_rows is None or logit_rows.shape[0] == 0:
             return None
         if self.lm_head.fuses_norm(self.final_norm, ctx, logit_rows.shape[0]):
-            return self.lm_head.forward_normed(x, logit_rows, self.final_norm, ctx)
+            return self.lm_head.forward_normed(x, logit_rows, self.final_norm, ctx, out=out)
         xn = self.final_norm.forward(x, ctx, "head.xn", logit_rows)
-        return self.lm_head.forward(xn, ctx)
+        return self.lm_head.forward(xn, ctx, out=out)

@@ -9,6 +9,7 @@ not on a CUDA device, the call raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -34,6 +35,26 @@ def lib() -> ctypes.CDLL:
 
 
 _launches = 0
+
+# The 32-bit path has two routings.  Exact (the default): every operation has ONE kernel, whatever the batch (the
+# tile product, the row-wise norm, attention_rows), and each of them sums an output's terms in an order that
+# depends on that output alone, so the logits of a position are the same BITS however the tokens are cut into
+# steps, whatever else is in the batch and wherever the pages lie.  Fast (VITNA_FLOAT32_FAST=1 in the environment,
+# or set_float32_exact(False)): the float32 twins of the serving kernels (few-rows products with fused norm,
+# rotation and SwiGLU, split-key decode attention) are chosen by batch size as in bfloat16; the result then
+# differs between ways of cutting by float32 rounding.
+_float32_exact = os.environ.get("VITNA_FLOAT32_FAST", "") in ("", "0")
+
+
+def set_float32_exact(exact: bool) -> bool:
+    """Choose the routing of the 32-bit path (see above); returns the setting that was in force."""
+    global _float32_exact
+    before, _float32_exact = _float32_exact, bool(exact)
+    return before
+
+
+def float32_exact() -> bool:
+    return _float32_exact
 
 
 def launch_count() -> int:
@@ -293,12 +314,41 @@ def error_word() -> torch.Tensor:
     return _error_word
 
 
+class KernelGaveUp(KernelError):
+    """A kernel's bounded wait ran out; what it and the kernels after it wrote is not valid."""
+
+
+def device_error_code() -> int:
+    """The code the last kernel that gave up a wait left (0: none), without clearing it.  The word is host memory,
+    so reading it costs nothing; it is up to date after any synchronisation with the kernels in question."""
+    return 0 if _error_word is None else int(_error_word[0])
+
+
 def check_device_errors() -> None:
     """Raise if a kernel gave up a bounded wait since the last check (call after a synchronisation)."""
-    if _error_word is not None and int(_error_word[0]) != 0:
-        code = int(_error_word[0])
+    code = device_error_code()
+    if code != 0:
         _error_word[0] = 0
-        raise KernelError(f"a kernel gave up waiting on an mbarrier (code {code}); its results are not valid")
+        raise KernelGaveUp(f"a kernel gave up waiting on an mbarrier (code {code}); its results are not valid")
+
+
+def set_wait_limit_ms(ms: float) -> None:
+    """The limit of one wait inside the kernels that wait on mbarriers, for every launch from now on, in
+    milliseconds at the device's highest clock (0 or less: the default, about a second).  Launches that a CUDA
+    graph already holds keep the limit they were captured with."""
+    status = lib().vk_set_wait_limit_ms(ctypes.c_double(float(ms)))
+    if status != 0:
+        raise KernelError(f"set_wait_limit_ms: CUDA error {status}")
+
+
+WAIT_FAMILIES = {"linear_tcgen05": 1, "linear_tcgen05_wide": 2, "attention_prefill_tcgen05": 3}
+
+
+def skip_stage_once(family: str, stage: int) -> None:
+    """For tests of the give-up path: the next launch of the named kernel family leaves one pipeline stage of
+    every block unarmed and unfilled, so its waits run out, the error word is set and the kernel returns by
+    itself.  Nothing faults: no address is out of range and nothing traps."""
+    lib().vk_test_skip_stage(WAIT_FAMILIES[family], int(stage))
 
 
 def tcgen05_takes(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -391,6 +441,8 @@ def fused_norm_takes(dtype: torch.dtype, M: int, K: int, N: int) -> bool:
 def skinny_takes(dtype: torch.dtype, M: int, K: int, N: int = 0) -> bool:
     """Whether the few-rows kernel should take this product (else the tile kernels do the work).  Every block
     stages all M rows for itself, so many rows times many blocks (a large N) is left to the tile kernels."""
+    if dtype == torch.float32 and _float32_exact:
+        return False
     if not (0 < M <= SKINNY_MAX_ROWS and K % (4 if dtype == torch.float32 else 8) == 0):
         return False
     return M <= 8 or N <= 8192 or dtype == torch.float32
@@ -462,6 +514,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> to
         return linear_skinny(x, w, out, mode)
     if tcgen05_takes(x, w) and out.data_ptr() % 16 == 0:
         return linear_tcgen05(x, w, out, mode)
+    if x.dtype == torch.float32 and _float32_exact:
+        return linear_simt(x, w, out, mode, few_rows=0)        # the tile kernel for every batch: one order of sums
     return linear_simt(x, w, out, mode)
 
 
@@ -519,7 +573,8 @@ def attention(q: torch.Tensor, pages: torch.Tensor, meta, ctx, out: torch.Tensor
     """Causal attention of a mixed batch over the paged cache; `meta` is the page group's GroupMeta.
     Single decoded tokens take the split-key kernel; tokens of prompt portions take the tensor-core kernel
     (bfloat16, head sizes it is built for); whatever is left takes attention_rows, which takes every size."""
-    dec_ok = bool(ctx.num_dec) and attention_decode_takes(q.dtype, hd, ctx.workspace.max_context)
+    dec_ok = (bool(ctx.num_dec) and attention_decode_takes(q.dtype, hd, ctx.workspace.max_context)
+              and not (q.dtype == torch.float32 and _float32_exact))
     pre_ok = (bool(ctx.num_pre) and q.dtype == torch.bfloat16 and hd in PREFILL_HEAD_SIZES and ctx.pre_tiles is not None
               and q.data_ptr() % 16 == 0)
     if dec_ok:

@@ -9,7 +9,7 @@ do the sum in its epilogue (float32 either way).
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence
+from typing import Callable, Dict, List, Optional, Sequence
 
 import torch
 
@@ -75,7 +75,9 @@ class StepContext:
     groups: List[GroupMeta]
     caches: List[LayerCacheView]
     workspace: Workspace
-    # the same on the host, for parts that plan launches per segment
+    # the same on the host, for parts that plan launches per segment.  A part that reads these (or anything else of
+    # a batch that is not a device array of this context) is not replayed faithfully by a captured graph and
+    # must set capture_safe = False.
     host_seg_lens: Sequence[int] = ()
     host_seg_first_pos: Sequence[int] = ()
     host_seg_slots: Sequence[int] = ()
@@ -92,10 +94,19 @@ class StepContext:
     pre_tiles: Optional[torch.Tensor] = None
     pre_tiles_big: Optional[torch.Tensor] = None     # the same cut into tiles of up to 128 tokens
     extra: dict = field(default_factory=dict)
+    after_run: Optional[Callable[[int], None]] = None    # called by the decoder after each run of its schedule (tests)
 
 
 class Part:
-    """Common base: a part may hold device tensors and says how many bytes of weights it reads per step."""
+    """Common base: a part may hold device tensors and says how many bytes of weights it reads per step.
+
+    capture_safe: whether a CUDA graph captured from one batch replays this part faithfully for any other batch
+    with the same counts (tokens, segments, wanted rows, single-token segments, prompt tiles).  True means: the
+    part's launches and their arguments depend only on those counts, on its own constants and on the context's
+    device arrays (a padding segment of a decode batch has seg_slots -1 and slot mapping -1), and it neither
+    synchronises nor allocates per batch.  A model with a part that says False is never captured."""
+
+    capture_safe: bool = True
 
     def weight_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.tensors())

@@ -6,6 +6,8 @@ ties them, the embedding table itself (engine/src/model.c:315-321, 975-978).
 """
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 from .. import ops
@@ -35,16 +37,23 @@ class LMHead(Part):
     def tensors(self):
         return [self.weight]
 
-    def forward(self, xn: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        """xn [R, hidden] in the compute dtype -> float32 logits [R, vocab] (a new tensor each call)."""
-        out = torch.empty((xn.shape[0], self.vocab), dtype=torch.float32, device=xn.device)
-        return ops.linear(xn, self.weight, out, ops.LINEAR_F32)
+    def _out(self, rows: int, out: Optional[torch.Tensor], device) -> torch.Tensor:
+        if out is None:
+            return torch.empty((rows, self.vocab), dtype=torch.float32, device=device)
+        if out.shape != (rows, self.vocab) or out.dtype != torch.float32 or not out.is_contiguous():
+            raise ValueError("the logits buffer is not a contiguous float32 [rows, vocab]")
+        return out
+
+    def forward(self, xn: torch.Tensor, ctx: StepContext, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """xn [R, hidden] in the compute dtype -> float32 logits [R, vocab] (in `out`, or a new tensor)."""
+        return ops.linear(xn, self.weight, self._out(xn.shape[0], out, xn.device), ops.LINEAR_F32)
 
     def fuses_norm(self, norm, ctx: StepContext, rows: int) -> bool:
         from .norms import RMSNorm
         return isinstance(norm, RMSNorm) and ops.fused_norm_takes(ctx.dtype, rows, self.hidden, self.vocab)
 
-    def forward_normed(self, x: torch.Tensor, rows: torch.Tensor, norm, ctx: StepContext) -> torch.Tensor:
+    def forward_normed(self, x: torch.Tensor, rows: torch.Tensor, norm, ctx: StepContext,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """logits of rmsnorm(x[rows]) in one launch (few rows); x is the float32 residual stream."""
-        out = torch.empty((rows.shape[0], self.vocab), dtype=torch.float32, device=x.device)
-        return ops.linear_skinny(x, self.weight, out, ops.EPI_F32, norm_weight=norm.weight, eps=norm.eps, rows=rows)
+        return ops.linear_skinny(x, self.weight, self._out(rows.shape[0], out, x.device), ops.EPI_F32, norm_weight=norm.weight,
+                                 eps=norm.eps, rows=rows)

@@ -6,12 +6,17 @@ which names may be absent (a tied output matrix).  The loader opens
 names (engine/src/model.c:196-263), and returns host tensors in their
 stored dtype.  Every mismatch is collected and reported in ONE error that
 lists missing tensors, unexpected tensors and wrong shapes
-(the reference stops at the first, engine/src/model.c:265-283).
+(the reference stops at the first, engine/src/model.c:265-283).  Tensors the
+model does not name are not an error by themselves: the reference binds by
+name and never looks at the rest (older exports carry rotary_emb.inv_freq
+buffers, for instance), so a checkpoint whose only difference is extra tensors
+loads, with a warning that names them.
 """
 from __future__ import annotations
 
 import json
 import os
+import warnings
 from dataclasses import dataclass
 from typing import Dict, List, Sequence, Tuple
 
@@ -88,8 +93,11 @@ def load_weights(model_dir: str, manifest: Sequence[WeightSpec]) -> Dict[str, to
                 wrong.append(f"{w.name} is {list(e.shape)}, the model needs {list(w.shape)}")
             elif w.floating != (e.dtype in ("F32", "BF16", "F16")):
                 wrong.append(f"{w.name} has dtype {e.dtype}")
-        if missing or unexpected or wrong:
+        if missing or wrong:
             raise WeightMismatch(model_dir, missing, unexpected, wrong)
+        if unexpected:
+            shown = ", ".join(unexpected[:8]) + (f", ... ({len(unexpected)} in all)" if len(unexpected) > 8 else "")
+            warnings.warn(f"{model_dir}: tensors the model does not use are ignored: {shown}", stacklevel=2)
         out = {}
         for w in manifest:
             if w.name in where:
