@@ -621,3 +621,80 @@ def test_attention_prefill_tcgen05_gives_up_a_wait_and_says_so(ops, stage):
     finally:
         ops.set_wait_limit_ms(0)
     _prefill_case(ops, ops.attention_prefill_tcgen05, 128, 4, 2, 64, 16, 0, [300, 448], [300, 200])
+
+
+@pytest.mark.parametrize("nh,nkv,ps,window,lens", [
+    (9, 3, 16, 0, [1, 7, 256, 257, 600, 1023]),
+    (4, 4, 8, 0, [31, 32, 33, 290, 1500]),
+    (32, 2, 32, 0, [5, 64, 300, 2047]),                       # a group of 16 heads: one full tile of rows
+    (40, 2, 16, 0, [100, 700]),                               # a group of 20 heads: two tiles a key-value head
+    (6, 2, 64, 0, [63, 64, 65, 1000]),
+    (3, 1, 128, 0, [200, 129, 3000]),
+    (3, 3, 16, 300, [10, 299, 300, 301, 900, 2000]),
+    (9, 3, 16, 700, [2048, 1700, 701]),
+    (9, 3, 16, 0, [int(n) for n in np.random.default_rng(3).integers(1, 2300, 200)]),     # many more units than warps: the ring runs across units
+])
+def test_attention_decode_tma_streams_the_pages(ops, nh, nkv, ps, window, lens):
+    """The persistent decode kernel (TMA boxes from the pages, a warp a unit, online softmax over chunks of 32 keys),
+    forced for every launch: contexts that end inside a chunk, on the edge of a chunk, a split and a page, windows that
+    begin inside a chunk, groups of more than 16 heads, pages of many sizes, and a batch of 200 tokens whose units
+    outnumber the grid's warps.  One key is made to stand out in each request; unused slots hold 1000.  Against the
+    plain attention, against the separate kernel, and twice over the same scratch."""
+    hd, dtype = 64, torch.bfloat16
+    rng = np.random.default_rng(8)
+    pages = sum(-(-n // ps) for n in lens) + 5
+    pool = torch.zeros(pages, 2, nkv, ps, hd, dtype=dtype) + 1000.0
+    free = list(rng.permutation(pages))
+    maxb = max(-(-n // ps) for n in lens)
+    bt = np.zeros((len(lens), maxb), dtype=np.int32)
+    qs, want = [], []
+    g = nh // nkv
+    for s, n in enumerate(lens):
+        k = (rng.standard_normal((n, nkv, hd)) * 1.5).astype(np.float32)
+        v = rng.standard_normal((n, nkv, hd)).astype(np.float32)
+        q = (rng.standard_normal((1, nh, hd)) * 1.5).astype(np.float32)
+        lo = max(0, n - window) if window else 0
+        far = min(n - 1, lo + 3 if s % 2 else max(lo, n - 260))
+        k[far] = q[0, ::g][:nkv] * 2.0
+        k, v, q = (torch.from_numpy(a).to(dtype).float().numpy() for a in (k, v, q))
+        blocks = [free.pop() for _ in range(-(-n // ps))]
+        bt[s, :len(blocks)] = blocks
+        kk = torch.from_numpy(k).to(dtype).reshape(n, nkv, hd); vv = torch.from_numpy(v).to(dtype).reshape(n, nkv, hd)
+        for b, page in enumerate(blocks):
+            m = min(ps, n - b * ps)
+            pool[page, 0, :, :m] = kk[b * ps:b * ps + m].transpose(0, 1)
+            pool[page, 1, :, :m] = vv[b * ps:b * ps + m].transpose(0, 1)
+        # the one query against its keys: scores, softmax, p * v (a query of the last position sees every key from lo on)
+        kf, vf = k[lo:], v[lo:]
+        ref = np.zeros((nh, hd), np.float32)
+        for h in range(nh):
+            sc = (kf[:, h // g] @ q[0, h]) / np.float32(math.sqrt(hd))
+            e = np.exp(sc - sc.max()); e /= e.sum()
+            ref[h] = e @ vf[:, h // g]
+        qs.append(q.reshape(-1)); want.append(ref.reshape(-1))
+    T = len(lens)
+    q_all = torch.from_numpy(np.stack(qs)).to(dtype).cuda()
+    seg = np.arange(T, dtype=np.int32)
+    pos = np.array(lens, np.int32) - 1
+    max_ctx = 4096
+    scratch = torch.zeros(ops.attention_decode_scratch_bytes(T, nh, nkv, hd, max_ctx), dtype=torch.uint8, device="cuda")
+    args = (q_all, pool.cuda(), dev(bt), dev(seg), dev(pos))
+    want = np.stack(want)
+    scale = max(1.0, float(np.abs(want).max()))
+    outs = {}
+    before = ops.set_decode_tma(1)
+    try:
+        for mode in (1, 0, 1):            # the streaming kernel, the separate kernel, the streaming kernel again on the same scratch
+            ops.set_decode_tma(mode)
+            out = torch.full((T, nh * hd), 5.0, dtype=dtype, device="cuda")
+            reach = -(-max(lens) // 256) * 256
+            ops.attention_decode(*args, out, scratch, T, nh, nkv, hd, 1.0 / math.sqrt(hd), max_ctx, reach if mode else max_ctx, window)
+            torch.cuda.synchronize()
+            ops.check_device_errors()
+            got = out.float().cpu().numpy()
+            assert np.isfinite(got).all()
+            assert np.abs(got - want).max() <= 2e-2 * scale, (mode, float(np.abs(got - want).max()))
+            outs.setdefault(mode, got)
+    finally:
+        ops.set_decode_tma(before)
+    assert np.abs(outs[1] - outs[0]).max() <= 1e-2 * scale

@@ -301,6 +301,14 @@ int launch_decode_mma(const void* q, const void* cache, const int32_t* bt, const
                       int hd, int page_size, int max_blocks, int splits, int grid_splits, int counter_tiles, float scale, int window,
                       cudaStream_t stream);
 
+// attention_decode_tma.cu: the persistent kernel for large launches (bfloat16, head size 64).
+bool decode_tma_takes(int n_tokens, int nh, int nkv, int hd, int page_size, int pages, int grid_splits, const void* q, const void* cache,
+                      const int* error);
+int launch_decode_tma(const void* q, const void* cache, const int32_t* bt, const int32_t* token_seg, const int32_t* positions,
+                      const int32_t* tok_list, void* out, float* part_o, float* part_ml, int* counters, int n_tokens, int nh, int nkv,
+                      int page_size, int pages, int max_blocks, int splits, int grid_splits, int counter_tiles, float scale, int window,
+                      int* error, cudaStream_t stream);
+
 }  // namespace vk
 
 using namespace vk;
@@ -317,10 +325,12 @@ VK_API size_t vk_attention_decode_scratch_bytes(int tokens, int nh, int nkv, int
 // scratch: vk_attention_decode_scratch_bytes(scratch_tokens, ..., max_context) bytes whose counters part (the
 // last) was zero before the first launch.  max_context fixes the layout of the scratch; grid_context
 // (<= max_context) bounds every position + 1 of this launch and sizes the grid (a captured graph keeps it).
+// pages: pages of the layer's cache (0: not known; only the kernel that streams the pages through TMA needs it);
+// error: a word a kernel with bounded waits sets when a wait runs out (null: such kernels are not chosen).
 VK_API int vk_attention_decode(const void* q, const void* cache, const int32_t* block_tables, const int32_t* token_seg,
                                const int32_t* positions, const int32_t* tok_list, void* out, void* scratch, int scratch_tokens,
-                               int n_tokens, int nh, int nkv, int hd, int page_size, int max_blocks, int max_context,
-                               int grid_context, float scale, int window, int dtype, cudaStream_t stream) {
+                               int n_tokens, int nh, int nkv, int hd, int page_size, int pages, int max_blocks, int max_context,
+                               int grid_context, float scale, int window, int dtype, int* error, cudaStream_t stream) {
     if (n_tokens <= 0) return VK_OK;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || page_size <= 0 || max_blocks <= 0 || window < 0 || max_context <= 0 ||
         grid_context <= 0 || grid_context > max_context)
@@ -338,6 +348,9 @@ VK_API int vk_attention_decode(const void* q, const void* cache, const int32_t* 
     float* part_o = (float*)base;
     float* part_ml = (float*)(base + up((size_t)scratch_tokens * nh * splits * hd * 4));
     int* counters = (int*)((char*)part_ml + up((size_t)scratch_tokens * nh * splits * 2 * 4));
+    if (dtype == 1 && decode_tma_takes(n_tokens, nh, nkv, hd, page_size, pages, grid_splits, q, cache, error))
+        return launch_decode_tma(q, cache, block_tables, token_seg, positions, tok_list, out, part_o, part_ml, counters, n_tokens, nh, nkv,
+                                 page_size, pages, max_blocks, splits, grid_splits, tiles, scale, window, error, stream);
     if (dtype == 1 && (hd == 16 || hd == 32 || hd == 64 || hd == 96 || hd == 128) && ((uintptr_t)q % 16 == 0))
         return launch_decode_mma(q, cache, block_tables, token_seg, positions, tok_list, out, part_o, part_ml, counters, n_tokens, nh,
                                  nkv, hd, page_size, max_blocks, splits, grid_splits, tiles, scale, window, stream);

@@ -18,7 +18,7 @@ struct WaitCtl {
     int skip_stage;
 };
 
-enum { WAIT_FAMILY_LINEAR = 1, WAIT_FAMILY_LINEAR_WIDE = 2, WAIT_FAMILY_ATTENTION_PREFILL = 3 };
+enum { WAIT_FAMILY_LINEAR = 1, WAIT_FAMILY_LINEAR_WIDE = 2, WAIT_FAMILY_ATTENTION_PREFILL = 3, WAIT_FAMILY_ATTENTION_DECODE = 4 };
 
 // Defined in runtime.cu: the limit in force and the one-shot test fault of a kernel family (taken by the next launch of it).
 WaitCtl wait_ctl(int* error, int family);

@@ -236,10 +236,17 @@ def attention_decode(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: t
     if scratch.numel() < attention_decode_scratch_bytes(scratch_tokens, nh, nkv, hd, max_context):
         raise KernelError("attention_decode: the scratch is too small")
     _check(lib().vk_attention_decode(_p(q), _p(cache_layer), _p(block_tables), _p(token_seg), _p(positions), _p(tok_list),
-                                     _p(out), _p(scratch), scratch_tokens, n, nh, nkv, hd, page_size, block_tables.shape[1],
-                                     max_context, grid_context, ctypes.c_float(scale), window, _dt(q), _stream()),
+                                     _p(out), _p(scratch), scratch_tokens, n, nh, nkv, hd, page_size, cache_layer.shape[0],
+                                     block_tables.shape[1], max_context, grid_context, ctypes.c_float(scale), window, _dt(q),
+                                     _p(error_word()), _stream()),
            "attention_decode")
     return out
+
+
+def set_decode_tma(mode: int) -> int:
+    """Which decode-attention launches the persistent TMA kernel takes: 0 none, 1 all whose sizes it takes, 2 those its
+    size rule gives it (the default).  Returns the mode that was in force."""
+    return int(lib().vk_set_decode_tma(int(mode)))
 
 
 def silu_mul(gu: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -341,7 +348,7 @@ def set_wait_limit_ms(ms: float) -> None:
         raise KernelError(f"set_wait_limit_ms: CUDA error {status}")
 
 
-WAIT_FAMILIES = {"linear_tcgen05": 1, "linear_tcgen05_wide": 2, "attention_prefill_tcgen05": 3}
+WAIT_FAMILIES = {"linear_tcgen05": 1, "linear_tcgen05_wide": 2, "attention_prefill_tcgen05": 3, "attention_decode_tma": 4}
 
 
 def skip_stage_once(family: str, stage: int) -> None:
