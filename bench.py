@@ -297,26 +297,41 @@ def mixed_run(model, clocks, requests=32, new_tokens=128, portion=512, seed=4):
 
 
 def gemm_run(pk, M=2048, reps=20):
-    """TFLOP/s of the tcgen05 product at the projection shapes of SmolLM2-135M / 360M / 1.7B, M rows of activations.
+    """TFLOP/s of the tcgen05 product at the projection shapes of SmolLM2-135M / 360M / 1.7B, M rows of activations, with the
+    epilogue the model uses there: gate_up with SwiGLU, o and down adding into the float32 residual stream, qkv plain.
     Operands are rotated through a set larger than L2 so that no launch finds its weights cached."""
     import torch
     from vitna_anchor_b200 import ops
-    shapes = {"135M qkv": (960, 576), "135M o": (576, 576), "135M gate_up": (3072, 576), "135M down": (576, 1536),
-              "360M gate_up": (5120, 960), "360M down": (960, 2560),
-              "1.7B qkv": (6144, 2048), "1.7B o": (2048, 2048), "1.7B gate_up": (16384, 2048), "1.7B down": (2048, 8192)}
+    shapes = {"135M qkv": (960, 576, "same"), "135M o": (576, 576, "acc"), "135M gate_up": (3072, 576, "swiglu"), "135M down": (576, 1536, "acc"),
+              "360M qkv": (1600, 960, "same"), "360M gate_up": (5120, 960, "swiglu"), "360M down": (960, 2560, "acc"),
+              "1.7B qkv": (6144, 2048, "same"), "1.7B o": (2048, 2048, "acc"), "1.7B gate_up": (16384, 2048, "swiglu"),
+              "1.7B down": (2048, 8192, "acc")}
     out = {}
-    for name, (N, K) in shapes.items():
+    for name, (N, K, kind) in shapes.items():
         copies = max(2, int(160e6 // (N * K * 2)) + 1)
         ws = [(torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(copies)]
         x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
-        y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        if kind == "swiglu":
+            y = torch.empty(M, N // 2, dtype=torch.bfloat16, device="cuda")
+            run = lambda w: ops.linear_tcgen05_swiglu(x, w, y)
+        elif kind == "acc":
+            y = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+            run = lambda w: ops.linear_tcgen05(x, w, y, ops.LINEAR_ACC_F32)
+        else:
+            y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+            run = lambda w: ops.linear_tcgen05(x, w, y, ops.LINEAR_SAME)
         for i in range(3):
-            ops.linear_tcgen05(x, ws[i % copies], y, ops.LINEAR_SAME)
+            run(ws[i % copies])
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()          # the launches are replayed from a graph, as in a step: the host's pace does not count
+        with torch.cuda.graph(graph):
+            for i in range(reps):
+                run(ws[i % copies])
+        graph.replay()
         torch.cuda.synchronize()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
-        for i in range(reps):
-            ops.linear_tcgen05(x, ws[i % copies], y, ops.LINEAR_SAME)
+        graph.replay()
         ev1.record()
         torch.cuda.synchronize()
         ops.check_device_errors()

@@ -475,6 +475,16 @@ def test_attention_prefill_tcgen05(ops, nh, nkv, ps, window):
     _prefill_case(ops, ops.attention_prefill_tcgen05, 128, nh, nkv, 64, ps, window, [300, 140, 601, 128 + 70, 448], [300, 37, 2, 70, 200])
 
 
+@pytest.mark.parametrize("nh,nkv,ps,window", [(3, 1, 16, 0), (2, 2, 32, 0), (2, 1, 16, 1500)])
+def test_attention_prefill_tcgen05_cuts_long_walks_into_parts(ops, nh, nkv, ps, window):
+    """Tiles whose walk over the keys is longer than 16 steps of 64 are cut into parts that different blocks take and the
+    last to arrive adds up: portions at the end of contexts of 2,300 and 4,000 positions (three and four parts), a whole
+    prompt of 1,025 tokens (its last tile has one row, whose second part is a single key), a walk of exactly 16 steps, and
+    a window that shortens the walk.  Run twice over the same scratch (the counters return to zero)."""
+    for _ in range(2):
+        _prefill_case(ops, ops.attention_prefill_tcgen05, 128, nh, nkv, 64, ps, window, [2300, 1100, 1025, 4000, 1024], [300, 70, 1025, 2, 128])
+
+
 def test_attention_prefill_tcgen05_refuses_what_it_does_not_take(ops):
     """Pages of 4 slots (a TMA box must be a multiple of eight 128-byte rows) and head sizes other than 64 are refused
     with a clear error; the dispatcher then takes the mma.sync kernel."""

@@ -20,8 +20,14 @@
 // probabilities are taken against the older maximum and may reach 256, which float32 sums and the two bfloat16
 // parts hold as well as values up to 1.  The result is normalised by the row's sum at the end.
 //
+// In a launch with few blocks (a portion of a few hundred tokens far into a context) a long walk is cut: a block takes at
+// most AT_PART key steps of its tile (part p of a tile is steps 16p .. 16p+15 from the tile's first), so that more
+// multiprocessors share the work.  A tile with one part is finished by its block as before; otherwise every part leaves its
+// unnormalised output, reference maxima and sums in scratch memory, and the part that arrives last (a counter per tile
+// and head, no waiting) adds them in part order and writes the result.
+//
 // A row's result does not depend on what else is in the batch: its keys are walked in 64s from absolute position
-// 0 (or the window's first tile), and every decision above is the row's own.
+// 0 (or the window's first tile), parts lie at fixed steps of that walk, and every decision above is the row's own.
 //
 // Every wait on an mbarrier is bounded: after the launch's limit (about a second unless the host set another) the
 // waiter sets *error (a word the host reads), the block stops, and its tensor memory is freed.
@@ -32,6 +38,17 @@
 namespace vk {
 
 constexpr int AT_BM = 128, AT_BN = 64, AT_THREADS = 320, AT_STAGES = 3;
+constexpr int AT_PART = 16;          // key steps of 64 a block walks at most, where walks are cut
+
+// Scratch of the parts: outputs [tiles][heads][parts][128][64] float32, then maxima and sums [tiles][heads][parts][128][2],
+// then counters [tiles][heads] (zero before the first launch; the kernel leaves them zero).
+struct AtScratch {
+    float* part_o;
+    float* part_ml;
+    int* counters;
+    int parts;                       // parts a tile can have in this launch (the grid's width is tiles * parts)
+    int part_steps;                  // key steps of a part (AT_PART; an experiment may set another through VITNA_ATT_PART)
+};
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -50,7 +67,7 @@ template <int HD>
 __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const int32_t* __restrict__ block_tables,
     const int32_t* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int max_blocks, float scale,
-    int window, const WaitCtl wc) {
+    int window, const WaitCtl wc, const AtScratch sc) {
     static_assert(HD == 64, "one 128-byte row per key");
     constexpr int STAGES = AT_STAGES;
     constexpr uint32_t Q_BYTES = AT_BM * HD * 2, KV_BYTES = AT_BN * HD * 2, P_BYTES = AT_BM * AT_BN * 2;
@@ -69,17 +86,22 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
     uint64_t* p_full = s_full + 2;
     uint64_t* pv_done = p_full + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
-    __shared__ int failed;
+    __shared__ int failed, is_last;
     __shared__ float xmax[4 * AT_BM];              // the halves' maxima of a row, two steps deep; at the end their sums
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = gridDim.x - 1 - blockIdx.x;     // later tiles of a prompt have more keys: start them first
+    const int unit = gridDim.x - 1 - blockIdx.x;     // later tiles of a prompt have more keys: start them first
+    const int tile = unit / sc.parts, part = unit % sc.parts;
     const int h = blockIdx.y;
     const int kvh = h / (nh / nkv);
     const int tok0 = tiles[tile * 4 + 0], rows = tiles[tile * 4 + 1], pos0 = tiles[tile * 4 + 2], seg = tiles[tile * 4 + 3];
     const int last_pos = pos0 + rows - 1;
     const int lo_first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;     // lowest key any row needs
-    const int kt0 = lo_first / AT_BN, kt1 = last_pos / AT_BN, n_it = kt1 - kt0 + 1;
+    const int kt_first = lo_first / AT_BN, kt1 = last_pos / AT_BN;      // the tile's walk: key steps kt_first .. kt1
+    const int n_parts = (kt1 - kt_first) / sc.part_steps + 1;                 // parts of this tile
+    if (part >= n_parts) return;                                        // the whole block: nothing to do
+    const int kt0 = kt_first + part * sc.part_steps;                          // this block's steps: kt0 .. kt0 + n_it - 1
+    const int n_it = min(sc.part_steps, kt1 - kt0 + 1);
 
     if (threadIdx.x == 0) {
         failed = 0;
@@ -289,14 +311,16 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
         asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
         l += xmax[(half ^ 1) * AT_BM + r];
         if (ok && !__all_sync(0xffffffffu, mbar_wait(pv_done, (n_it - 1) & 1, wc.cycles))) { if (lane == 0) give_up(wc.error, &failed, 18); ok = false; }
+        uint32_t orr[32];
         if (ok) {
             tc_fence_after();
-            const float inv = 1.0f / l;
-            __nv_bfloat16* dst = out + ((size_t)(tok0 + r) * nh + h) * HD + half * 32;
-            uint32_t orr[32];
             tmem_ld32(tmem_o + lane_off + half * 32, orr);
             tmem_loaded(orr);
-            if (valid) {
+        }
+        if (n_parts == 1) {
+            if (ok && valid) {
+                const float inv = 1.0f / l;
+                __nv_bfloat16* dst = out + ((size_t)(tok0 + r) * nh + h) * HD + half * 32;
 #pragma unroll
                 for (int d = 0; d < 32; d += 8) {
                     uint4 v;
@@ -304,6 +328,63 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
                     v.y = at_pack(__uint_as_float(orr[d + 2]) * inv, __uint_as_float(orr[d + 3]) * inv);
                     v.z = at_pack(__uint_as_float(orr[d + 4]) * inv, __uint_as_float(orr[d + 5]) * inv);
                     v.w = at_pack(__uint_as_float(orr[d + 6]) * inv, __uint_as_float(orr[d + 7]) * inv);
+                    *reinterpret_cast<uint4*>(dst + d) = v;
+                }
+            }
+        } else {
+            // this part's unnormalised output, reference maximum and sum; a row without a counted key in this part
+            // (its keys all lie in earlier parts) leaves maximum -inf and nothing else
+            const size_t slot = ((size_t)tile * nh + h) * sc.parts + part;
+            float* po = sc.part_o + (slot * AT_BM + r) * HD + half * 32;
+            if (ok && valid) {
+#pragma unroll
+                for (int d = 0; d < 32; d += 4)
+                    *reinterpret_cast<float4*>(po + d) = make_float4(__uint_as_float(orr[d]), __uint_as_float(orr[d + 1]), __uint_as_float(orr[d + 2]),
+                                                                     __uint_as_float(orr[d + 3]));
+                if (half == 0) *reinterpret_cast<float2*>(sc.part_ml + (slot * AT_BM + r) * 2) = make_float2(m, l);
+            }
+            // The 256 softmax threads meet; thread 0's counting releases the block's partial and acquires the others'.
+            // (A block whose wait ran out counts too, so that the counter returns to zero; the error word says that
+            // the result is not valid.)
+            asm volatile("bar.sync 5, 256;" ::: "memory");
+            if (threadIdx.x == 0) {
+                int* counter = sc.counters + (size_t)tile * nh + h;
+                int old;
+                asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(counter) : "memory");
+                is_last = old == n_parts - 1;
+                if (is_last) *counter = 0;          // ready for the next launch
+            }
+            asm volatile("bar.sync 5, 256;" ::: "memory");
+            if (is_last && valid) {
+                // parts in part order: running maximum, weights 2^(part's maximum - maximum), sum, output
+                const size_t first = ((size_t)tile * nh + h) * sc.parts;
+                float mm = -INFINITY, ll = 0.0f, acc[32];
+#pragma unroll
+                for (int d = 0; d < 32; d++) acc[d] = 0.0f;
+                for (int j = 0; j < n_parts; j++) {
+                    const float2 ml = __ldcg(reinterpret_cast<const float2*>(sc.part_ml + ((first + j) * AT_BM + r) * 2));
+                    if (ml.x == -INFINITY) continue;
+                    const float cm = fmaxf(mm, ml.x);
+                    const float keep = mm == -INFINITY ? 0.0f : at_ex2(mm - cm), w = at_ex2(ml.x - cm);
+                    const float4* src = reinterpret_cast<const float4*>(sc.part_o + ((first + j) * AT_BM + r) * HD + half * 32);
+                    ll = ll * keep + ml.y * w;
+#pragma unroll
+                    for (int d = 0; d < 32; d += 4) {
+                        const float4 v = __ldcg(src + d / 4);
+                        acc[d] = acc[d] * keep + v.x * w; acc[d + 1] = acc[d + 1] * keep + v.y * w;
+                        acc[d + 2] = acc[d + 2] * keep + v.z * w; acc[d + 3] = acc[d + 3] * keep + v.w * w;
+                    }
+                    mm = cm;
+                }
+                const float inv = 1.0f / ll;
+                __nv_bfloat16* dst = out + ((size_t)(tok0 + r) * nh + h) * HD + half * 32;
+#pragma unroll
+                for (int d = 0; d < 32; d += 8) {
+                    uint4 v;
+                    v.x = at_pack(acc[d] * inv, acc[d + 1] * inv);
+                    v.y = at_pack(acc[d + 2] * inv, acc[d + 3] * inv);
+                    v.z = at_pack(acc[d + 4] * inv, acc[d + 5] * inv);
+                    v.w = at_pack(acc[d + 6] * inv, acc[d + 7] * inv);
                     *reinterpret_cast<uint4*>(dst + d) = v;
                 }
             }
@@ -334,27 +415,56 @@ static bool at_make_map(CUtensorMap* map, const void* base, long long rows, int 
 
 using namespace vk;
 
+// Bytes of scratch for launches of up to cap_tiles tiles whose contexts reach max_context positions: the parts' outputs,
+// their maxima and sums, and the counters, in that order, each 256-byte aligned.
+VK_API size_t vk_attention_prefill_tcgen05_scratch_bytes(int cap_tiles, int nh, int max_context) {
+    const size_t parts = (size_t)((max_context - 1) / AT_BN) / AT_PART + 1;
+    auto up = [](size_t b) { return (b + 255) / 256 * 256; };
+    return up((size_t)cap_tiles * nh * parts * AT_BM * 64 * 4) + up((size_t)cap_tiles * nh * parts * AT_BM * 2 * 4) +
+           up((size_t)cap_tiles * nh * 4);
+}
+
 // q [n_tokens, nh*hd] bfloat16; cache [pages][2][nkv][page_size][hd] bfloat16 (one layer); tiles [n_tiles][4] with up to 128
 // rows a tile; out as q.  hd = 64; page_size a multiple of 8 that divides 64 or is a multiple of it.
+// scratch: vk_attention_prefill_tcgen05_scratch_bytes(cap_tiles, nh, max_context) bytes whose counters part (the last) was
+// zero before the first launch; cap_tiles and max_context fix its layout; grid_context (<= max_context) bounds every
+// position + 1 of this launch and sizes the grid (a captured graph keeps it).
 // error: a word the kernel sets (non-zero) if a bounded wait ran out.  VK_BAD_SHAPE for what this kernel does not take.
 VK_API int vk_attention_prefill_tcgen05(const void* q, const void* cache, const int32_t* block_tables, const int32_t* tiles, void* out,
                                         int n_tokens, int n_tiles, int pages, int nh, int nkv, int hd, int page_size, int max_blocks,
-                                        float scale, int window, int* error, cudaStream_t stream) {
+                                        float scale, int window, void* scratch, int cap_tiles, int max_context, int grid_context,
+                                        int* error, cudaStream_t stream) {
     if (n_tiles <= 0) return VK_OK;
-    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || max_blocks <= 0 || window < 0 || n_tokens <= 0 || pages <= 0 || !error)
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || max_blocks <= 0 || window < 0 || n_tokens <= 0 || pages <= 0 || !error ||
+        !scratch || max_context <= 0 || grid_context <= 0 || grid_context > max_context)
         return VK_BAD_SHAPE;
     if (hd != 64 || page_size % 8 != 0 || (AT_BN % page_size != 0 && page_size % AT_BN != 0)) return VK_BAD_SHAPE;
-    if (nh > 65535) return VK_TOO_LARGE;
+    if (nh > 65535 || n_tiles > cap_tiles) return VK_TOO_LARGE;
     const long long cache_rows = (long long)pages * 2 * nkv * page_size;
     if (cache_rows >= (1ll << 31)) return VK_TOO_LARGE;
-    if (((uintptr_t)q % 16) || ((uintptr_t)cache % 16) || ((uintptr_t)out % 16)) return VK_BAD_ALIGNMENT;
+    if (((uintptr_t)q % 16) || ((uintptr_t)cache % 16) || ((uintptr_t)out % 16) || ((uintptr_t)scratch % 16)) return VK_BAD_ALIGNMENT;
     CUtensorMap mq, mkv;
     if (!at_make_map(&mq, q, n_tokens, nh * hd, (long long)nh * hd, AT_BM)) return VK_BAD_SHAPE;
     if (!at_make_map(&mkv, cache, cache_rows, hd, hd, page_size < AT_BN ? page_size : AT_BN)) return VK_BAD_SHAPE;
+    const size_t max_parts = (size_t)((max_context - 1) / AT_BN) / AT_PART + 1;
+    auto up = [](size_t b) { return (b + 255) / 256 * 256; };
+    AtScratch sc;
+    sc.part_o = (float*)scratch;
+    sc.part_ml = (float*)((char*)scratch + up((size_t)cap_tiles * nh * max_parts * AT_BM * 64 * 4));
+    sc.counters = (int*)((char*)sc.part_ml + up((size_t)cap_tiles * nh * max_parts * AT_BM * 2 * 4));
+    // Walks are cut only when the launch has fewer blocks than three quarters of the multiprocessors (a portion of a few
+    // hundred tokens far into a context): measured, a part costs about five key steps of set-up, meeting and adding
+    // up, which a whole prompt's launch (a block or more a multiprocessor already) does not win back.
+    // VITNA_ATT_PART=n (n >= 16) cuts every launch into parts of n steps, for measurements.
+    static const int forced = [] { const char* e = getenv("VITNA_ATT_PART"); const int v = e ? atoi(e) : 0; return v >= AT_PART ? v : 0; }();
+    const bool cut = forced || (long long)n_tiles * nh * 4 <= (long long)148 * 3;
+    sc.part_steps = forced ? forced : cut ? AT_PART : (1 << 24);      // never below AT_PART: the scratch is laid out for that
+    sc.parts = cut ? ((grid_context - 1) / AT_BN) / sc.part_steps + 1 : 1;
+    if ((long long)n_tiles * sc.parts > 0x7fffffffll) return VK_TOO_LARGE;
     const size_t smem = (size_t)AT_BM * 64 * 2 + 2 * AT_STAGES * AT_BN * 64 * 2 + 2 * AT_BM * AT_BN * 2 + 1024 + 256;
     auto kern = attention_prefill_tcgen05_kernel<64>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    return launch_plain(kern, dim3(n_tiles, nh), dim3(AT_THREADS), smem, stream, mq, mkv, block_tables, tiles, (__nv_bfloat16*)out, nh,
-                        nkv, page_size, max_blocks, scale, window, wait_ctl(error, WAIT_FAMILY_ATTENTION_PREFILL));
+    return launch_plain(kern, dim3(n_tiles * sc.parts, nh), dim3(AT_THREADS), smem, stream, mq, mkv, block_tables, tiles, (__nv_bfloat16*)out, nh,
+                        nkv, page_size, max_blocks, scale, window, wait_ctl(error, WAIT_FAMILY_ATTENTION_PREFILL), sc);
 }

@@ -30,6 +30,14 @@ enum { TC_SAME = 0, TC_F32 = 1, TC_ACC = 2, TC_SWIGLU = 3, TC_ROPE = 4 };
 //   TC_ROPE    the weight is [(nh + 2*nkv) * hd, K]; BN = hd, so a tile is one head: a q head is rotated by the
 //              token's position and written to out [M, nh*hd]; a k head is rotated and written into the token's
 //              cache slot; a v head is written there as it is (engine/src/ops.c:273-281, engine/src/model.c:927-930)
+// silu(g) * up for the bfloat16 path: 2^x and the reciprocal come from the special-function unit (relative error about
+// 1e-6, far below the bfloat16 rounding of the result); the float32 path keeps expf and the division.
+__device__ __forceinline__ float tc_silu_mul(float g, float up) {
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * g));
+    return __fdividef(g, 1.0f + e) * up;
+}
+
 struct TcExtra {
     int inter;
     const int32_t* positions;
@@ -174,7 +182,7 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
                         for (int e = 0; e < 2; e++) {
                             const float gte = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gr[j + e])));
                             const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ur[j + e])));
-                            a[e] = (gte / (1.0f + expf(-gte))) * up;
+                            a[e] = tc_silu_mul(gte, up);
                         }
                         __nv_bfloat162 v = __floats2bfloat162_rn(a[0], a[1]);
                         packed[j / 2] = *reinterpret_cast<uint32_t*>(&v);
@@ -310,15 +318,15 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
 
 // ---------------------------------------------------------------------------------------------------------------
 // The wide variant for large products: a block (one a multiprocessor, as many blocks as multiprocessors) walks over
-// output tiles of 128 x 256, and two accumulators in tensor memory (2 x 256 columns, all there is) let the four
+// output tiles of 128 x 256, and two accumulators in tensor memory (2 x 256 columns, all there is) let the eight
 // epilogue warps drain one tile while the tensor core fills the next.  A 128 x 256 tile reads a quarter fewer bytes
 // a flop from the second-level cache than 128 x 128 (which that traffic bounded at about 60 % of the tensor peak),
 // and N = 256 instructions take the tensor core longer than they take their thread to issue.
 // SwiGLU: a tile is 128 gate rows and the 128 up rows of the same columns.
-constexpr int TW_BN = 256, TW_STAGES = 4;
+constexpr int TW_BN = 256, TW_STAGES = 4, TW_THREADS = 320;      // warps 0 and 1 feed and issue; eight warps drain the accumulators
 
 template <int EPI, int HD = 0>
-__global__ void __launch_bounds__(TC_THREADS, 1) linear_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x,
+__global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                          const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
                                                                          int M, int N, int K, const WaitCtl wc, const TcExtra ex) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = TW_BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -341,7 +349,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tcgen05_wide_kernel(cons
     if (threadIdx.x == 0) {
         failed = 0;
         for (int s = 0; s < TW_STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -398,8 +406,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tcgen05_wide_kernel(cons
             }
         }
     } else {
-        // epilogue: warp w reads lanes 32*(w%4) .. +31 of the accumulator, one output row per thread
-        const int quarter = warp & 3;
+        // epilogue: warp w reads lanes 32*(w%4) .. +31 of the accumulator (the lanes a warp may read), one output row per
+        // thread; the two warps of a lane quarter take half of the tile's columns each
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         int j = 0;
         bool ok = true;
@@ -412,7 +421,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tcgen05_wide_kernel(cons
                 const uint32_t acc = lane_base + b * TW_BN;
                 if (EPI == TC_SWIGLU) {
 #pragma unroll 1
-                    for (int c = 0; c < TW_BN / 2; c += 32) {
+                    for (int c = half * (TW_BN / 4); c < (half + 1) * (TW_BN / 4); c += 32) {
                         uint32_t gr[32], ur[32];
                         tmem_ld32_nowait(acc + c, gr);
                         tmem_ld32_nowait(acc + TW_BN / 2 + c, ur);
@@ -430,7 +439,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tcgen05_wide_kernel(cons
                                 for (int e = 0; e < 2; e++) {
                                     const float gte = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gr[q + e])));
                                     const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ur[q + e])));
-                                    v[e] = (gte / (1.0f + expf(-gte))) * up;
+                                    v[e] = tc_silu_mul(gte, up);
                                 }
                                 __nv_bfloat162 pk = __floats2bfloat162_rn(v[0], v[1]);
                                 packed[q / 2] = *reinterpret_cast<uint32_t*>(&pk);
@@ -451,7 +460,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tcgen05_wide_kernel(cons
                     const int sl = row < M ? ex.slot[row] : -1;
                     const int p0 = row < M ? ex.positions[row] : 0;
 #pragma unroll 1
-                    for (int hh = 0; hh < TW_BN / HDX; hh++) {
+                    for (int hh = half * (TW_BN / HDX / 2); hh < (half + 1) * (TW_BN / HDX / 2); hh++) {
                         const int head = n0 / HDX + hh;
                         if (head >= ex.nh + 2 * ex.nkv) break;          // the same for the whole warp
                         const bool is_q = head < ex.nh, is_k = !is_q && head < ex.nh + ex.nkv;
@@ -503,7 +512,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) linear_tcgen05_wide_kernel(cons
                     }
                 } else {
 #pragma unroll 1
-                    for (int c = 0; c < TW_BN; c += 32) {
+                    for (int c = half * (TW_BN / 2); c < (half + 1) * (TW_BN / 2); c += 32) {
                         uint32_t r[32];
                         tmem_ld32(acc + c, r);
                         tmem_loaded(r);
@@ -602,9 +611,10 @@ static int sm_count() {
     return n;
 }
 
-// Whether the wide variant takes a product.  Measured at M = 2,048: it wins where a block gets more than one tile
-// (the epilogue of one hides behind the main loop of the next) or where K is long enough that the main loop is nearly
-// all of a tile's time; with one short tile a block the narrow kernel's two blocks a multiprocessor do better.
+// Whether the wide variant takes a product.  Measured at M = 2,048 (bench.py --only-gemm, replayed from a graph): it wins
+// where a block gets more than one tile (the epilogue of one hides behind the main loop of the next; with eight epilogue
+// warps also at K = 576, where a tile's main loop is only nine stages long) or where K is long enough that the main loop
+// is nearly all of a tile's time; with one short tile a block the narrow kernel's two blocks a multiprocessor do better.
 // tile_cols: output columns of a wide tile.  VITNA_TCGEN05_WIDE=0 or 1 overrides (for measurements).
 static bool wide_takes(int M, int out_cols, int K, int tile_cols = TW_BN) {
     static int forced = -1;
@@ -615,7 +625,7 @@ static bool wide_takes(int M, int out_cols, int K, int tile_cols = TW_BN) {
     if (forced != 2) return forced == 1;
     if (M < 512 || out_cols < 1024 || K < 512) return false;
     const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((out_cols + tile_cols - 1) / tile_cols);
-    return K >= 2048 || (K >= 768 && tiles * 4 >= (long long)sm_count() * 5);    // at K = 576 a tile's epilogue outlasts its main loop
+    return K >= 2048 || tiles * 4 >= (long long)sm_count() * 5;
 }
 
 template <int EPI, int HD = 0>
@@ -630,7 +640,7 @@ static int launch_wide(const CUtensorMap& mx, const CUtensorMap& mw, void* out, 
     const int cols = EPI == TC_SWIGLU ? ex.inter : N;
     const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((cols + tile_cols - 1) / tile_cols);
     const int grid = tiles < sm_count() ? (int)tiles : sm_count();
-    return launch_plain(kern, dim3(grid), dim3(TC_THREADS), smem, stream, mx, mw, out, M, N, K, wc, ex);
+    return launch_plain(kern, dim3(grid), dim3(TW_THREADS), smem, stream, mx, mw, out, M, N, K, wc, ex);
 }
 
 }  // namespace vk

@@ -555,11 +555,22 @@ def attention_prefill_tcgen05_takes(q: torch.Tensor, cache_layer: torch.Tensor, 
             and cache_layer.is_contiguous())
 
 
+def attention_prefill_tcgen05_scratch_bytes(cap_tiles: int, nh: int, max_context: int) -> int:
+    fn = lib().vk_attention_prefill_tcgen05_scratch_bytes
+    fn.restype = ctypes.c_size_t
+    return int(fn(cap_tiles, nh, max_context))
+
+
 def attention_prefill_tcgen05(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: torch.Tensor, tiles: torch.Tensor,
-                              out: torch.Tensor, nh: int, nkv: int, hd: int, scale: float, window: int = 0) -> torch.Tensor:
+                              out: torch.Tensor, nh: int, nkv: int, hd: int, scale: float, window: int = 0, *,
+                              scratch: Optional[torch.Tensor] = None, cap_tiles: int = 0, max_context: int = 0,
+                              grid_context: int = 0) -> torch.Tensor:
     """Causal attention of prompt portions on the tcgen05 tensor cores (scores and P V in tensor memory, keys and
     values by TMA straight from the pages).  tiles int32 [n, 4]: first token, rows (1..128), position of the first
-    token, segment."""
+    token, segment.  A tile whose walk over the keys is long is cut into parts that different blocks take; their
+    partial results meet in `scratch`: a byte buffer of attention_prefill_tcgen05_scratch_bytes(cap_tiles, nh,
+    max_context) that was zero at first use and is used with no other (cap_tiles, nh, max_context); grid_context
+    (<= max_context) bounds the positions of this launch.  Without a scratch one is made for this call."""
     _req(q, "q", torch.bfloat16, 2); _req(cache_layer, "cache_layer", torch.bfloat16, 5)
     _req(block_tables, "block_tables", torch.int32, 2); _req(tiles, "tiles", torch.int32, 2); _req(out, "out", torch.bfloat16, 2)
     page_size = cache_layer.shape[3]
@@ -568,9 +579,17 @@ def attention_prefill_tcgen05(q: torch.Tensor, cache_layer: torch.Tensor, block_
         raise KernelError("attention_prefill_tcgen05: shapes do not fit the head counts")
     if not attention_prefill_tcgen05_takes(q, cache_layer, hd):
         raise KernelError("attention_prefill_tcgen05: bfloat16, head size 64 and pages of 8, 16, 32 or a multiple of 64 slots only")
+    if scratch is None:
+        cap_tiles = tiles.shape[0]
+        max_context = grid_context = max_context or block_tables.shape[1] * page_size
+        scratch = torch.zeros(attention_prefill_tcgen05_scratch_bytes(cap_tiles, nh, max_context), dtype=torch.uint8, device=q.device)
+    _req(scratch, "scratch", torch.uint8, 1)
+    if scratch.numel() < attention_prefill_tcgen05_scratch_bytes(cap_tiles, nh, max_context):
+        raise KernelError("attention_prefill_tcgen05: the scratch is too small")
     _check(lib().vk_attention_prefill_tcgen05(_p(q), _p(cache_layer), _p(block_tables), _p(tiles), _p(out), q.shape[0], tiles.shape[0],
                                               cache_layer.shape[0], nh, nkv, hd, page_size, block_tables.shape[1],
-                                              ctypes.c_float(scale), window, _p(error_word()), _stream()),
+                                              ctypes.c_float(scale), window, _p(scratch), cap_tiles, max_context,
+                                              grid_context or max_context, _p(error_word()), _stream()),
            "attention_prefill_tcgen05")
     return out
 
@@ -593,7 +612,13 @@ def attention(q: torch.Tensor, pages: torch.Tensor, meta, ctx, out: torch.Tensor
                          layout, min(layout, max(1, ctx.max_context)), window, ctx.dec_tokens)
     if pre_ok:
         if ctx.pre_tiles_big is not None and attention_prefill_tcgen05_takes(q, pages, hd) and out.stride(0) == out.shape[1]:
-            attention_prefill_tcgen05(q, pages, meta.block_tables, ctx.pre_tiles_big, out, nh, nkv, hd, scale, window)
+            ws = ctx.workspace
+            cap_tiles, layout = ws.max_tokens // 128 + ws.max_segments, ws.max_context
+            nbytes = attention_prefill_tcgen05_scratch_bytes(cap_tiles, nh, layout)
+            scratch = ws.flat(f"att.pre/{nh}/{cap_tiles}/{layout}", nbytes, torch.uint8, zero=True)
+            attention_prefill_tcgen05(q, pages, meta.block_tables, ctx.pre_tiles_big, out, nh, nkv, hd, scale, window,
+                                      scratch=scratch, cap_tiles=cap_tiles, max_context=layout,
+                                      grid_context=min(layout, max(1, ctx.max_context)))
         else:
             attention_prefill(q, pages, meta.block_tables, ctx.pre_tiles, out, nh, nkv, hd, scale, window)
     if not dec_ok and not pre_ok:
