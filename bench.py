@@ -284,13 +284,16 @@ def mixed_run(model, clocks, requests=32, new_tokens=128, portion=512, seed=4):
         wall = time.perf_counter() - t0
         assert all(len(r.output) == new_tokens for r in reqs)
         return wall, eng.runner.steps_run - steps0, ops.launch_count() - launches0
-    once()                                   # warm-up: the same lengths, so the same shapes of steps are captured
+    # warm-up: the same lengths, so the same shapes of steps come again; a shape is captured into a graph at its second
+    # coming, so two rounds go before the timed one
+    rounds = [once()[0], once()[0]]
     clocks.active = True
     wall, steps, launches = once()
     clocks.active = False
     out = {"value": requests * new_tokens / wall, "unit": "new tokens/s", "all_tokens_per_s": (sum(lengths) + requests * new_tokens) / wall,
            "seconds": wall, "steps": steps, "launches": launches, "prompt_tokens": sum(lengths), "requests": requests,
-           "new_tokens_each": new_tokens, "portion": portion, "graph_replays": eng.runner.graph_replays}
+           "new_tokens_each": new_tokens, "portion": portion, "graph_replays": eng.runner.graph_replays,
+           "warmup_round_seconds": rounds, "graphs": len(eng.runner._mixed_graphs) + len(eng.runner._decode_graphs)}
     del eng
     torch.cuda.empty_cache()
     return out

@@ -9,7 +9,9 @@
 //            (a box of one page's rows for one key-value head, 128-byte swizzle) into two three-stage rings
 //   warp 9   one lane issues tcgen05.mma: S[128 x 64] = Q K^T into one of two score buffers in tensor memory (the
 //            next step's scores are computed while the softmax warps work on this step's), and, once the
-//            probabilities lie in shared memory, O[128 x 64] += P V (V as it lies in the cache: the N-major operand)
+//            probabilities lie in shared memory, O[128 x 64] += P V (V as it lies in the cache: the N-major operand);
+//            the probabilities have two buffers too, so that the softmax warps write a step's while the tensor core
+//            still reads the step's before
 //   warps 0-7  two threads a query row (warps w and w+4 share rows 32w .. 32w+31 and take 32 of the step's keys
 //            each): read the scores from tensor memory, mask, maximum (the two meet once a step), 2^x, write the
 //            probabilities as a high and a low bfloat16 part (p = hi + lo to about 2^-17, so that P V matches
@@ -63,16 +65,23 @@ __device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int HD>
-__global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kernel(
+// DBUF: two buffers of probabilities (132 KB of shared memory, one block a multiprocessor) instead of one (96 KB, two
+// blocks): the softmax warps then write a step's probabilities while the tensor core still reads the step's before.
+// Measured, that wins a little where a launch has no more blocks than multiprocessors, and loses where two blocks
+// can share one.
+template <int HD, bool DBUF>
+__global__ void __launch_bounds__(AT_THREADS, DBUF ? 1 : 2) attention_prefill_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const int32_t* __restrict__ block_tables,
     const int32_t* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int max_blocks, float scale,
     int window, const WaitCtl wc, const AtScratch sc) {
     static_assert(HD == 64, "one 128-byte row per key");
     constexpr int STAGES = AT_STAGES;
     constexpr uint32_t Q_BYTES = AT_BM * HD * 2, KV_BYTES = AT_BN * HD * 2, P_BYTES = AT_BM * AT_BN * 2;
-    constexpr uint32_t K_OFF = Q_BYTES, V_OFF = K_OFF + STAGES * KV_BYTES, PH_OFF = V_OFF + STAGES * KV_BYTES, PL_OFF = PH_OFF + P_BYTES,
-                       BAR_OFF = PL_OFF + P_BYTES;
+    constexpr uint32_t K_OFF = Q_BYTES, V_OFF = K_OFF + STAGES * KV_BYTES, PH_OFF = V_OFF + STAGES * KV_BYTES, PL_OFF = PH_OFF + (DBUF ? 2 : 1) * P_BYTES,
+                       BAR_OFF = PL_OFF + (DBUF ? 2 : 1) * P_BYTES;
+    // the probabilities of step i lie in buffer pbuf(i); its completions on p_full and pv_done have parity ppar(i)
+    auto pbuf = [](int i) -> int { return DBUF ? (i & 1) : 0; };
+    auto ppar = [](int i) -> uint32_t { return DBUF ? ((i >> 1) & 1) : (i & 1); };
     constexpr uint32_t TMEM_COLS = 256;              // S in columns 0..63 and 64..127 (two buffers), O in 128..191
     constexpr float RAISE = 8.0f;                    // the reference maximum follows when the step's exceeds it by 2^8
     extern __shared__ uint8_t smem_raw[];
@@ -83,9 +92,9 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
     uint64_t* v_full = k_empty + STAGES;
     uint64_t* v_empty = v_full + STAGES;
     uint64_t* s_full = v_empty + STAGES;             // [2]
-    uint64_t* p_full = s_full + 2;
-    uint64_t* pv_done = p_full + 1;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+    uint64_t* p_full = s_full + 2;                   // [2]: the probabilities of step i lie in buffer i & 1
+    uint64_t* pv_done = p_full + 2;                  // [2]: P V of step i has read buffer i & 1 (and added into O)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
     __shared__ int failed, is_last;
     __shared__ float xmax[4 * AT_BM];              // the halves' maxima of a row, two steps deep; at the end their sums
 
@@ -109,8 +118,10 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
         for (int s = 0; s < STAGES; s++) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
         mbar_init(&s_full[0], 1);
         mbar_init(&s_full[1], 1);
-        mbar_init(p_full, 2 * AT_BM);
-        mbar_init(pv_done, 1);
+        mbar_init(&p_full[0], 2 * AT_BM);
+        mbar_init(&p_full[1], 2 * AT_BM);
+        mbar_init(&pv_done[0], 1);
+        mbar_init(&pv_done[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -189,18 +200,19 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
                 // the next step's scores go into the other buffer while the softmax warps work on this step's
                 if (i + 1 < n_it && !scores(i + 1)) break;
                 if (!mbar_wait(&v_full[i % STAGES], (i / STAGES) & 1, wc.cycles)) { give_up(wc.error, &failed, 20); break; }
-                if (!mbar_wait(p_full, i & 1, wc.cycles)) { give_up(wc.error, &failed, 14); break; }
+                if (!mbar_wait(&p_full[pbuf(i)], ppar(i), wc.cycles)) { give_up(wc.error, &failed, 14); break; }
+                const uint32_t pb = (uint32_t)pbuf(i) * P_BYTES;
                 tc_fence_after();
                 const uint32_t v_addr = smem_u32(smem + V_OFF + (i % STAGES) * KV_BYTES);
                 // 16 keys an instruction: two groups of eight 128-byte rows of the values
 #pragma unroll
                 for (int k = 0; k < AT_BN / 16; k++)
-                    umma_bf16(tmem_o, umma_desc_sw128(ph_addr + k * 32), umma_desc_sw128(v_addr + k * 2048), idesc_pv, (i | k) != 0);
+                    umma_bf16(tmem_o, umma_desc_sw128(ph_addr + pb + k * 32), umma_desc_sw128(v_addr + k * 2048), idesc_pv, (i | k) != 0);
 #pragma unroll
                 for (int k = 0; k < AT_BN / 16; k++)
-                    umma_bf16(tmem_o, umma_desc_sw128(pl_addr + k * 32), umma_desc_sw128(v_addr + k * 2048), idesc_pv, 1);
+                    umma_bf16(tmem_o, umma_desc_sw128(pl_addr + pb + k * 32), umma_desc_sw128(v_addr + k * 2048), idesc_pv, 1);
                 umma_commit(&v_empty[i % STAGES]);
-                umma_commit(pv_done);
+                umma_commit(&pv_done[pbuf(i)]);
             }
         }
     } else {
@@ -244,15 +256,13 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
             xmax[((i & 1) * 2 + half) * AT_BM + r] = mx;
             asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
             mx = fmaxf(mx, xmax[((i & 1) * 2 + (half ^ 1)) * AT_BM + r]);
-            bool pv_waited = false;
             if (i == 0) {
                 m = mx;                             // O is written, not added to, by the first step
             } else if (ok) {
                 const bool raise = mx > m + RAISE;  // also the first counted key after none (m = -inf)
                 if (__any_sync(0xffffffffu, raise)) {
                     // scale this warp's part of O (and the sums) to the new maxima; every earlier P V must have landed
-                    if (!__all_sync(0xffffffffu, mbar_wait(pv_done, (i - 1) & 1, wc.cycles))) { if (lane == 0) give_up(wc.error, &failed, 16); ok = false; }
-                    pv_waited = true;
+                    if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[pbuf(i - 1)], ppar(i - 1), wc.cycles))) { if (lane == 0) give_up(wc.error, &failed, 16); ok = false; }
                     if (ok) {
                         tc_fence_after();
                         const float alpha = raise ? at_ex2(m - mx) : 1.0f;
@@ -269,9 +279,11 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
                 }
             }
             const float m_use = m == -INFINITY ? 0.0f : m;
-            // the probabilities may only replace the last step's once its P V has read them
-            if (ok && i > 0 && !pv_waited) {
-                if (!__all_sync(0xffffffffu, mbar_wait(pv_done, (i - 1) & 1, wc.cycles))) { if (lane == 0) give_up(wc.error, &failed, 17); ok = false; }
+            // the probabilities of this step replace those of the step that had the buffer last, once its P V has read them
+            // (with two buffers that is the step before last, and the step before this one may still be under way)
+            const int had = DBUF ? i - 2 : i - 1;
+            if (ok && had >= 0) {
+                if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[pbuf(had)], ppar(had), wc.cycles))) { if (lane == 0) give_up(wc.error, &failed, 17); ok = false; }
             }
             if (ok) {
                 float sum = 0.0f;
@@ -288,8 +300,8 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
                         lo[j / 2] = at_pack(p0 - __bfloat162float(hv.x), p1 - __bfloat162float(hv.y));
                     }
                     const int chunk = (half * 4 + (j8 >> 3)) ^ (r & 7);      // 128-byte swizzle: 16-byte piece index xor row mod 8
-                    *reinterpret_cast<uint4*>(ph_row + chunk * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                    *reinterpret_cast<uint4*>(pl_row + chunk * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                    *reinterpret_cast<uint4*>(ph_row + pbuf(i) * P_BYTES + chunk * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<uint4*>(pl_row + pbuf(i) * P_BYTES + chunk * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                 }
                 l += sum;
                 // the values' rows beyond the last position (pages not loaded, slots not yet written): never counted,
@@ -304,13 +316,13 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attention_prefill_tcgen05_kerne
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P (and the zeros) are for the tensor core
                 tc_fence_before();
             }
-            mbar_arrive(p_full);
+            mbar_arrive(&p_full[pbuf(i)]);
         }
         // the row's sum is the two halves' (both against the same maximum)
         xmax[half * AT_BM + r] = l;
         asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
         l += xmax[(half ^ 1) * AT_BM + r];
-        if (ok && !__all_sync(0xffffffffu, mbar_wait(pv_done, (n_it - 1) & 1, wc.cycles))) { if (lane == 0) give_up(wc.error, &failed, 18); ok = false; }
+        if (ok && !__all_sync(0xffffffffu, mbar_wait(&pv_done[pbuf(n_it - 1)], ppar(n_it - 1), wc.cycles))) { if (lane == 0) give_up(wc.error, &failed, 18); ok = false; }
         uint32_t orr[32];
         if (ok) {
             tc_fence_after();
@@ -461,8 +473,9 @@ VK_API int vk_attention_prefill_tcgen05(const void* q, const void* cache, const 
     sc.part_steps = forced ? forced : cut ? AT_PART : (1 << 24);      // never below AT_PART: the scratch is laid out for that
     sc.parts = cut ? ((grid_context - 1) / AT_BN) / sc.part_steps + 1 : 1;
     if ((long long)n_tiles * sc.parts > 0x7fffffffll) return VK_TOO_LARGE;
-    const size_t smem = (size_t)AT_BM * 64 * 2 + 2 * AT_STAGES * AT_BN * 64 * 2 + 2 * AT_BM * AT_BN * 2 + 1024 + 256;
-    auto kern = attention_prefill_tcgen05_kernel<64>;
+    const bool dbuf = (long long)n_tiles * nh <= 148;       // no more blocks than multiprocessors: two buffers of probabilities
+    const size_t smem = (size_t)AT_BM * 64 * 2 + 2 * AT_STAGES * AT_BN * 64 * 2 + (dbuf ? 4 : 2) * AT_BM * AT_BN * 2 + 1024 + 256;
+    auto kern = dbuf ? attention_prefill_tcgen05_kernel<64, true> : attention_prefill_tcgen05_kernel<64, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     return launch_plain(kern, dim3(n_tiles * sc.parts, nh), dim3(AT_THREADS), smem, stream, mq, mkv, block_tables, tiles, (__nv_bfloat16*)out, nh,
