@@ -291,3 +291,54 @@ def test_toy_routed_feed_forward_and_learned_positions(tmp_path):
     runner.open("b")
     moved = runner.step([StepEntry("b", ids[1:2], [0])]).cpu().numpy()   # token ids[1] at position 0 instead of 1
     assert np.abs(moved[0] - whole[1]).max() > 1e-3
+
+
+def test_a_norm_defined_elsewhere_is_fused_if_it_says_it_is_rms_like():
+    """The built-in mixer and feed-forward apply a norm in their first kernel when the norm says that it has the RMS form
+    (Norm.as_rms), whatever its class; a norm of another form runs as a kernel of its own.  Both give what the plain
+    functions give."""
+    from vitna_anchor_b200 import ops
+    from vitna_anchor_b200.parts import Norm
+    from vitna_anchor_b200.parts.feed_forward import SwiGLU
+
+    class MyRms(Norm):                       # not the framework's class, but the same formula
+        def __init__(self, w, eps):
+            self.w, self.eps = w, eps
+
+        def as_rms(self):
+            return self.w, self.eps
+
+        def forward(self, x, ctx, name, rows=None):
+            out = ctx.workspace.rows(name, x.shape[0] if rows is None else rows.shape[0], x.shape[1], ctx.dtype)
+            return ops.rmsnorm_rows(x, self.w, self.eps, out, rows)
+
+    class ScaleOnly(Norm):                   # y = x * w: not of the RMS form
+        def __init__(self, w):
+            self.w = w
+
+        def forward(self, x, ctx, name, rows=None):
+            return (x * self.w).to(ctx.dtype)
+
+    H, I, T = 64, 96, 5
+    dtype = torch.bfloat16
+    rnd = lambda *s: (torch.randn(*s) * 0.3).to(dtype).float()
+    wg, wu, wd = rnd(I, H), rnd(I, H), rnd(H, I)
+    w = (1 + 0.1 * torch.randn(H)).float()
+    x = torch.randn(T, H) * 2
+    _, ctx = make_ctx([], [("a", 0, T)], dtype=dtype)
+    part = SwiGLU(H, I, torch.cat([wg, wu]).to(dtype).cuda(), wd.to(dtype).cuda())
+    rms, scale = MyRms(w.cuda(), 1e-5), ScaleOnly(w.cuda())
+    assert part.fuses_norm(rms, ctx) and not part.fuses_norm(scale, ctx)
+    fused = x.clone().cuda()
+    part.forward(fused, ctx, fused, norm=rms)                                   # the norm inside the first kernel
+    apart = x.clone().cuda()
+    part.forward(rms.forward(apart, ctx, "t.xn"), ctx, apart)                   # the norm as a kernel of its own
+    xn = torch.from_numpy(P.rms_norm(x.numpy(), w.numpy(), 1e-5)).to(dtype).float().numpy()
+    want = x.numpy() + P.swiglu(xn, wg.numpy(), wu.numpy(), wd.numpy(), rnd=P.bf16_round)
+    tol = 2e-2 * np.abs(want).max()
+    assert np.abs(fused.cpu().numpy() - want).max() <= tol and np.abs(apart.cpu().numpy() - want).max() <= tol
+    other = x.clone().cuda()
+    part.forward(scale.forward(other, ctx, "t.xn"), ctx, other)
+    xs = (x * w).to(dtype).float().numpy()
+    want2 = x.numpy() + P.swiglu(xs, wg.numpy(), wu.numpy(), wd.numpy(), rnd=P.bf16_round)
+    assert np.abs(other.cpu().numpy() - want2).max() <= 2e-2 * np.abs(want2).max()

@@ -151,6 +151,7 @@ __global__ void __launch_bounds__(DT_THREADS, 1) attention_decode_tma_kernel(con
     uint8_t* my_stages = smem + (size_t)warp * DT_STAGES * DT_STAGE_BYTES;
     uint64_t* my_bars = bars + warp * DT_STAGES;
 
+    int ipages = 0;                             // the pages of the unit the issuing cursor is in (lane j: the j-th of its split)
     // The chunk `c` of unit `it` into stage `s`: lane b asks for box b of the keys and of the values.
     auto issue = [&](const DtUnit& it, int c, int s) {
         const int kc0 = it.k0 + c * DT_CHUNK;
@@ -159,14 +160,21 @@ __global__ void __launch_bounds__(DT_THREADS, 1) attention_decode_tma_kernel(con
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the stage's last readers were this warp's own lanes
         if (lane == 0) mbar_expect_tx(&my_bars[s], (uint32_t)nb * box_rows * HD * 2 * 2);
         __syncwarp();
+        // the page of box `lane`: the split's pages were read once, lane j holding the j-th of them (see load_pages)
+        const int key = kc0 + lane * box_rows;
+        const int page = __shfl_sync(0xffffffffu, ipages, key / ps - it.k0 / ps);
         if (lane < nb) {
-            const int key = kc0 + lane * box_rows;
-            const int page = it.bt[key / ps];
             const int off = key % ps;
             uint8_t* dst = my_stages + (size_t)s * DT_STAGE_BYTES + lane * box_rows * (HD * 2);
             tma_load_2d(dst, &map_kv, 0, (page * 2 * a.nkv + it.kvh) * ps + off, &my_bars[s]);
             tma_load_2d(dst + DT_HALF_BYTES, &map_kv, 0, ((page * 2 + 1) * a.nkv + it.kvh) * ps + off, &my_bars[s]);
         }
+    };
+    // The pages of a unit's split (at most 32: pages hold at least 8 keys), lane j the j-th, in one trip: a trip to the
+    // block table for every chunk would stand between the warp and its next copy.
+    auto load_pages = [&](const DtUnit& it) -> int {
+        const int pg0 = it.k0 / ps, pg_end = min(it.pos, it.k0 + DT_SPLIT - 1) / ps;      // the split's pages that the request has
+        return pg0 + lane <= pg_end ? it.bt[pg0 + lane] : 0;
     };
     // The queries of the unit's heads as the 16-row operand: lane (gq, qd) holds rows gq and gq+8.
     auto load_q = [&](const DtUnit& it, uint32_t (*qf)[4]) {
@@ -188,6 +196,7 @@ __global__ void __launch_bounds__(DT_THREADS, 1) attention_decode_tma_kernel(con
     int ic = iunit.c0;
     uint32_t qn[KSTEPS][4];                     // the queries of the unit the issuing cursor has reached
     load_q(iunit, qn);
+    ipages = load_pages(iunit);
     int issued = 0, consumed = 0;               // chunks so far: stage = count % DT_STAGES, parity = (count / DT_STAGES) & 1
     int cu = my_first;                          // unit being consumed
     bool ok = true;
@@ -216,6 +225,7 @@ __global__ void __launch_bounds__(DT_THREADS, 1) attention_decode_tma_kernel(con
                 iunit = unit_of(iu);
                 ic = iunit.c0;
                 load_q(iunit, qn);
+                ipages = load_pages(iunit);
                 ipending = false;
             }
             while (!ipending && issued - consumed < DT_STAGES && iu < n_units) {
@@ -228,6 +238,7 @@ __global__ void __launch_bounds__(DT_THREADS, 1) attention_decode_tma_kernel(con
                     iunit = unit_of(iu);
                     ic = iunit.c0;
                     load_q(iunit, qn);
+                    ipages = load_pages(iunit);
                 }
             }
             const int s = consumed % DT_STAGES;
@@ -366,36 +377,42 @@ __global__ void __launch_bounds__(DT_THREADS, 1) attention_decode_tma_kernel(con
             }
             old = __shfl_sync(0xffffffffu, old, 0);
             if (old == it.n_active - 1) {
-                // the last to arrive folds the splits in split order, every lane its own output elements, eight splits a trip
-                for (int i = lane; i < it.gt * HD; i += 32) {
-                    const int h = i / HD, d = i % HD;
-                    const float2* ml = reinterpret_cast<const float2*>(a.part_ml) + ((size_t)it.zi * a.nh + it.h0 + h) * a.max_splits + it.first_split;
-                    const float* po = a.part_o + (((size_t)it.zi * a.nh + it.h0 + h) * a.max_splits + it.first_split) * HD + d;
-                    float mm = -INFINITY, ll = 0.0f, oo = 0.0f;
-                    for (int j0 = 0; j0 < it.n_active; j0 += 8) {
-                        float2 st[8];
-                        float pv[8];
+                // The last to arrive folds the splits in split order, a row at a time: a lane takes the row's output elements
+                // `lane` and `lane + 32`, and asks for the maxima, sums and partial outputs of sixteen splits in one trip.
+                for (int h = 0; h < it.gt; h++) {
+                    const size_t row = ((size_t)it.zi * a.nh + it.h0 + h) * a.max_splits + it.first_split;
+                    const float2* ml = reinterpret_cast<const float2*>(a.part_ml) + row;
+                    const float* po = a.part_o + row * HD + lane;
+                    float mm = -INFINITY, ll = 0.0f, o0 = 0.0f, o1 = 0.0f;
+                    for (int j0 = 0; j0 < it.n_active; j0 += 16) {
+                        float2 st[16];
+                        float p0[16], p1[16];
 #pragma unroll
-                        for (int j = 0; j < 8; j++) {
+                        for (int j = 0; j < 16; j++) {
                             const bool on = j0 + j < it.n_active;
                             st[j] = on ? __ldcg(ml + j0 + j) : make_float2(-INFINITY, 0.0f);
-                            pv[j] = on ? __ldcg(po + (size_t)(j0 + j) * HD) : 0.0f;
+                            p0[j] = on ? __ldcg(po + (size_t)(j0 + j) * HD) : 0.0f;
+                            p1[j] = on ? __ldcg(po + (size_t)(j0 + j) * HD + 32) : 0.0f;
                         }
                         float cm = mm;
 #pragma unroll
-                        for (int j = 0; j < 8; j++) cm = fmaxf(cm, st[j].x);
+                        for (int j = 0; j < 16; j++) cm = fmaxf(cm, st[j].x);
                         const float keep = mm == -INFINITY ? 0.0f : dt_ex2(mm - cm);       // maxima are in base 2
                         ll *= keep;
-                        oo *= keep;
+                        o0 *= keep;
+                        o1 *= keep;
 #pragma unroll
-                        for (int j = 0; j < 8; j++) {
+                        for (int j = 0; j < 16; j++) {
                             const float e = st[j].x == -INFINITY ? 0.0f : dt_ex2(st[j].x - cm);
                             ll += st[j].y * e;
-                            oo += pv[j] * e;
+                            o0 += p0[j] * e;
+                            o1 += p1[j] * e;
                         }
                         mm = cm;
                     }
-                    a.out[((size_t)it.t * a.nh + it.h0 + h) * HD + d] = __float2bfloat16_rn(oo / ll);
+                    __nv_bfloat16* dst = a.out + ((size_t)it.t * a.nh + it.h0 + h) * HD + lane;
+                    dst[0] = __float2bfloat16_rn(o0 / ll);
+                    dst[32] = __float2bfloat16_rn(o1 / ll);
                 }
             }
         }

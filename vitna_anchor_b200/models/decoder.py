@@ -15,8 +15,7 @@ from typing import List, Optional, Sequence
 import torch
 
 from ..cache.manager import CacheSpec
-from ..parts.base import Block, Norm, Part, PositionEncoding, StepContext
-from ..parts.embedding import Embedding, LMHead
+from ..parts.base import Block, LogitsOutput, Norm, Part, PositionEncoding, StepContext, TokenInput
 
 
 @dataclass(frozen=True)
@@ -27,8 +26,8 @@ class LayerRun:
 
 
 class DecoderModel:
-    def __init__(self, *, embedding: Embedding, blocks: Sequence[Block], schedule: Sequence[LayerRun], final_norm: Norm,
-                 lm_head: LMHead, position: Optional[PositionEncoding], dtype: torch.dtype, vocab_size: int,
+    def __init__(self, *, embedding: TokenInput, blocks: Sequence[Block], schedule: Sequence[LayerRun], final_norm: Norm,
+                 lm_head: LogitsOutput, position: Optional[PositionEncoding], dtype: torch.dtype, vocab_size: int,
                  max_positions: int, config=None):
         self.embedding, self.blocks, self.schedule = embedding, list(blocks), list(schedule)
         self.final_norm, self.lm_head, self.position = final_norm, lm_head, position

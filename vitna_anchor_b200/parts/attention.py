@@ -42,8 +42,7 @@ class PagedAttention(Mixer):
         return KVSpec(self.nkv, self.hd, self.window)
 
     def fuses_norm(self, norm, ctx: StepContext) -> bool:
-        from .norms import RMSNorm
-        return isinstance(norm, RMSNorm) and ops.fused_norm_takes(ctx.dtype, ctx.num_tokens, self.hidden, self.qd + 2 * self.kvd)
+        return norm.as_rms() is not None and ops.fused_norm_takes(ctx.dtype, ctx.num_tokens, self.hidden, self.qd + 2 * self.kvd)
 
     def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCacheView, residual: torch.Tensor,
                 write_cache: bool = True, norm=None) -> None:
@@ -55,7 +54,8 @@ class PagedAttention(Mixer):
         q_buf = ws.rows("att.q", T, self.qd, ctx.dtype)
         if norm is not None and rot == self.hd and write_cache:
             # few rows: norm, the three projections, the rotation and the cache write in one launch
-            q = ops.linear_skinny(xn, self.wqkv, q_buf, ops.EPI_ROPE, norm_weight=norm.weight, eps=norm.eps,
+            nw, eps = norm.as_rms()
+            q = ops.linear_skinny(xn, self.wqkv, q_buf, ops.EPI_ROPE, norm_weight=nw, eps=eps,
                                   rope=(ctx.positions, cos, sin, meta.slot_mapping, cache.pages, self.nh, self.nkv, self.hd))
         elif (norm is None and rot == self.hd and write_cache and xn.stride(0) % 8 == 0 and xn.data_ptr() % 16 == 0
               and ops.skinny_takes(ctx.dtype, T, self.hidden, self.qd + 2 * self.kvd)):
@@ -70,7 +70,8 @@ class PagedAttention(Mixer):
         else:
             qkv_buf = ws.rows("att.qkv", T, self.qd + 2 * self.kvd, ctx.dtype)
             if norm is not None:
-                qkv = ops.linear_skinny(xn, self.wqkv, qkv_buf, ops.EPI_SAME, norm_weight=norm.weight, eps=norm.eps)
+                nw, eps = norm.as_rms()
+                qkv = ops.linear_skinny(xn, self.wqkv, qkv_buf, ops.EPI_SAME, norm_weight=nw, eps=eps)
             else:
                 qkv = ops.linear(xn, self.wqkv, qkv_buf, ops.LINEAR_SAME)
             q = ops.rope_store(qkv, ctx.positions, cos, sin, meta.slot_mapping, q_buf, cache.pages if write_cache else None,

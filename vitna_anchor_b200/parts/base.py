@@ -120,6 +120,36 @@ class Norm(Part):
         """x float32 [T, width] -> compute dtype [T or len(rows), width]."""
         raise NotImplementedError
 
+    def as_rms(self):
+        """(weight float32 [width], eps) if this norm is y = x / sqrt(mean(x^2) + eps) * weight, else None.  A part whose
+        first kernel can apply such a norm itself (fuses_norm) asks this, not for a class, so that any norm of
+        that form may be fused."""
+        return None
+
+
+class TokenInput(Part):
+    """What turns a batch's token ids into the float32 residual stream."""
+
+    def forward(self, ctx: StepContext) -> torch.Tensor:
+        """-> float32 [T, hidden]"""
+        raise NotImplementedError
+
+
+class LogitsOutput(Part):
+    """What turns normed activations into float32 logits."""
+
+    def forward(self, xn: torch.Tensor, ctx: StepContext, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """xn [R, hidden] in the compute dtype -> float32 [R, vocab] (in `out`, or a new tensor)."""
+        raise NotImplementedError
+
+    def fuses_norm(self, norm: "Norm", ctx: StepContext, rows: int) -> bool:
+        """Whether forward_normed can apply `norm` itself for this many rows."""
+        return False
+
+    def forward_normed(self, x: torch.Tensor, rows: torch.Tensor, norm: "Norm", ctx: StepContext,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
 
 class PositionEncoding(Part):
     """Either rotation tables that the mixer applies to q and k, or a change to the embeddings, or both."""

@@ -11,10 +11,10 @@ from typing import Optional
 import torch
 
 from .. import ops
-from .base import Part, StepContext
+from .base import LogitsOutput, StepContext, TokenInput
 
 
-class Embedding(Part):
+class Embedding(TokenInput):
     def __init__(self, vocab: int, hidden: int, table: torch.Tensor):
         if table.shape != (vocab, hidden):
             raise ValueError("the embedding table does not fit the sizes")
@@ -28,7 +28,7 @@ class Embedding(Part):
         return ops.embed_rows(self.table, ctx.tokens, x)
 
 
-class LMHead(Part):
+class LMHead(LogitsOutput):
     def __init__(self, vocab: int, hidden: int, weight: torch.Tensor):
         if weight.shape != (vocab, hidden):
             raise ValueError("the output matrix does not fit the sizes")
@@ -49,11 +49,10 @@ class LMHead(Part):
         return ops.linear(xn, self.weight, self._out(xn.shape[0], out, xn.device), ops.LINEAR_F32)
 
     def fuses_norm(self, norm, ctx: StepContext, rows: int) -> bool:
-        from .norms import RMSNorm
-        return isinstance(norm, RMSNorm) and ops.fused_norm_takes(ctx.dtype, rows, self.hidden, self.vocab)
+        return norm.as_rms() is not None and ops.fused_norm_takes(ctx.dtype, rows, self.hidden, self.vocab)
 
     def forward_normed(self, x: torch.Tensor, rows: torch.Tensor, norm, ctx: StepContext,
                        out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """logits of rmsnorm(x[rows]) in one launch (few rows); x is the float32 residual stream."""
-        return ops.linear_skinny(x, self.weight, self._out(rows.shape[0], out, x.device), ops.EPI_F32, norm_weight=norm.weight,
-                                 eps=norm.eps, rows=rows)
+        nw, eps = norm.as_rms()
+        return ops.linear_skinny(x, self.weight, self._out(rows.shape[0], out, x.device), ops.EPI_F32, norm_weight=nw, eps=eps, rows=rows)

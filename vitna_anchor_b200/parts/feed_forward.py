@@ -20,8 +20,7 @@ class SwiGLU(FeedForward):
         return [self.w_gate_up, self.w_down]
 
     def fuses_norm(self, norm, ctx: StepContext) -> bool:
-        from .norms import RMSNorm
-        return isinstance(norm, RMSNorm) and ops.fused_norm_takes(ctx.dtype, ctx.num_tokens, self.hidden, 2 * self.intermediate)
+        return norm.as_rms() is not None and ops.fused_norm_takes(ctx.dtype, ctx.num_tokens, self.hidden, 2 * self.intermediate)
 
     def forward(self, xn: torch.Tensor, ctx: StepContext, residual: torch.Tensor, norm=None) -> None:
         T = ctx.num_tokens
@@ -29,7 +28,8 @@ class SwiGLU(FeedForward):
         act_buf = ws.rows("ffn.act", T, self.intermediate, ctx.dtype)
         if norm is not None:
             # few rows: norm, gate and up, and silu(gate) * up in one launch
-            act = ops.linear_skinny(xn, self.w_gate_up, act_buf, ops.EPI_SWIGLU, norm_weight=norm.weight, eps=norm.eps)
+            nw, eps = norm.as_rms()
+            act = ops.linear_skinny(xn, self.w_gate_up, act_buf, ops.EPI_SWIGLU, norm_weight=nw, eps=eps)
         elif (xn.stride(0) % 8 == 0 and xn.data_ptr() % 16 == 0
               and ops.skinny_takes(ctx.dtype, T, self.hidden, 2 * self.intermediate)):
             # a few dozen rows: the norm ran once for all of them; gate, up and silu(gate) * up in one launch

@@ -19,6 +19,9 @@ class RMSNorm(Norm):
     def tensors(self):
         return [self.weight]
 
+    def as_rms(self):
+        return self.weight, self.eps
+
     def forward(self, x: torch.Tensor, ctx: StepContext, name: str, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         n = x.shape[0] if rows is None else rows.shape[0]
         out = ctx.workspace.rows(name, n, self.width, ctx.dtype)
