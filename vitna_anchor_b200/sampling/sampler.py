@@ -19,10 +19,19 @@ from .params import SamplingParams, SplitMix64
 class Sampler:
     def __init__(self, vocab: int, max_rows: int, device):
         self.vocab, self.max_rows, self.device = vocab, max_rows, torch.device(device)
-        self._out = torch.empty(max_rows, dtype=torch.int32, device=self.device)
-        self._f32 = torch.empty(2 * max_rows, dtype=torch.float32, device=self.device)      # temperature, top_p
-        self._i32 = torch.empty(max_rows, dtype=torch.int32, device=self.device)            # top_k
-        self._f64 = torch.empty(max_rows, dtype=torch.float64, device=self.device)          # uniforms
+        m = max_rows
+        self._out = torch.empty(m, dtype=torch.int32, device=self.device)
+        # the rows' settings in one device buffer, filled by ONE copy from pinned host memory:
+        # uniforms (float64), temperature, top_p (float32), top_k (int32), max_rows of each
+        self._dev = torch.empty(20 * m, dtype=torch.uint8, device=self.device)
+        self._f64 = self._dev[:8 * m].view(torch.float64)
+        self._temp = self._dev[8 * m:12 * m].view(torch.float32)
+        self._top_p = self._dev[12 * m:16 * m].view(torch.float32)
+        self._top_k = self._dev[16 * m:20 * m].view(torch.int32)
+        self._host = [torch.empty(20 * m, dtype=torch.uint8).pin_memory() for _ in range(4)]
+        self._host_np = [h.numpy() for h in self._host]
+        self._events = [None] * 4
+        self._turn = 0
         self._probs = None   # scratch [max_rows, vocab], made when a sampled row first appears
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], rngs: Sequence[SplitMix64]) -> List[int]:
@@ -42,11 +51,17 @@ class Sampler:
             return ops.argmax_rows(logits, out)
         if self._probs is None:
             self._probs = torch.empty(self.max_rows * self.vocab, dtype=torch.float32, device=self.device)
-        temp = np.array([p.temperature for p in params], dtype=np.float32)
-        top_p = np.array([p.top_p for p in params], dtype=np.float32)
-        top_k = np.array([p.top_k for p in params], dtype=np.int32)
-        u = np.array([0.0 if p.greedy else rngs[i].uniform() for i, p in enumerate(params)], dtype=np.float64)
-        self._f32[:R].copy_(torch.from_numpy(temp)); self._f32[self.max_rows:self.max_rows + R].copy_(torch.from_numpy(top_p))
-        self._i32[:R].copy_(torch.from_numpy(top_k)); self._f64[:R].copy_(torch.from_numpy(u))
-        return ops.sample_rows(logits, self._f32[:R], self._i32[:R], self._f32[self.max_rows:self.max_rows + R], self._f64[:R],
-                               self._probs, out)
+        m, t = self.max_rows, self._turn
+        self._turn = (t + 1) % len(self._host)
+        if self._events[t] is not None:
+            self._events[t].synchronize()        # the copy that last used this staging buffer is done
+        buf = self._host_np[t]
+        buf[:8 * m].view(np.float64)[:R] = [0.0 if p.greedy else rngs[i].uniform() for i, p in enumerate(params)]
+        buf[8 * m:12 * m].view(np.float32)[:R] = [p.temperature for p in params]
+        buf[12 * m:16 * m].view(np.float32)[:R] = [p.top_p for p in params]
+        buf[16 * m:20 * m].view(np.int32)[:R] = [p.top_k for p in params]
+        self._dev.copy_(self._host[t], non_blocking=True)
+        if self._events[t] is None:
+            self._events[t] = torch.cuda.Event()
+        self._events[t].record()
+        return ops.sample_rows(logits, self._temp[:R], self._top_k[:R], self._top_p[:R], self._f64[:R], self._probs, out)
