@@ -50,6 +50,7 @@ struct AtScratch {
     int* counters;
     int parts;                       // parts a tile can have in this launch (the grid's width is tiles * parts)
     int part_steps;                  // key steps of a part (AT_PART; an experiment may set another through VITNA_ATT_PART)
+    int n_tiles;
 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -99,17 +100,20 @@ __global__ void __launch_bounds__(AT_THREADS, DBUF ? 1 : 2) attention_prefill_tc
     __shared__ float xmax[4 * AT_BM];              // the halves' maxima of a row, two steps deep; at the end their sums
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int unit = gridDim.x - 1 - blockIdx.x;     // later tiles of a prompt have more keys: start them first
-    const int tile = unit / sc.parts, part = unit % sc.parts;
-    const int h = blockIdx.y;
+    // Blocks in the order of their tiles, last tile first, all heads and parts of a tile together: later tiles of a
+    // prompt walk over more keys, and a launch ends sooner when its longest blocks start first.  (Measured at 32 heads
+    // and 2,048 tokens: 84 -> 62 microseconds against the order head by head.)
+    const int per_tile = sc.parts * nh;
+    const int tile = sc.n_tiles - 1 - blockIdx.x / per_tile, part = (blockIdx.x % per_tile) / nh;
+    const int h = blockIdx.x % nh;
     const int kvh = h / (nh / nkv);
     const int tok0 = tiles[tile * 4 + 0], rows = tiles[tile * 4 + 1], pos0 = tiles[tile * 4 + 2], seg = tiles[tile * 4 + 3];
     const int last_pos = pos0 + rows - 1;
     const int lo_first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;     // lowest key any row needs
     const int kt_first = lo_first / AT_BN, kt1 = last_pos / AT_BN;      // the tile's walk: key steps kt_first .. kt1
-    const int n_parts = (kt1 - kt_first) / sc.part_steps + 1;                 // parts of this tile
+    const int n_parts = (kt1 - kt_first) / sc.part_steps + 1;           // parts of this tile
     if (part >= n_parts) return;                                        // the whole block: nothing to do
-    const int kt0 = kt_first + part * sc.part_steps;                          // this block's steps: kt0 .. kt0 + n_it - 1
+    const int kt0 = kt_first + part * sc.part_steps;                    // this block's steps: kt0 .. kt0 + n_it - 1
     const int n_it = min(sc.part_steps, kt1 - kt0 + 1);
 
     if (threadIdx.x == 0) {
@@ -472,12 +476,13 @@ VK_API int vk_attention_prefill_tcgen05(const void* q, const void* cache, const 
     const bool cut = forced || (long long)n_tiles * nh * 4 <= (long long)148 * 3;
     sc.part_steps = forced ? forced : cut ? AT_PART : (1 << 24);      // never below AT_PART: the scratch is laid out for that
     sc.parts = cut ? ((grid_context - 1) / AT_BN) / sc.part_steps + 1 : 1;
-    if ((long long)n_tiles * sc.parts > 0x7fffffffll) return VK_TOO_LARGE;
+    sc.n_tiles = n_tiles;
+    if ((long long)n_tiles * sc.parts * nh > 0x7fffffffll) return VK_TOO_LARGE;
     const bool dbuf = (long long)n_tiles * nh <= 148;       // no more blocks than multiprocessors: two buffers of probabilities
     const size_t smem = (size_t)AT_BM * 64 * 2 + 2 * AT_STAGES * AT_BN * 64 * 2 + (dbuf ? 4 : 2) * AT_BM * AT_BN * 2 + 1024 + 256;
     auto kern = dbuf ? attention_prefill_tcgen05_kernel<64, true> : attention_prefill_tcgen05_kernel<64, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    return launch_plain(kern, dim3(n_tiles * sc.parts, nh), dim3(AT_THREADS), smem, stream, mq, mkv, block_tables, tiles, (__nv_bfloat16*)out, nh,
+    return launch_plain(kern, dim3(n_tiles * sc.parts * nh), dim3(AT_THREADS), smem, stream, mq, mkv, block_tables, tiles, (__nv_bfloat16*)out, nh,
                         nkv, page_size, max_blocks, scale, window, wait_ctl(error, WAIT_FAMILY_ATTENTION_PREFILL), sc);
 }

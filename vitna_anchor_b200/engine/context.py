@@ -121,12 +121,17 @@ class ContextBuilder:
         pre = [t for i in range(S) if lens[i] > 1 for t in range(int(seg_starts[i]), int(seg_starts[i + 1]))]
         s_dec = put(np.asarray(dec, dtype=np.int32), len(dec)) if dec else None
         s_pre = put(np.asarray(pre, dtype=np.int32), len(pre)) if pre and dec else None
+        # tiles in the order of the keys they walk over, longest walk LAST (the kernels start from the end of the list):
+        # a launch ends sooner when its longest blocks start first, and in a batch of several prompts the longest walks
+        # are not those of the last prompt
         tiles = [(int(seg_starts[i]) + o, min(64, lens[i] - o), first[i] + o, i)
                  for i in range(S) if lens[i] > 1 for o in range(0, lens[i], 64)]
+        tiles.sort(key=lambda t: t[2] + t[1])
         off = (off + 3) & ~3                                   # 16-byte alignment for what follows
         s_tiles = put(np.asarray(tiles, dtype=np.int32).reshape(-1), 4 * len(tiles)) if tiles else None
         big = [(int(seg_starts[i]) + o, min(128, lens[i] - o), first[i] + o, i)
                for i in range(S) if lens[i] > 1 for o in range(0, lens[i], 128)]
+        big.sort(key=lambda t: t[2] + t[1])
         s_big = put(np.asarray(big, dtype=np.int32).reshape(-1), 4 * len(big)) if big else None
         group_slices = []
         for g in range(len(self.cache.groups)):

@@ -26,7 +26,9 @@ def lib() -> ctypes.CDLL:
     """The loaded kernel library; built at the first call if need be."""
     global _lib
     if _lib is None:
-        path = _build.library_path(build=True)
+        # VITNA_KERNEL_LIB names a library that was built elsewhere from these sources (a read-only installation, a build
+        # with other compiler flags); otherwise the in-tree library, compiled now if it is missing or out of date
+        path = os.environ.get("VITNA_KERNEL_LIB") or _build.library_path(build=True)
         try:
             _lib = ctypes.CDLL(path)
         except OSError as e:
