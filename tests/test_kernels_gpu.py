@@ -708,3 +708,65 @@ def test_attention_decode_tma_streams_the_pages(ops, nh, nkv, ps, window, lens):
     finally:
         ops.set_decode_tma(before)
     assert np.abs(outs[1] - outs[0]).max() <= 1e-2 * scale
+
+
+def _rope_oracle(x, w, positions, cos, sin, slots, nh, nkv, hd, ps, pages):
+    """q rotated [M, nh*hd] and the cache [pages, 2, nkv, ps, hd] (7.0 where nothing is written), in float64 from bfloat16
+    inputs, rounding where the kernels store: the products to bfloat16, then the rotated values to bfloat16."""
+    M = x.shape[0]
+    qkv = P.bf16_round((x.astype(np.float64) @ w.astype(np.float64).T).astype(np.float32))
+    q = qkv[:, :nh * hd].reshape(M, nh, hd)
+    k = qkv[:, nh * hd:(nh + nkv) * hd].reshape(M, nkv, hd)
+    v = qkv[:, (nh + nkv) * hd:].reshape(M, nkv, hd)
+    c, s = cos[positions], sin[positions]
+    q_rot = P.bf16_round(P.rope_half(q, c, s)).reshape(M, nh * hd)
+    k_rot = P.bf16_round(P.rope_half(k, c, s))
+    cache = np.full((pages, 2, nkv, ps, hd), 7.0, np.float32)
+    for m, sl in enumerate(slots):
+        if sl >= 0:
+            cache[sl // ps, 0, :, sl % ps] = k_rot[m]
+            cache[sl // ps, 1, :, sl % ps] = v[m]
+    return q_rot, cache
+
+
+@pytest.mark.parametrize("kind,nh,nkv,hd,ps,M,K", [("skinny", 9, 3, 64, 16, 6, 576), ("skinny", 4, 1, 128, 8, 40, 256),
+                                                   ("skinny_norm", 9, 3, 64, 16, 5, 576), ("tcgen05", 9, 3, 64, 16, 300, 576),
+                                                   ("tcgen05", 4, 2, 128, 8, 130, 256), ("tcgen05", 32, 32, 64, 16, 1100, 2048)])
+def test_fused_rotary_epilogues_against_a_plain_statement(ops, kind, nh, nkv, hd, ps, M, K):
+    """The projections with the rotation and the cache write in their epilogue (few-rows kernel, with and without the
+    fused norm; tcgen05 product, narrow and wide): q and every slot of the cache against float64 products rounded where
+    the kernels round; slots that are not named stay as they were, a token with slot -1 writes nothing."""
+    rng = np.random.default_rng(nh + M)
+    N = (nh + 2 * nkv) * hd
+    pages = -(-M // ps) + 3
+    to_bf = lambda a: torch.from_numpy(a.astype(np.float32)).to(torch.bfloat16)
+    w_t = to_bf(rng.standard_normal((N, K)) / math.sqrt(K) * 2)
+    positions = rng.integers(0, 900, M).astype(np.int32)
+    cos, sin = P.rope_tables(np.arange(1000), hd, 100000.0)
+    slots = rng.permutation(pages * ps)[:M].astype(np.int32)
+    slots[min(5, M - 1)] = -1
+    cache = torch.full((pages, 2, nkv, ps, hd), 7.0, dtype=torch.bfloat16, device="cuda")
+    q_out = torch.empty(M, nh * hd, dtype=torch.bfloat16, device="cuda")
+    if kind == "skinny_norm":
+        xf = (rng.standard_normal((M, K)) * 2).astype(np.float32)
+        nw = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+        x_np = P.bf16_round(P.rms_norm(xf, nw, 1e-5))
+        ops.linear_skinny(dev(xf), w_t.cuda(), q_out, ops.EPI_ROPE, norm_weight=dev(nw), eps=1e-5,
+                          rope=(dev(positions), dev(cos), dev(sin), dev(slots), cache, nh, nkv, hd))
+    else:
+        x_t = to_bf(rng.standard_normal((M, K)))
+        x_np = x_t.float().numpy()
+        if kind == "skinny":
+            ops.linear_skinny(x_t.cuda(), w_t.cuda(), q_out, ops.EPI_ROPE,
+                              rope=(dev(positions), dev(cos), dev(sin), dev(slots), cache, nh, nkv, hd))
+        else:
+            ops.linear_tcgen05_rope(x_t.cuda(), w_t.cuda(), q_out, dev(positions), dev(cos), dev(sin), dev(slots), cache, nh, nkv, hd)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    want_q, want_cache = _rope_oracle(x_np, w_t.float().numpy(), positions, cos, sin, slots, nh, nkv, hd, ps, pages)
+    got_q, got_cache = q_out.float().cpu().numpy(), cache.float().cpu().numpy()
+    # one bfloat16 step of the largest value: a float32 sum that lands on the other side of a rounding point
+    t = 2 ** -7 * max(1.0, float(np.abs(want_q).max()))
+    assert np.abs(got_q - want_q).max() <= t
+    assert np.array_equal(got_cache == 7.0, want_cache == 7.0)          # the same slots were written, no others
+    assert np.abs(got_cache - want_cache).max() <= t

@@ -121,3 +121,26 @@ def test_a_prompt_is_cut_where_the_free_pages_end():
     s.add(a); s.add(b)
     p = s.schedule()
     assert [(x.request.request_id, len(x.tokens), x.samples) for x in p] == [("a", 6, True), ("b", 8, False)]
+
+
+def test_the_metadata_buffer_holds_the_largest_legal_step():
+    """The step function's metadata buffer is sized by a bound (meta_words); whatever mixture of segments a step may
+    legally hold must fit it: many segments of two tokens at small limits, all tokens wanted, wide block tables."""
+    import random
+    from vitna_anchor_b200.engine.context import meta_words, words_used
+    rng = random.Random(0)
+    for max_tokens, max_segments, max_blocks, groups in [(16, 8, 4, 1), (17, 16, 64, 2), (64, 64, 2, 1), (2048, 64, 512, 1),
+                                                         (130, 40, 3, 3), (5, 64, 8, 1)]:
+        bound = meta_words(max_tokens, max_segments, max_blocks, groups)
+        S = min(max_segments, max_tokens // 2)
+        cases = [[2] * S + ([max_tokens - 2 * S] if max_tokens - 2 * S and S < max_segments else []),      # segments of two tokens
+                 [1] * min(max_segments, max_tokens), [max_tokens]]
+        for _ in range(200):
+            lens, left = [], max_tokens
+            while left and len(lens) < max_segments:
+                n = rng.choice([1, 2, 3, 63, 64, 65, 127, 128, 129, left])
+                n = max(1, min(n, left))
+                lens.append(n); left -= n
+            cases.append(lens)
+        for lens in cases:
+            assert words_used(lens, sum(lens), max_blocks, groups) <= bound, (max_tokens, max_segments, lens)

@@ -44,6 +44,18 @@ def meta_words(max_tokens: int, max_segments: int, max_blocks: int, n_groups: in
     return 3 * T + (S + 1) + 2 * S + T + S + T + 3 + 4 * tiles64 + 4 * tiles128 + n_groups * (T + S * max_blocks)
 
 
+def words_used(lens: Sequence[int], wanted: int, max_blocks: int, n_groups: int) -> int:
+    """The words build() puts for segments of these lengths with `wanted` rows in all and block tables `max_blocks` wide
+    (the same terms in the same order; tests hold it against meta_words)."""
+    T, S = sum(lens), len(lens)
+    dec = sum(1 for n in lens if n == 1)
+    pre = sum(n for n in lens if n > 1)
+    off = 3 * T + (S + 1) + 2 * S + wanted + dec + (pre if dec else 0)
+    off = (off + 3) & ~3
+    off += 4 * sum(-(-n // 64) for n in lens if n > 1) + 4 * sum(-(-n // 128) for n in lens if n > 1)
+    return off + n_groups * (T + S * max_blocks)
+
+
 class ContextBuilder:
     def __init__(self, cache: CacheManager, dtype: torch.dtype, workspace: Workspace, *, max_batch_tokens: int,
                  max_segments: int, max_model_len: int, device):
