@@ -427,6 +427,59 @@ def test_linear_skinny_rope_store_matches_the_separate_kernels(ops, dtype, nh, n
     assert torch.equal(cache_a == 7.0, cache_b == 7.0)        # the same slots were written, no others
 
 
+@pytest.mark.parametrize("M,N,K", [(8, 5000, 2048), (3, 700, 8192), (16, 4100, 960), (40, 1200, 576), (5, 130, 8224), (7, 40, 544),
+                                   (1, 18, 64), (64, 960, 1536), (11, 333, 12288)])
+def test_the_streaming_few_rows_kernel_gives_the_bits_of_the_plain_one(ops, M, N, K):
+    """The streaming kernel (weights kept on their way across tiles) against the tensor-core few-rows kernel that asks
+    tile by tile, every epilogue, forced on at sizes its own rule would not take: the same bits, and both near float64."""
+    dtype = torch.bfloat16
+    gen = torch.Generator().manual_seed(M * 7 + N)
+    x = torch.randn(M, K, generator=gen).to(dtype).cuda()
+    xf = (torch.randn(M + 3, K, generator=gen) * 2).cuda()
+    nw = (1 + 0.1 * torch.randn(K, generator=gen)).cuda()
+    rows = torch.randperm(M + 3, generator=gen)[:M].to(torch.int32).cuda()
+    N2 = N + (N % 2)
+    w = (torch.randn(N2, K, generator=gen) / math.sqrt(K)).to(dtype).cuda()
+    fused = ops.fused_norm_takes(dtype, M, K, N2)
+    nh, nkv, hd, ps = 3, 1, 16, 4
+    wq = (torch.randn((nh + 2 * nkv) * hd, K, generator=gen) / math.sqrt(K)).to(dtype).cuda()
+    positions = dev(np.arange(M, dtype=np.int32) * 3)
+    cos, sin = P.rope_tables(np.arange(3 * M + 1), hd, 10000.0)
+    slots = dev(np.random.default_rng(M).permutation(M * 2)[:M].astype(np.int32))
+
+    def run(mode):
+        was = ops.set_skinny_stream(mode)
+        try:
+            outs = []
+            f32 = torch.empty(M, N2, device="cuda")
+            ops.linear_skinny(x, w, f32, ops.EPI_F32); outs.append(f32)
+            acc = torch.ones(M, N2, device="cuda")
+            ops.linear_skinny(x, w, acc, ops.EPI_ACC); outs.append(acc)
+            same = torch.empty(M, N2, dtype=dtype, device="cuda")
+            ops.linear_skinny(x, w, same, ops.EPI_SAME); outs.append(same)
+            sw = torch.empty(M, N2 // 2, dtype=dtype, device="cuda")
+            ops.linear_skinny(x, w, sw, ops.EPI_SWIGLU); outs.append(sw)
+            cache = torch.full((M, 2, nkv, ps, hd), 7.0, dtype=dtype, device="cuda")
+            q = torch.empty(M, nh * hd, dtype=dtype, device="cuda")
+            ops.linear_skinny(x, wq, q, ops.EPI_ROPE, rope=(positions, dev(cos), dev(sin), slots, cache, nh, nkv, hd))
+            outs += [q, cache]
+            if fused:
+                nf = torch.empty(M, N2, device="cuda")
+                ops.linear_skinny(xf, w, nf, ops.EPI_F32, norm_weight=nw, eps=1e-5, rows=rows); outs.append(nf)
+                ns = torch.empty(M, N2 // 2, dtype=dtype, device="cuda")
+                ops.linear_skinny(xf, w, ns, ops.EPI_SWIGLU, norm_weight=nw, eps=1e-5, rows=rows); outs.append(ns)
+            torch.cuda.synchronize()
+            return outs
+        finally:
+            ops.set_skinny_stream(was)
+
+    plain, stream = run(0), run(1)
+    for i, (a, b) in enumerate(zip(plain, stream)):
+        assert torch.equal(a, b), (i, float((a.float() - b.float()).abs().max()))
+    want = x.double() @ w.double().T
+    assert (stream[0].double() - want).abs().max() <= 2e-5 * float(want.abs().max())
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 64, 64), (128, 128, 576), (2048, 960, 576), (300, 576, 1536), (65, 200, 72), (1000, 3072, 576),
                                    (257, 49152, 576), (130, 72, 200), (700, 1100, 520), (1500, 2048, 2048)])   # the last three of the big ones: 128 x 256 tiles
 def test_linear_tcgen05(ops, M, N, K):

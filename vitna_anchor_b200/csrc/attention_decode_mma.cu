@@ -98,8 +98,12 @@ __device__ __forceinline__ uint32_t dm_pack(float x, float y) {
 // pages of the warp's keys are read from the block table in one trip (lane p reads the p-th of them) and handed
 // round by shuffle: a trip to memory per copy was a third of the block's time.  Rows that do not count are zeroed
 // (never counted, p = 0, but 0 * garbage must not be NaN).  No commit.
+//
+// The key and value at the token's own position are left out: they are what the kernel before this one writes, and
+// this copy runs before the wait for that kernel (dm_copy_own brings them afterwards).  Every earlier key of the
+// request was written by an earlier step.  Returns the page of the token's own position (to every lane).
 template <int HD>
-__device__ __forceinline__ void dm_copy_warp(const DmArgs& a, const DmItem& it, __nv_bfloat16* sk, __nv_bfloat16* sv) {
+__device__ __forceinline__ int dm_copy_warp(const DmArgs& a, const DmItem& it, __nv_bfloat16* sk, __nv_bfloat16* sv) {
     typedef __nv_bfloat16 T;
     constexpr int LD = HD + 8, CH = HD / 8;             // CH pieces of 16 bytes a row
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -119,15 +123,33 @@ __device__ __forceinline__ void dm_copy_warp(const DmArgs& a, const DmItem& it, 
         T* dk = sk + kl * LD + part * 8;
         T* dv = sv + kl * LD + part * 8;
         if (kl < it.nkeys && key >= it.lo) {
-            const int off = key - pg * a.page_size;
-            const T* kr = a.cache + (size_t)page * page_stride + ((size_t)it.kvh * a.page_size + off) * HD + part * 8;
-            dm_cp_async16(dk, kr);
-            dm_cp_async16(dv, kr + v_off);
+            if (key < it.pos) {
+                const int off = key - pg * a.page_size;
+                const T* kr = a.cache + (size_t)page * page_stride + ((size_t)it.kvh * a.page_size + off) * HD + part * 8;
+                dm_cp_async16(dk, kr);
+                dm_cp_async16(dv, kr + v_off);
+            }
         } else {
             *reinterpret_cast<uint4*>(dk) = make_uint4(0, 0, 0, 0);
             *reinterpret_cast<uint4*>(dv) = make_uint4(0, 0, 0, 0);
         }
     }
+    return __shfl_sync(0xffffffffu, my_page, min(max(pg_last - pg0, 0), 31));
+}
+
+// The key and value at the token's own position, for the warp whose 32 keys hold it: lanes 0 .. HD/8-1 copy a piece each.
+template <int HD>
+__device__ __forceinline__ void dm_copy_own(const DmArgs& a, const DmItem& it, int own_page, __nv_bfloat16* sk, __nv_bfloat16* sv) {
+    typedef __nv_bfloat16 T;
+    constexpr int LD = HD + 8, CH = HD / 8;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int kl = it.pos - it.k0;
+    if (kl < warp * 32 || kl >= warp * 32 + 32 || lane >= CH) return;
+    const int pg = a.page_shift >= 0 ? it.pos >> a.page_shift : it.pos / a.page_size;
+    const int off = it.pos - pg * a.page_size;
+    const T* kr = a.cache + (size_t)own_page * 2 * a.nkv * a.page_size * HD + ((size_t)it.kvh * a.page_size + off) * HD + lane * 8;
+    dm_cp_async16(sk + kl * LD + lane * 8, kr);
+    dm_cp_async16(sv + kl * LD + lane * 8, kr + (size_t)a.nkv * a.page_size * HD);
 }
 
 // The queries of the item's heads as the 16-row operand of m16n8k16, straight from global memory into registers
@@ -180,12 +202,16 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 3 : 1) attention_decode
     // keys of this warp: wk0 .. wk0+31; the warp has work if one of them counts
     const int wk0 = k0 + warp * 32;
     const bool warp_on = wk0 <= pos && wk0 + 31 >= lo;
-    dependency_wait();                          // q and the cache come from the kernels before this one
+    // The keys and values of earlier steps are asked for before the wait: they are most of what a block reads,
+    // and the kernel before this one writes the token's own key and value only.
+    int own_page = 0;
+    if (warp_on) own_page = dm_copy_warp<HD>(a, it, sk, sv);
+    dependency_wait();                          // q and the token's own key and value come from the kernel before this one
     let_dependents_start();
 
     float* wo = reinterpret_cast<float*>(sk + warp * 32 * LD);       // [16][HD], over the warp's own keys
     if (warp_on) {
-        dm_copy_warp<HD>(a, it, sk, sv);
+        dm_copy_own<HD>(a, it, own_page, sk, sv);
         asm volatile("cp.async.commit_group;" ::: "memory");
         uint32_t qf[KSTEPS][4];
         dm_load_q<HD>(a, it, qf);

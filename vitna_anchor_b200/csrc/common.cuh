@@ -89,8 +89,10 @@ template <> __device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfl
 inline int launch_status() { return (int)cudaGetLastError(); }
 
 // Programmatic dependent launch.  A kernel launched with launch_dependent() may start while the kernel before it
-// in the stream is still running; what it does before dependency_wait() must touch only memory that no kernel
-// of the step writes (weights, tables, the step's metadata).  dependency_wait() returns when the kernel before
+// in the stream is still running; what it does before dependency_wait() must touch only memory that the kernel
+// before it does not write: weights, tables, the step's metadata, and (decode attention) the keys and values of
+// earlier steps.  Every kernel calls let_dependents_start() after its own dependency_wait(), so when a prologue
+// runs, everything but the kernel directly before it has finished.  dependency_wait() returns when the kernel before
 // it has finished and its writes are visible; let_dependents_start() allows the kernel after this one to begin
 // its own prologue.  Calling them in a kernel launched the ordinary way does nothing.
 __device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

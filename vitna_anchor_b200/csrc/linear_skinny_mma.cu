@@ -38,6 +38,7 @@ struct MmaParams {
     int M, N, K, ldx, kc, ks;    // kc: columns staged at a time (a multiple of 32 * ks); ks: warps = splits of K
     int xstride;                 // elements of bfloat16 between two staged rows
     int tpb;                     // most tiles of eight units a block works through (tile = blockIdx.x + i * gridDim.x)
+    int depth;                   // streaming kernel: batches of weights in flight for every lane
     const int32_t* positions;
     const float* cos_t;
     const float* sin_t;
@@ -373,6 +374,281 @@ __global__ void __launch_bounds__(256, MG <= 4 ? 2 : 1) skinny_mma_kernel(const 
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// The streaming variant, for weights large enough that a block works through several tiles or a long row.
+//
+// The kernel above asks for a tile's weights, waits, multiplies, lets the warps' sums meet and only then asks for
+// the next tile: between two tiles a block has nothing on its way.  Measured alone over weights of 67 to 200 MB both
+// stream at 5.4 TB/s once they run (a library reduction reads at 5.9); this one starts and ends a little sooner
+// (4.4 against 7.4 microseconds of fixed time a launch).  Here a lane
+// keeps `depth` batches of its own weights (four runs of 32 columns, two rows: 128 bytes) on their way into a ring in
+// shared memory that only this lane reads back (cp.async; consecutive lanes write consecutive 16 bytes), across
+// tiles and across the meeting of the warps.  One block a multiprocessor; the ring takes what shared memory the
+// staged rows leave.  Which warp adds which run, and in which order, is as above, so the sums are the same bits.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int ST_UN = 4;
+
+__device__ __forceinline__ void st_wait_pending(int n) {        // until at most n of the lane's latest batches are on their way
+    switch (n) {
+        case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+        case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+        case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+        case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+        case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+        case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+        case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+        default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
+    }
+}
+
+template <int EPI, bool NORM, int MG>
+__global__ void __launch_bounds__(256, 1) skinny_stream_kernel(const MmaParams p) {
+    typedef __nv_bfloat16 T;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int xstride = p.xstride;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nth = blockDim.x;
+    const int g = lane >> 2, q = lane & 3;
+    const int K = p.K, ks = p.ks, kc = p.kc, depth = p.depth;
+    const int m0 = blockIdx.y * (MG * 8);
+    T* xs = reinterpret_cast<T*>(smem_raw);
+    float* nw_s = reinterpret_cast<float*>(smem_raw + (size_t)MG * 8 * xstride * sizeof(T));
+    float* red = nw_s + (NORM ? K : 0);                                        // [ks][MG][32][4]
+    uint4* ring = reinterpret_cast<uint4*>(red + (size_t)ks * MG * 32 * 4);    // [depth][ST_UN][2][nth]
+    const int units = (EPI == ME_SWIGLU) ? p.N / 2 : (p.N + 1) / 2;
+    const int total_tiles = (units + 7) / 8;
+    const int n_my = (int)blockIdx.x < total_tiles ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+
+    auto tile_rows = [&](int it, int& u, bool& on, int& r0, int& r1, bool& has1) {
+        u = ((int)blockIdx.x + it * (int)gridDim.x) * 8 + g;
+        on = u < units;
+        r0 = r1 = 0;
+        if (on) mma_unit_rows<EPI>(p, u, r0, r1);
+        has1 = on && r1 < p.N;
+    };
+    // ---- the side that asks: batch after batch in the order the other side uses them ----------------------------
+    int l_it = 0, l_kb = 0, l_b = warp;
+    const T *lw0 = p.w, *lw1 = p.w;
+    auto loader_tile = [&]() {
+        int u, r0, r1; bool on, has1;
+        tile_rows(l_it, u, on, r0, r1, has1);
+        lw0 = p.w + (size_t)r0 * K;
+        lw1 = p.w + (size_t)(has1 ? r1 : r0) * K;
+    };
+    if (n_my > 0) loader_tile();
+    auto ask = [&](int slot) {
+        if (l_it < n_my) {
+            const int nblk = min(kc, K - l_kb) / 32;
+#pragma unroll
+            for (int i = 0; i < ST_UN; i++) {
+                const int bb = l_b + i * ks;
+                if (bb < nblk) {
+                    const int col = l_kb + bb * 32 + q * 8;
+                    uint4* dst = ring + ((size_t)(slot * ST_UN + i) * 2) * nth + tid;
+                    mm_cp_async16(dst, lw0 + col);
+                    mm_cp_async16(dst + nth, lw1 + col);
+                }
+            }
+            l_b += ST_UN * ks;
+            if (l_b >= nblk) {                          // a chunk is at least one batch for every warp, be it empty
+                l_b = warp;
+                l_kb += kc;
+                if (l_kb >= K) {
+                    l_kb = 0;
+                    l_it++;
+                    if (l_it < n_my) loader_tile();
+                }
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    // weights are nobody's output: the first batches are on their way before the kernel before this one has finished
+    for (int sl = 0; sl < depth; sl++) ask(sl);
+    if (NORM) {
+        for (int k = tid * 4; k < K; k += nth * 4) mm_cp_async16(nw_s + k, p.norm_w + k);
+    }
+    dependency_wait();
+    let_dependents_start();
+
+    if (NORM) {                                         // as above: the rows in float32, normed where they lie
+        for (int m = warp; m < MG * 8 && m0 + m < p.M; m += ks) {
+            const int src = p.rows ? p.rows[m0 + m] : m0 + m;
+            const float* xr = reinterpret_cast<const float*>(p.x) + (size_t)src * p.ldx;
+            float* xf = reinterpret_cast<float*>(xs + (size_t)m * xstride);
+            for (int k = lane * 4; k < K; k += 128) mm_cp_async16(xf + k, xr + k);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");       // the rows came last; the first batches are here too
+        __syncthreads();
+        for (int m = warp; m < MG * 8; m += ks) {
+            T* dst = xs + (size_t)m * xstride;
+            if (m0 + m >= p.M) {
+                for (int k = lane * 8; k < K; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
+                continue;
+            }
+            const float* xf = reinterpret_cast<const float*>(dst);
+            float ss = 0.0f;
+            for (int k = lane * 4; k < K; k += 128) {
+                const float4 v = *reinterpret_cast<const float4*>(xf + k);
+                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            }
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)K + p.eps);
+            for (int k0 = 0; k0 < K; k0 += 128) {
+                const int k = k0 + lane * 4;
+                float4 xv = make_float4(0.0f, 0.0f, 0.0f, 0.0f), wv = xv;
+                if (k < K) {
+                    xv = *reinterpret_cast<const float4*>(xf + k);
+                    wv = *reinterpret_cast<const float4*>(nw_s + k);
+                }
+                __syncwarp();
+                if (k < K) {
+                    __nv_bfloat162 lo = __floats2bfloat162_rn((xv.x * inv) * wv.x, (xv.y * inv) * wv.y);
+                    __nv_bfloat162 hi = __floats2bfloat162_rn((xv.z * inv) * wv.z, (xv.w * inv) * wv.w);
+                    uint2 v;
+                    v.x = *reinterpret_cast<uint32_t*>(&lo);
+                    v.y = *reinterpret_cast<uint32_t*>(&hi);
+                    *reinterpret_cast<uint2*>(dst + k) = v;
+                }
+                __syncwarp();
+            }
+        }
+        __syncthreads();
+    }
+
+    // ---- the side that multiplies -------------------------------------------------------------------------------
+    const bool one_chunk = kc >= K;
+    int slot = 0;
+    for (int it = 0; it < n_my; it++) {
+        int u, r0, r1; bool on, has1;
+        tile_rows(it, u, on, r0, r1, has1);
+        float d[MG][4];
+#pragma unroll
+        for (int mg = 0; mg < MG; mg++) { d[mg][0] = d[mg][1] = d[mg][2] = d[mg][3] = 0.0f; }
+        for (int kb = 0; kb < K; kb += kc) {
+            const int kn = min(kc, K - kb);
+            if (!NORM && (it == 0 || !one_chunk)) {
+                __syncthreads();                        // the chunk before has been read
+                for (int m = warp; m < MG * 8; m += ks) {
+                    T* dst = xs + (size_t)m * xstride;
+                    if (m0 + m >= p.M) {
+                        for (int k = lane * 8; k < kn; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
+                    } else {
+                        const T* xr = reinterpret_cast<const T*>(p.x) + (size_t)(m0 + m) * p.ldx + kb;
+#pragma unroll 4
+                        for (int k = lane * 8; k < kn; k += 256) *reinterpret_cast<uint4*>(dst + k) = *reinterpret_cast<const uint4*>(xr + k);
+                    }
+                }
+                __syncthreads();
+            }
+            const int nblk = kn / 32;
+            int b = warp;
+            do {
+                st_wait_pending(depth - 1);             // the oldest batch on its way is the one used now
+#pragma unroll
+                for (int i = 0; i < ST_UN; i++) {
+                    const int bb = b + i * ks;
+                    if (bb < nblk) {
+                        const uint4* src = ring + ((size_t)(slot * ST_UN + i) * 2) * nth + tid;
+                        const uint4 r = src[0], t = src[nth];
+#pragma unroll
+                        for (int mg = 0; mg < MG; mg++) {
+                            const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)(mg * 8 + g) * xstride + bb * 32 + q * 8);
+                            mma_bf16(d[mg], r.x, t.x, r.y, t.y, xv.x, xv.y);
+                            mma_bf16(d[mg], r.z, t.z, r.w, t.w, xv.z, xv.w);
+                        }
+                    }
+                }
+                ask(slot);                              // the place just read takes the batch `depth` further on
+                slot = slot + 1 == depth ? 0 : slot + 1;
+                b += ST_UN * ks;
+            } while (b < nblk);
+        }
+        // the warps' sums meet, as above
+#pragma unroll
+        for (int mg = 0; mg < MG; mg++)
+            *reinterpret_cast<float4*>(red + (((size_t)warp * MG + mg) * 32 + lane) * 4) = make_float4(d[mg][0], d[mg][1], d[mg][2], d[mg][3]);
+        __syncthreads();
+        for (int mg = warp; mg < MG; mg += ks) {
+            float4 s = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int w = 0; w < ks; w++) {
+                const float4 v = *reinterpret_cast<const float4*>(red + (((size_t)w * MG + mg) * 32 + lane) * 4);
+                s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+            }
+            if (!on) continue;
+            const int m = m0 + mg * 8 + 2 * q;
+            if (m < p.M) mma_finish<EPI>(p, u, r0, r1, has1, m, s.x, s.z, false, 0, 1.0f, 0.0f, nullptr);
+            if (m + 1 < p.M) mma_finish<EPI>(p, u, r0, r1, has1, m + 1, s.y, s.w, false, 0, 1.0f, 0.0f, nullptr);
+        }
+        __syncthreads();
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+// 0: never the streaming kernel, 1: whenever its sizes fit, 2 (default): large weights with long rows (see launch_stream).
+static int g_stream_mode = -1;
+static int stream_mode() {
+    if (g_stream_mode < 0) {
+        const char* e = getenv("VITNA_SKINNY_STREAM");
+        g_stream_mode = e ? atoi(e) : 2;
+    }
+    return g_stream_mode;
+}
+
+// Launches the streaming kernel if it should and can take the product; returns -1 if not.
+template <int EPI, bool NORM>
+static int launch_stream(MmaParams p, int mg, int ks, cudaStream_t stream) {
+    if (mg > 2 || stream_mode() == 0) return -1;
+    const int units = (EPI == ME_SWIGLU) ? p.N / 2 : (p.N + 1) / 2;
+    const int tiles = (units + 7) / 8;
+    const int ychunks = (p.M + 8 * mg - 1) / (8 * mg);
+    const int per_chunk = 148 / ychunks > 0 ? 148 / ychunks : 1;
+    const int blocks = tiles < per_chunk ? tiles : per_chunk;
+    // Measured inside decode steps: it wins (a tenth of the kernel's time) where the weights are large and the rows long
+    // (the 1.7B sizes); with small weights the kernel above, two blocks a multiprocessor and room beside the kernels
+    // before and after it, is the faster one, and so it is when the batch rows are split over blocks.
+    if (stream_mode() == 2 && !((size_t)p.N * p.K * 2 >= ((size_t)16 << 20) && p.K >= 2048 && ychunks == 1)) return -1;
+    const int rows = mg * 8, nth = 32 * ks;
+    const size_t stage = (size_t)ST_UN * 2 * 16 * nth;                  // a batch of every lane
+    const size_t red = (size_t)ks * mg * 32 * 4 * sizeof(float);
+    const size_t budget = 224 * 1024;
+    int kc = p.K;
+    size_t stride_bytes, fixed;
+    if (NORM) {
+        stride_bytes = (size_t)4 * p.K + 64;
+        fixed = rows * stride_bytes + (size_t)4 * p.K + red;
+        if (fixed + 2 * stage > budget) return -1;
+    } else {
+        // the rows take at most what leaves the ring four batches: columns in multiples of 32 * ks
+        const size_t room = budget - red - 4 * stage;
+        const int fit = (int)(((room / rows - 64) / 2) / (32 * ks)) * (32 * ks);
+        if (fit <= 0) return -1;
+        if (kc > fit) kc = fit;
+        stride_bytes = (size_t)2 * kc + ((2 * kc) % 128 == 64 ? 0 : 64);
+        fixed = rows * stride_bytes + red;
+    }
+    int depth = (int)((budget - fixed) / stage);
+    if (depth > 8) depth = 8;
+    if (depth < 2) return -1;
+    p.ks = ks;
+    p.kc = kc;
+    p.xstride = (int)(stride_bytes / 2);
+    p.depth = depth;
+    p.tpb = (tiles + blocks - 1) / blocks;
+    const size_t smem = fixed + depth * stage;
+#define LAUNCH_ST(MGV)                                                                                                      \
+    {                                                                                                                       \
+        auto kern = skinny_stream_kernel<EPI, NORM, MGV>;                                                                   \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                 \
+        if (e != cudaSuccess) return (int)e;                                                                                \
+        const int rc = launch_dependent(kern, dim3(blocks, ychunks), dim3(nth), smem, stream, p);                           \
+        if (rc != 0) return rc;                                                                                             \
+    }
+    if (mg == 1) LAUNCH_ST(1) else LAUNCH_ST(2)
+#undef LAUNCH_ST
+    return launch_status();
+}
+
 template <int EPI, bool NORM>
 static int launch_mma(MmaParams p, cudaStream_t stream) {
     const int units = (EPI == ME_SWIGLU) ? p.N / 2 : (p.N + 1) / 2;
@@ -393,6 +669,10 @@ static int launch_mma(MmaParams p, cudaStream_t stream) {
         if (nblk % cand == 0) ks = cand;
     if (!ks) { ks = 8; while (ks > 1 && nblk / ks < 2) ks--; }
     p.ks = ks;
+    {
+        const int rc = launch_stream<EPI, NORM>(p, mg, ks, stream);
+        if (rc >= 0) return rc;
+    }
     // columns staged at a time: all of K if the rows fit in 160 KB, else the largest multiple of 32*ks that does.
     // With the norm a row is staged whole, in float32.
     const int rows = mg * 8;
@@ -452,6 +732,13 @@ static int mma_dispatch(int epi, const MmaParams& p, cudaStream_t stream) {
 
 using namespace vk;
 
+// Which launches the streaming kernel takes (see stream_mode); returns the mode that was in force.
+VK_API int vk_set_skinny_stream(int mode) {
+    const int was = stream_mode();
+    if (mode >= 0 && mode <= 2) g_stream_mode = mode;
+    return was;
+}
+
 // The bfloat16 few-rows product on tensor cores.  Arguments as vk_linear_skinny; in addition K must be a
 // multiple of 32, and with the fused norm x's rows must be 16-byte aligned (ldx a multiple of 4).
 VK_API int vk_linear_skinny_mma(const void* x, const int32_t* rows, const float* norm_w, float eps, const void* w, void* out,
@@ -469,7 +756,7 @@ VK_API int vk_linear_skinny_mma(const void* x, const int32_t* rows, const float*
             !slot || !cache)
             return VK_BAD_SHAPE;
     }
-    MmaParams p{x, rows, norm_w, eps, (const __nv_bfloat16*)w, out, M, N, K, ldx, 0, 0, 0, 1, positions, cos_t, sin_t, slot,
+    MmaParams p{x, rows, norm_w, eps, (const __nv_bfloat16*)w, out, M, N, K, ldx, 0, 0, 0, 1, 0, positions, cos_t, sin_t, slot,
                 (__nv_bfloat16*)cache, nh, nkv, hd, page_size};
     return norm_w ? mma_dispatch<true>(epi, p, stream) : mma_dispatch<false>(epi, p, stream);
 }

@@ -251,6 +251,12 @@ def set_decode_tma(mode: int) -> int:
     return int(lib().vk_set_decode_tma(int(mode)))
 
 
+def set_skinny_stream(mode: int) -> int:
+    """Which few-rows products the streaming tensor-core kernel takes: 0 none, 1 all whose sizes it takes, 2 those its
+    size rule gives it (the default; VITNA_SKINNY_STREAM sets the initial mode).  Returns the mode that was in force."""
+    return int(lib().vk_set_skinny_stream(int(mode)))
+
+
 def silu_mul(gu: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out = silu(gu[:, :I]) * gu[:, I:]."""
     _req(gu, "gu", dims=2); _req(out, "out", gu.dtype, 2)
