@@ -118,16 +118,15 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
+            const uint32_t a_lo0 = umma_desc_lo(smem_u32(smem));      // low words of the descriptors (see umma_bf16_lo)
             bool ok = true;
             for (int kb = 0; kb < num_kb && ok; kb++) {
                 const int s = kb % TC_STAGES;
                 if (!mbar_wait(&full[s], (kb / TC_STAGES) & 1, wc.cycles)) { give_up(wc.error, &failed, 2); ok = false; break; }
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+                const uint32_t a_lo = a_lo0 + s * (STAGE_BYTES >> 4), b_lo = a_lo + (A_BYTES >> 4);
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; k++) {
-                    umma_bf16(tmem_base, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32), idesc, (kb | k) != 0);
-                }
+                for (int k = 0; k < TC_BK / 16; k++) umma_bf16_lo(tmem_base, a_lo + 2 * k, b_lo + 2 * k, idesc, (kb | k) != 0);
                 umma_commit(&empty[s]);           // arrives when the instructions above have read the stage
             }
             umma_commit(acc_full);                // arrives when every instruction has written the accumulator
@@ -386,6 +385,7 @@ __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(cons
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_bf16(TC_BM, TW_BN);
+            const uint32_t a_lo0 = umma_desc_lo(smem_u32(smem));      // low words of the descriptors (see umma_bf16_lo)
             int kc = 0, j = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, j++) {
@@ -396,10 +396,9 @@ __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(cons
                     const int s = kc % TW_STAGES;
                     if (!mbar_wait(&full[s], (kc / TW_STAGES) & 1, wc.cycles)) { give_up(wc.error, &failed, 33); ok = false; break; }
                     tc_fence_after();
-                    const uint64_t a_desc = umma_desc_sw128(smem_u32(smem + s * STAGE_BYTES));
-                    const uint64_t b_desc = umma_desc_sw128(smem_u32(smem + s * STAGE_BYTES + A_BYTES));
+                    const uint32_t a_lo = a_lo0 + s * (STAGE_BYTES >> 4), b_lo = a_lo + (A_BYTES >> 4);
 #pragma unroll
-                    for (int k = 0; k < TC_BK / 16; k++) umma_bf16(tmem_base + b * TW_BN, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+                    for (int k = 0; k < TC_BK / 16; k++) umma_bf16_lo(tmem_base + b * TW_BN, a_lo + 2 * k, b_lo + 2 * k, idesc, (kb | k) != 0);
                     umma_commit(&empty[s]);
                 }
                 if (ok) umma_commit(&acc_full[b]);
