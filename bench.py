@@ -351,7 +351,21 @@ def gemm_run(pk, M=2048, reps=20):
 
 REF_DIR = os.path.join(ROOT, "baseline", "_ref", "engine")
 REF_EXE = os.path.join(REF_DIR, "vitna-anchor")
-REF_SOURCE = "/root/reference/engine"
+
+
+def reference_source():
+    """Where the reference's engine sources lie: VITNA_REFERENCE_SOURCE, else the `reference_path` that BASELINE.json names."""
+    env = os.environ.get("VITNA_REFERENCE_SOURCE")
+    if env:
+        return env
+    try:
+        with open(os.path.join(ROOT, "BASELINE.json")) as fh:
+            return os.path.join(json.load(fh)["reference_path"], "engine")
+    except (OSError, KeyError, ValueError):
+        return ""
+
+
+REF_SOURCE = reference_source()
 
 
 def byte_level_tokenizer_json():

@@ -13,6 +13,10 @@
 //     stages, each with an mbarrier; the ring runs across units, so the first chunk of the next unit is on
 //     its way while the last of this one is used, and a multiprocessor always has copies in flight.
 //
+// A warp asks for the first chunks of its first unit before the wait on the kernel before this launch (programmatic
+// dependent launch): that kernel writes the tokens' own keys and values only, and a chunk that ends before the token's
+// position holds keys of earlier steps.
+//
 // The arithmetic of a chunk is kept short, because a warp that works alone cannot hide its own latencies: scores and
 // probabilities are kept in base 2 (the scale carries log2 e, 2^x is one instruction of the special-function unit),
 // keys are masked only in chunks that touch the position or the window's edge, and the running output is rescaled
@@ -144,10 +148,6 @@ __global__ void __launch_bounds__(DT_THREADS, 1) attention_decode_tma_kernel(con
         return it;
     };
 
-    dependency_wait();                          // q and the cache come from the kernels before this one
-    let_dependents_start();
-    if (my_first >= n_units) return;
-
     uint8_t* my_stages = smem + (size_t)warp * DT_STAGES * DT_STAGE_BYTES;
     uint64_t* my_bars = bars + warp * DT_STAGES;
 
@@ -191,19 +191,43 @@ __global__ void __launch_bounds__(DT_THREADS, 1) attention_decode_tma_kernel(con
     };
 
     // ---- the stream of chunks: an issuing cursor runs up to DT_STAGES chunks (and at most one unit) ahead --------
+    const bool have = my_first < n_units;
     int iu = my_first;                          // unit being issued, and its next chunk
-    DtUnit iunit = unit_of(iu);
+    DtUnit iunit = have ? unit_of(iu) : DtUnit{};
     int ic = iunit.c0;
     uint32_t qn[KSTEPS][4];                     // the queries of the unit the issuing cursor has reached
-    load_q(iunit, qn);
-    ipages = load_pages(iunit);
     int issued = 0, consumed = 0;               // chunks so far: stage = count % DT_STAGES, parity = (count / DT_STAGES) & 1
     int cu = my_first;                          // unit being consumed
     bool ok = true;
+    // The first chunks of the warp's first unit are asked for before the wait on the kernel before this one, which
+    // writes the token's own key and value only: every chunk that ends before the token's position holds keys of
+    // earlier steps.
+    if (have) {
+        ipages = load_pages(iunit);
+        while (issued < DT_STAGES && ic <= iunit.c1 && iunit.k0 + ic * DT_CHUNK + DT_CHUNK - 1 < iunit.pos) {
+            issue(iunit, ic, issued % DT_STAGES);
+            issued++;
+            ic++;
+        }
+    }
+    dependency_wait();                          // q and the token's own key and value come from the kernel before this one
+    let_dependents_start();
+    if (!have) return;
+    load_q(iunit, qn);
 
     // The issuing cursor stops before the unit after next (its queries would overwrite, in qn, those of a unit not yet
     // begun); iu then names that unit without its fields, which are made when the cursor may go on.
     bool ipending = false;
+    auto next_unit = [&]() {                    // the issuing cursor has passed its unit's last chunk
+        iu += grid_warps;
+        if (iu >= n_units) return;
+        if (iu > cu + grid_warps) { ipending = true; return; }
+        iunit = unit_of(iu);
+        ic = iunit.c0;
+        load_q(iunit, qn);
+        ipages = load_pages(iunit);
+    };
+    if (ic > iunit.c1) next_unit();             // (a first unit of one or two chunks, none at the position, is asked for whole)
 
     while (cu < n_units && ok) {
         const DtUnit it = cu == iu && !ipending ? iunit : unit_of(cu);
@@ -232,13 +256,8 @@ __global__ void __launch_bounds__(DT_THREADS, 1) attention_decode_tma_kernel(con
                 issue(iunit, ic, issued % DT_STAGES);
                 issued++;
                 if (++ic > iunit.c1) {
-                    iu += grid_warps;
-                    if (iu >= n_units) break;
-                    if (iu > cu + grid_warps) { ipending = true; break; }
-                    iunit = unit_of(iu);
-                    ic = iunit.c0;
-                    load_q(iunit, qn);
-                    ipages = load_pages(iunit);
+                    next_unit();
+                    if (iu >= n_units || ipending) break;
                 }
             }
             const int s = consumed % DT_STAGES;
