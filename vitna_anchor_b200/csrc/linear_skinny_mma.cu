@@ -289,16 +289,19 @@ __global__ void __launch_bounds__(256, MG <= 4 ? 2 : 1) skinny_mma_kernel(const 
         if (!NORM && (it == 0 || !one_chunk)) {
             __syncthreads();                            // the previous chunk has been read
             // stage rows 0..M-1 (rows up to MG*8 are zero) of columns kb .. kb+kn
+            // (cp.async: all of a lane's pieces are on their way at once; through registers, four at a time, a long row
+            // took several trips to the second-level cache)
             for (int m = warp; m < MG * 8; m += ks) {
                 T* dst = xs + (size_t)m * xstride;
                 if (m0 + m >= p.M) {
                     for (int k = lane * 8; k < kn; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
                 } else {
                     const T* xr = reinterpret_cast<const T*>(p.x) + (size_t)(m0 + m) * p.ldx + kb;
-#pragma unroll 4
-                    for (int k = lane * 8; k < kn; k += 256) *reinterpret_cast<uint4*>(dst + k) = *reinterpret_cast<const uint4*>(xr + k);
+                    for (int k = lane * 8; k < kn; k += 256) mm_cp_async16(dst + k, xr + k);
                 }
             }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncthreads();
         }
         // this warp's share of the chunk: the runs of 32 columns whose index is warp modulo ks.  A chunk starts
@@ -535,10 +538,13 @@ __global__ void __launch_bounds__(256, 1) skinny_stream_kernel(const MmaParams p
                         for (int k = lane * 8; k < kn; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
                     } else {
                         const T* xr = reinterpret_cast<const T*>(p.x) + (size_t)(m0 + m) * p.ldx + kb;
-#pragma unroll 4
-                        for (int k = lane * 8; k < kn; k += 256) *reinterpret_cast<uint4*>(dst + k) = *reinterpret_cast<const uint4*>(xr + k);
+                        for (int k = lane * 8; k < kn; k += 256) mm_cp_async16(dst + k, xr + k);
                     }
                 }
+                // the rows came last: the batches of weights asked for before them are here too, and the count of
+                // batches on their way starts again from none
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
                 __syncthreads();
             }
             const int nblk = kn / 32;
