@@ -345,30 +345,32 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 3 : 1) attention_decode
     __syncthreads();
     if (!is_last) return;
     // Every thread combines one output element on its own: the splits' maxima, sums and partial outputs are asked
-    // for eight splits at a time in one trip to the second-level cache, and folded into a running maximum, sum and
-    // output in split order (the same order whatever else is in the batch).
+    // for sixteen splits at a time in one trip to the second-level cache (contexts of up to 4,096 positions in one
+    // trip), and folded into a running maximum, sum and output in split order (the same order whatever else is in
+    // the batch).
+    constexpr int TRIP = 16;
     for (int i = tid; i < gt * HD; i += DM_THREADS) {
         const int h = i / HD, d = i % HD;
         const float2* ml = reinterpret_cast<const float2*>(a.part_ml) + ((size_t)zi * nh + h0 + h) * max_splits + first_split;
         const float* po = a.part_o + (((size_t)zi * nh + h0 + h) * max_splits + first_split) * HD + d;
         float mm = -INFINITY, l = 0.0f, o = 0.0f;
-        for (int j0 = 0; j0 < n_active; j0 += 8) {
-            float2 st[8];
-            float pv[8];
+        for (int j0 = 0; j0 < n_active; j0 += TRIP) {
+            float2 st[TRIP];
+            float pv[TRIP];
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
+            for (int j = 0; j < TRIP; j++) {
                 const bool on = j0 + j < n_active;
                 st[j] = on ? __ldcg(ml + j0 + j) : make_float2(-INFINITY, 0.0f);
                 pv[j] = on ? __ldcg(po + (size_t)(j0 + j) * HD) : 0.0f;
             }
             float cm = mm;
 #pragma unroll
-            for (int j = 0; j < 8; j++) cm = fmaxf(cm, st[j].x);
+            for (int j = 0; j < TRIP; j++) cm = fmaxf(cm, st[j].x);
             const float keep = mm == -INFINITY ? 0.0f : expf(mm - cm);          // cm is finite: every split has a counted key
             l *= keep;
             o *= keep;
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
+            for (int j = 0; j < TRIP; j++) {
                 const float e = st[j].x == -INFINITY ? 0.0f : expf(st[j].x - cm);
                 l += st[j].y * e;
                 o += pv[j] * e;

@@ -124,6 +124,42 @@ __device__ __forceinline__ void mma_finish(const MmaParams& p, int u, int r0, in
     }
 }
 
+// A row of up to 128 * NV float32 values straight from global memory into a warp's registers (all its 16-byte pieces
+// on their way at once), normed there, left as bfloat16 in dst.  The sum of squares runs in the order of the staged
+// path (a lane's pieces in ascending order, then the shuffle tree), so both give the same bits.
+template <int NV>
+__device__ __forceinline__ void norm_row_in_regs(const float* __restrict__ xr, const float* __restrict__ nw, int K, float eps,
+                                                 __nv_bfloat16* dst, int lane) {
+    float4 xv[NV];
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        const int k = lane * 4 + j * 128;
+        if (k < K) xv[j] = *reinterpret_cast<const float4*>(xr + k);
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        if (lane * 4 + j * 128 < K) {
+            ss = fmaf(xv[j].x, xv[j].x, ss); ss = fmaf(xv[j].y, xv[j].y, ss); ss = fmaf(xv[j].z, xv[j].z, ss); ss = fmaf(xv[j].w, xv[j].w, ss);
+        }
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)K + eps);
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        const int k = lane * 4 + j * 128;
+        if (k < K) {
+            const float4 wv = __ldg(reinterpret_cast<const float4*>(nw + k));
+            __nv_bfloat162 lo = __floats2bfloat162_rn((xv[j].x * inv) * wv.x, (xv[j].y * inv) * wv.y);
+            __nv_bfloat162 hi = __floats2bfloat162_rn((xv[j].z * inv) * wv.z, (xv[j].w * inv) * wv.w);
+            uint2 v;
+            v.x = *reinterpret_cast<uint32_t*>(&lo);
+            v.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(dst + k) = v;
+        }
+    }
+}
+
 // MG: groups of eight batch rows (1, 2, 4 or 8).  PIPE: the variant for long rows (two batches of loads a warp in flight).
 // blockDim.x = 32 * ks.  Block (b, y) works on tiles b, b + gridDim.x, ... for batch rows y * MG*8 ...
 template <int EPI, bool NORM, int MG, bool PIPE>
@@ -176,8 +212,24 @@ __global__ void __launch_bounds__(256, MG <= 4 ? 2 : 1) skinny_mma_kernel(const 
             }
         }
     }
-    if (NORM) {                                         // the norm's weights, nobody's output either
+    // With the fused norm, rows of up to NORM_REG columns never touch shared memory in float32: a warp takes a row
+    // straight from global memory into registers (all its 16-byte pieces and the norm's weights on their way at once),
+    // norms it there and leaves only the bfloat16 values.  Measured inside decode steps at K = 576, staging the rows in
+    // float32 first (cp.async, a barrier, two passes over shared memory) took 2.8-3.2 of a kernel's 6.4 microseconds.
+    // (Rows of up to 640 columns: with eight pieces a lane instead of five the kernel for K = 960 kept them in local
+    // memory and a step at the 360M sizes took 1.27 instead of 1.20 ms.)
+    constexpr int NORM_NV = 5, NORM_REG = 128 * NORM_NV;
+    const bool norm_in_regs = NORM && K <= NORM_REG;
+    int norm_src[2] = {0, 0};                           // the input rows of the warp's first two rows (an index array may name them)
+    if (NORM && !norm_in_regs) {                        // the norm's weights, nobody's output either
         for (int k = tid * 4; k < K; k += blockDim.x * 4) mm_cp_async16(nw_s + k, p.norm_w + k);
+    }
+    if (norm_in_regs) {
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            const int m = m0 + warp + e * ks;
+            norm_src[e] = (warp + e * ks < MG * 8 && m < p.M) ? (p.rows ? p.rows[m] : m) : 0;
+        }
     }
     // what the first finishing pass of this lane needs besides the sums
     const int m_first = m0 + warp * 8 + 2 * q;          // rows m_first, m_first + 1 of row group `warp`
@@ -205,7 +257,20 @@ __global__ void __launch_bounds__(256, MG <= 4 ? 2 : 1) skinny_mma_kernel(const 
     dependency_wait();
     let_dependents_start();
 
-    if (NORM) {
+    if (norm_in_regs) {
+        const float* xg = reinterpret_cast<const float*>(p.x);
+        int round = 0;
+        for (int m = warp; m < MG * 8; m += ks, round++) {
+            T* dst = xs + (size_t)m * xstride;
+            if (m0 + m >= p.M) {
+                for (int k = lane * 8; k < K; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
+                continue;
+            }
+            const int src = round < 2 ? norm_src[round] : (p.rows ? p.rows[m0 + m] : m0 + m);
+            norm_row_in_regs<NORM_NV>(xg + (size_t)src * p.ldx, p.norm_w, K, p.eps, dst, lane);
+        }
+        __syncthreads();
+    } else if (NORM) {
         // One trip to memory for all rows: every warp asks for its rows (float32) into their staging rows, then
         // norms them where they lie.  A row's sum of squares is one warp's, in a fixed order.
         for (int m = warp; m < MG * 8 && m0 + m < p.M; m += ks) {
@@ -228,7 +293,7 @@ __global__ void __launch_bounds__(256, MG <= 4 ? 2 : 1) skinny_mma_kernel(const 
             }
         }
     }
-    if (NORM) {
+    if (NORM && !norm_in_regs) {
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();                                // the norm's weights came through all threads
         for (int m = warp; m < MG * 8; m += ks) {
@@ -467,13 +532,26 @@ __global__ void __launch_bounds__(256, 1) skinny_stream_kernel(const MmaParams p
     };
     // weights are nobody's output: the first batches are on their way before the kernel before this one has finished
     for (int sl = 0; sl < depth; sl++) ask(sl);
-    if (NORM) {
+    constexpr int ST_NORM_NV = 16;                      // rows of up to 2,048 columns are normed in registers (one block a multiprocessor: registers to spare)
+    const bool norm_in_regs = NORM && K <= 128 * ST_NORM_NV;
+    if (NORM && !norm_in_regs) {
         for (int k = tid * 4; k < K; k += nth * 4) mm_cp_async16(nw_s + k, p.norm_w + k);
     }
     dependency_wait();
     let_dependents_start();
 
-    if (NORM) {                                         // as above: the rows in float32, normed where they lie
+    if (norm_in_regs) {
+        for (int m = warp; m < MG * 8; m += ks) {
+            T* dst = xs + (size_t)m * xstride;
+            if (m0 + m >= p.M) {
+                for (int k = lane * 8; k < K; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
+                continue;
+            }
+            const int src = p.rows ? p.rows[m0 + m] : m0 + m;
+            norm_row_in_regs<ST_NORM_NV>(reinterpret_cast<const float*>(p.x) + (size_t)src * p.ldx, p.norm_w, K, p.eps, dst, lane);
+        }
+        __syncthreads();
+    } else if (NORM) {                                  // as above: the rows in float32, normed where they lie
         for (int m = warp; m < MG * 8 && m0 + m < p.M; m += ks) {
             const int src = p.rows ? p.rows[m0 + m] : m0 + m;
             const float* xr = reinterpret_cast<const float*>(p.x) + (size_t)src * p.ldx;
