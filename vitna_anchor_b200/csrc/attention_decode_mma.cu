@@ -88,6 +88,12 @@ __device__ __forceinline__ void dm_ldsm_x4_trans(uint32_t& r0, uint32_t& r1, uin
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"((uint32_t)__cvta_generic_to_shared(p)));
 }
+// 2^x in one instruction of the special-function unit: scores and maxima are kept in base 2 (the scale carries log2 e).
+__device__ __forceinline__ float dm_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t dm_pack(float x, float y) {
     __nv_bfloat162 v = __floats2bfloat162_rn(x, y);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -199,6 +205,7 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 3 : 1) attention_decode
     const int nh = a.nh, max_splits = a.max_splits;
     const int zi = it.zi, t = it.t, split = it.split, h0 = it.h0, gt = it.gt, pos = it.pos, lo = it.lo, k0 = it.k0;
     const int first_split = it.first_split, n_active = it.n_active;
+    const float scale_log2 = a.scale * 1.4426950408889634f;         // scores, maxima and the partials' maxima are kept in base 2
     // keys of this warp: wk0 .. wk0+31; the warp has work if one of them counts
     const int wk0 = k0 + warp * 32;
     const bool warp_on = wk0 <= pos && wk0 + 31 >= lo;
@@ -232,14 +239,19 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 3 : 1) attention_decode
                 dm_mma(s[nb2 * 2 + 1], qf[ks], b2, b3);
             }
         }
-        // scale, mask; rows gq and gq+8 (heads), keys wk0 + nb*8 + 2*qd + {0,1}
+        // scale (base 2) and, in a warp whose keys touch the position or the window's edge, mask; rows gq and gq+8
+        // (heads), keys wk0 + nb*8 + 2*qd + {0,1}
         float mx[2] = {-INFINITY, -INFINITY};
+        const bool edge = wk0 + 31 > pos || wk0 < lo;
 #pragma unroll
         for (int nb = 0; nb < 4; nb++) {
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                const int kk = wk0 + nb * 8 + qd * 2 + (e & 1);
-                const float v = (kk <= pos && kk >= lo) ? s[nb][e] * a.scale : -INFINITY;
+                float v = s[nb][e] * scale_log2;
+                if (edge) {
+                    const int kk = wk0 + nb * 8 + qd * 2 + (e & 1);
+                    if (!(kk <= pos && kk >= lo)) v = -INFINITY;
+                }
                 s[nb][e] = v;
                 mx[e >> 1] = fmaxf(mx[e >> 1], v);
             }
@@ -253,8 +265,8 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 3 : 1) attention_decode
         uint32_t ph[2][4], pl[2][4];            // the 16-row operand of the two k-steps of 16 keys, high and low parts
 #pragma unroll
         for (int nb = 0; nb < 4; nb++) {
-            const float p0 = expf(s[nb][0] - mx[0]), p1 = expf(s[nb][1] - mx[0]);
-            const float p2 = expf(s[nb][2] - mx[1]), p3 = expf(s[nb][3] - mx[1]);
+            const float p0 = dm_ex2(s[nb][0] - mx[0]), p1 = dm_ex2(s[nb][1] - mx[0]);
+            const float p2 = dm_ex2(s[nb][2] - mx[1]), p3 = dm_ex2(s[nb][3] - mx[1]);
             rs[0] += p0 + p1;
             rs[1] += p2 + p3;
             const __nv_bfloat162 h01 = __floats2bfloat162_rn(p0, p1), h23 = __floats2bfloat162_rn(p2, p3);
@@ -318,7 +330,7 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 3 : 1) attention_decode
 #pragma unroll
         for (int w = 0; w < 8; w++) {
             if (ml[w].x == -INFINITY) continue;     // a warp without a counted key left nothing
-            const float e = expf(ml[w].x - m);
+            const float e = dm_ex2(ml[w].x - m);
             l += ml[w].y * e;
             acc += reinterpret_cast<const float*>(sk + w * 32 * LD)[row * HD + d] * e;
         }
@@ -366,12 +378,12 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 3 : 1) attention_decode
             float cm = mm;
 #pragma unroll
             for (int j = 0; j < TRIP; j++) cm = fmaxf(cm, st[j].x);
-            const float keep = mm == -INFINITY ? 0.0f : expf(mm - cm);          // cm is finite: every split has a counted key
+            const float keep = mm == -INFINITY ? 0.0f : dm_ex2(mm - cm);        // cm is finite: every split has a counted key; maxima are in base 2
             l *= keep;
             o *= keep;
 #pragma unroll
             for (int j = 0; j < TRIP; j++) {
-                const float e = st[j].x == -INFINITY ? 0.0f : expf(st[j].x - cm);
+                const float e = st[j].x == -INFINITY ? 0.0f : dm_ex2(st[j].x - cm);
                 l += st[j].y * e;
                 o += pv[j] * e;
             }
