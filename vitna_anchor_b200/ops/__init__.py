@@ -423,6 +423,7 @@ def linear_tcgen05_rope(x: torch.Tensor, wqkv: torch.Tensor, q_out: torch.Tensor
 EPI_SAME, EPI_F32, EPI_ACC, EPI_SWIGLU, EPI_ROPE = 0, 1, 2, 3, 4
 SKINNY_MAX_ROWS = 64
 FUSED_NORM_MAX_ROWS = 16     # a block of the few-rows kernel norms every row it stages: beyond this many a norm kernel runs once
+NORM_IN_REGISTERS_MAX_K = 640    # the tensor-core few-rows kernel norms rows of up to this many columns without staging them
 
 
 def _mma_rows_per_block(M: int, N: int, K: int) -> int:
@@ -450,7 +451,13 @@ def fused_norm_takes(dtype: torch.dtype, M: int, K: int, N: int) -> bool:
         return False
     if dtype == torch.float32 or K % 32 != 0:
         return M <= FUSED_NORM_MAX_ROWS
-    return _mma_rows_per_block(M, N, K) <= FUSED_NORM_MAX_ROWS and _mma_norm_smem(M, K, N) <= 112 * 1024
+    rows = _mma_rows_per_block(M, N, K)
+    # Rows of up to 640 columns are normed in registers, and a block may norm 16 of them; longer rows are staged in
+    # float32 first, and beyond eight of them a norm kernel that runs once is faster (measured at K = 960 and 16 / 64
+    # decode rows: 1.48 against 1.53 and 2.73 against 2.91 ms a step; at K = 576 the fused form wins: 1.42 against 1.53).
+    if rows > (FUSED_NORM_MAX_ROWS if K <= NORM_IN_REGISTERS_MAX_K else min(8, FUSED_NORM_MAX_ROWS)):
+        return False
+    return _mma_norm_smem(M, K, N) <= 112 * 1024
 
 
 def skinny_takes(dtype: torch.dtype, M: int, K: int, N: int = 0) -> bool:
