@@ -519,23 +519,58 @@ def test_attention_prefill_tiles(ops, nh, nkv, hd, ps, window):
     _prefill_case(ops, ops.attention_prefill, 64, nh, nkv, hd, ps, window, [150, 140, 601, 128 + 70], [150, 37, 2, 70])
 
 
+@pytest.fixture(params=[0, 1], ids=["two_threads_a_row", "two_streams"])
+def prefill_kernel(ops, request):
+    """Both tcgen05 prompt-attention kernels, whatever the launcher's size rule would take."""
+    was = ops.set_prefill_streams(request.param)
+    yield request.param
+    ops.set_prefill_streams(was)
+
+
 @pytest.mark.parametrize("nh,nkv,ps,window", [(9, 3, 16, 0), (4, 4, 8, 0), (2, 1, 32, 0), (6, 2, 64, 0), (3, 1, 128, 0),
                                               (3, 3, 16, 70), (2, 1, 8, 200)])
-def test_attention_prefill_tcgen05(ops, nh, nkv, ps, window):
-    """The same on the fifth-generation tensor cores (head size 64, tiles of up to 128 tokens): a whole prompt of 300
-    tokens, portions in mid-request across boundaries of 64 and 128, two tokens far into a context, a portion that
-    ends exactly at a multiple of 64, and pages of many sizes.  Unused slots of the pages hold 1000."""
+def test_attention_prefill_tcgen05(ops, prefill_kernel, nh, nkv, ps, window):
+    """The same on the fifth-generation tensor cores (head size 64, tiles of up to 128 tokens), both kernels: a whole
+    prompt of 300 tokens, portions in mid-request across boundaries of 64 and 128, two tokens far into a context, a
+    portion that ends exactly at a multiple of 64, and pages of many sizes.  Unused slots of the pages hold 1000."""
     _prefill_case(ops, ops.attention_prefill_tcgen05, 128, nh, nkv, 64, ps, window, [300, 140, 601, 128 + 70, 448], [300, 37, 2, 70, 200])
 
 
 @pytest.mark.parametrize("nh,nkv,ps,window", [(3, 1, 16, 0), (2, 2, 32, 0), (2, 1, 16, 1500)])
-def test_attention_prefill_tcgen05_cuts_long_walks_into_parts(ops, nh, nkv, ps, window):
+def test_attention_prefill_tcgen05_cuts_long_walks_into_parts(ops, prefill_kernel, nh, nkv, ps, window):
     """Tiles whose walk over the keys is longer than 16 steps of 64 are cut into parts that different blocks take and the
     last to arrive adds up: portions at the end of contexts of 2,300 and 4,000 positions (three and four parts), a whole
     prompt of 1,025 tokens (its last tile has one row, whose second part is a single key), a walk of exactly 16 steps, and
-    a window that shortens the walk.  Run twice over the same scratch (the counters return to zero)."""
+    a window that shortens the walk.  Run twice over the same scratch (the counters return to zero).  Both kernels."""
     for _ in range(2):
         _prefill_case(ops, ops.attention_prefill_tcgen05, 128, nh, nkv, 64, ps, window, [2300, 1100, 1025, 4000, 1024], [300, 70, 1025, 2, 128])
+
+
+def test_attention_prefill_tcgen05_takes_the_kernel_by_the_size_of_the_launch(ops):
+    """A launch of 32 heads and 13 tiles (416 blocks: the first kernel) and one of 8 heads (104 blocks: two streams) give
+    the same result as each kernel forced on the same operands, to rounding: the size rule only chooses."""
+    torch.manual_seed(5)
+    hd, ps, T = 64, 16, 13 * 128
+    pages = T // ps + 3
+    for nh, nkv in ((32, 8), (8, 8)):
+        pool = torch.randn(pages, 2, nkv, ps, hd, device="cuda").to(torch.bfloat16)
+        bt = torch.randperm(pages, device="cuda")[: T // ps].to(torch.int32)[None, :].contiguous()
+        q = torch.randn(T, nh * hd, device="cuda").to(torch.bfloat16)
+        tiles = dev(np.asarray([(o, 128, o, 0) for o in range(0, T, 128)], np.int32))
+        outs = []
+        for mode in (2, 0, 1):
+            was = ops.set_prefill_streams(mode)
+            try:
+                out = torch.empty_like(q)
+                ops.attention_prefill_tcgen05(q, pool, bt, tiles, out, nh, nkv, hd, 0.125, 0)
+                torch.cuda.synchronize()
+                ops.check_device_errors()
+                outs.append(out.float())
+            finally:
+                ops.set_prefill_streams(was)
+        scale = float(outs[0].abs().max())
+        assert (outs[0] - outs[1]).abs().max() <= 2e-2 * scale and (outs[0] - outs[2]).abs().max() <= 2e-2 * scale
+        assert torch.equal(outs[0], outs[1] if nh == 32 else outs[2])        # the rule took the kernel this size stands for
 
 
 def test_attention_prefill_tcgen05_refuses_what_it_does_not_take(ops):
@@ -673,9 +708,9 @@ def test_linear_tcgen05_gives_up_a_wait_and_says_so(ops, family, M, N, K, stage)
 
 
 @pytest.mark.parametrize("stage", [0, 2])
-def test_attention_prefill_tcgen05_gives_up_a_wait_and_says_so(ops, stage):
-    """The same for the prompt attention: one step's keys never arrive; the tensor-core lane, the softmax warps and the
-    producer each give up within the limit, keep their appointments, and the block returns."""
+def test_attention_prefill_tcgen05_gives_up_a_wait_and_says_so(ops, prefill_kernel, stage):
+    """The same for the prompt attention, both kernels: one step's keys never arrive; the tensor-core lanes, the softmax
+    warps and the copying warps each give up within the limit, keep their appointments, and the block returns."""
     ops.set_wait_limit_ms(5.0)
     try:
         ops.skip_stage_once("attention_prefill_tcgen05", stage)

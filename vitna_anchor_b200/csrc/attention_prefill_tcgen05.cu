@@ -868,6 +868,22 @@ static bool at_make_map(CUtensorMap* map, const void* base, long long rows, int 
 
 using namespace vk;
 
+// Which of the two kernels a launch takes: 0 the first, 1 the one with two streams, 2 (default) by the size of the launch.
+static int g_prefill_streams_mode = -1;
+static int prefill_streams_mode() {
+    if (g_prefill_streams_mode < 0) {
+        const char* e = getenv("VITNA_ATT_STREAMS");
+        g_prefill_streams_mode = e ? (atoi(e) ? 1 : 0) : 2;
+    }
+    return g_prefill_streams_mode;
+}
+// Returns the mode that was in force.
+VK_API int vk_set_prefill_streams(int mode) {
+    const int was = prefill_streams_mode();
+    if (mode >= 0 && mode <= 2) g_prefill_streams_mode = mode;
+    return was;
+}
+
 // Bytes of scratch for launches of up to cap_tiles tiles whose contexts reach max_context positions: the parts' outputs,
 // their maxima and sums, and the counters, in that order, each 256-byte aligned.
 VK_API size_t vk_attention_prefill_tcgen05_scratch_bytes(int cap_tiles, int nh, int max_context) {
@@ -919,10 +935,10 @@ VK_API int vk_attention_prefill_tcgen05(const void* q, const void* cache, const 
     // 32 heads and 300 to 8,192 tokens: 12.7 against 13.6, 29.6 against 36.5, 32.1 against 43.0, 58.3 against 80.7
     // microseconds); from about two and a half blocks a multiprocessor on, two blocks of the first kernel that share a
     // multiprocessor keep it a little busier (50.0 against 52.0, 63.0 against 65.2, 649 against 692).
-    // VITNA_ATT_STREAMS=0 / 1 in the environment forces one or the other, for measurements.
-    static const int forced_kernel = [] { const char* e = getenv("VITNA_ATT_STREAMS"); return e ? (atoi(e) ? 1 : 0) : -1; }();
+    // VITNA_ATT_STREAMS=0 / 1 in the environment, or vk_set_prefill_streams, forces one or the other (tests, measurements).
+    const int forced_kernel = prefill_streams_mode();
     const long long blocks = (long long)n_tiles * sc.parts * nh;
-    if (forced_kernel == 1 || (forced_kernel < 0 && blocks < 370)) {
+    if (forced_kernel == 1 || (forced_kernel == 2 && blocks < 370)) {
         const size_t smem2 = (size_t)AT_BM * 64 * 2 + 2 * AS_STAGES * AT_BN * 64 * 2 + 4 * AT_BM * AT_BN * 2 + 1024 + 256;
         auto kern2 = attention_prefill_streams_kernel<64>;
         cudaError_t e2 = cudaFuncSetAttribute(kern2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);

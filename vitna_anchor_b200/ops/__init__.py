@@ -561,6 +561,12 @@ def attention_prefill(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: 
     return out
 
 
+def set_prefill_streams(mode: int) -> int:
+    """Which tcgen05 prompt-attention kernel a launch takes: 0 the kernel with two threads a query row, 1 the kernel with
+    two streams of key steps, 2 by the size of the launch (the default).  Returns the mode that was in force."""
+    return int(lib().vk_set_prefill_streams(int(mode)))
+
+
 def attention_prefill_tcgen05_takes(q: torch.Tensor, cache_layer: torch.Tensor, hd: int) -> bool:
     """Whether the tcgen05 prompt-attention kernel takes these operands: bfloat16, head size 64, pages of 8, 16, 32
     or a multiple of 64 slots, q rows dense and 16-byte aligned."""
