@@ -366,7 +366,8 @@ constexpr int TW_BN = TW_BN_V, TW_STAGES = 4, TW_THREADS = 320;      // warps 0 
 
 template <int EPI, int HD = 0>
 __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x,
-                                                                         const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
+                                                                         const __grid_constant__ CUtensorMap map_w,
+                                                                         const __grid_constant__ CUtensorMap map_out, void* __restrict__ out,
                                                                          int M, int N, int K, const WaitCtl wc, const TcExtra ex) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = TW_BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
     extern __shared__ uint8_t smem_raw[];
@@ -455,7 +456,42 @@ __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(cons
             const int b = j & 1;
             const int row = (t % tiles_m) * TC_BM + quarter * 32 + lane, n0 = (t / tiles_m) * tile_cols;
             if (ok && !__all_sync(0xffffffffu, mbar_wait(&acc_full[b], (j >> 1) & 1, wc.cycles))) { if (lane == 0) give_up(wc.error, &failed, 34); ok = false; }
-            if (ok) {
+            // The block's last tile of a residual sum goes out by TMA reductions from shared memory (see the narrow kernel): its
+            // epilogue hides behind no further tile, and every stage is free by now.  The eight epilogue warps meet for it,
+            // so they go on together or not at all.
+            const bool by_tma = EPI == TC_ACC && ex.tma_out && t + (int)gridDim.x >= num_tiles;
+            if (by_tma) {
+                asm volatile("bar.sync 2, 256;" ::: "memory");
+                if (*reinterpret_cast<volatile int*>(&failed)) ok = false;
+            }
+            if (ok && by_tma) {
+                tc_fence_after();
+                const uint32_t acc = lane_base + b * TW_BN;
+                const int r_loc = quarter * 32 + lane;
+#pragma unroll 1
+                for (int c = half * (TW_BN / 2); c < (half + 1) * (TW_BN / 2); c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(acc + c, r);
+                    tmem_loaded(r);
+                    uint8_t* box = smem + (c / 32) * (TC_BM * 128) + r_loc * 128;
+#pragma unroll
+                    for (int q = 0; q < 8; q++)
+                        *reinterpret_cast<uint4*>(box + ((q ^ (r_loc & 7)) << 4)) = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                tc_fence_before();
+                asm volatile("bar.sync 2, 256;" ::: "memory");
+                if (warp == 2 && lane == 0) {
+                    const int m0 = (t % tiles_m) * TC_BM;
+                    for (int c = 0; c < TW_BN; c += 32) {
+                        if (n0 + c < N)
+                            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                                         ::"l"(&map_out), "r"(smem_u32(smem + (c / 32) * (TC_BM * 128))), "r"(n0 + c), "r"(m0) : "memory");
+                    }
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                }
+            } else if (ok) {
                 tc_fence_after();
                 const uint32_t acc = lane_base + b * TW_BN;
                 if (EPI == TC_SWIGLU) {
@@ -688,6 +724,10 @@ static int launch_wide(const CUtensorMap& mx, const CUtensorMap& mw, void* out, 
                        const TcExtra& ex = TcExtra{}) {
     const WaitCtl wc = wait_ctl(error, WAIT_FAMILY_LINEAR_WIDE);
     const size_t smem = (size_t)TW_STAGES * (TC_BM * TC_BK * 2 + TW_BN * TC_BK * 2) + 1024 + 128;
+    TcExtra exx = ex;
+    CUtensorMap mo = mx;                               // (a valid map for the epilogues that do not use it)
+    exx.tma_out = 0;
+    if (EPI == TC_ACC && N % 4 == 0 && ((uintptr_t)out % 16 == 0) && make_out_map(&mo, out, M, N)) exx.tma_out = 1;
     auto kern = linear_tcgen05_wide_kernel<EPI, HD>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -695,7 +735,7 @@ static int launch_wide(const CUtensorMap& mx, const CUtensorMap& mw, void* out, 
     const int cols = EPI == TC_SWIGLU ? ex.inter : N;
     const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((cols + tile_cols - 1) / tile_cols);
     const int grid = tiles < sm_count() ? (int)tiles : sm_count();
-    return launch_plain(kern, dim3(grid), dim3(TW_THREADS), smem, stream, mx, mw, out, M, N, K, wc, ex);
+    return launch_plain(kern, dim3(grid), dim3(TW_THREADS), smem, stream, mx, mw, mo, out, M, N, K, wc, exx);
 }
 
 }  // namespace vk
