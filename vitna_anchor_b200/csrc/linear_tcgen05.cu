@@ -364,12 +364,13 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
 #endif
 constexpr int TW_BN = TW_BN_V, TW_STAGES = 4, TW_THREADS = 320;      // warps 0 and 1 feed and issue; eight warps drain the accumulators
 
-template <int EPI, int HD = 0>
+template <int EPI, int HD = 0, int BNW = TW_BN>
 __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                          const __grid_constant__ CUtensorMap map_w,
                                                                          const __grid_constant__ CUtensorMap map_out, void* __restrict__ out,
                                                                          int M, int N, int K, const WaitCtl wc, const TcExtra ex) {
-    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = TW_BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BNW * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t TM_COLS = 2 * BNW <= 256 ? 256 : 512;      // the two accumulators; tensor memory comes in powers of two
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + TW_STAGES * STAGE_BYTES);
@@ -381,7 +382,7 @@ __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (K + TC_BK - 1) / TC_BK;
-    const int tile_cols = EPI == TC_SWIGLU ? TW_BN / 2 : TW_BN;                // output columns of a tile
+    const int tile_cols = EPI == TC_SWIGLU ? BNW / 2 : BNW;                // output columns of a tile
     const int out_cols = EPI == TC_SWIGLU ? ex.inter : N;
     const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (out_cols + tile_cols - 1) / tile_cols;
     const int num_tiles = tiles_m * tiles_n;      // tile t: rows (t % tiles_m) * 128, columns (t / tiles_m) * tile_cols
@@ -394,7 +395,7 @@ __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(cons
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * TW_BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -425,7 +426,7 @@ __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(cons
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_bf16(TC_BM, TW_BN);
+            const uint32_t idesc = umma_idesc_bf16(TC_BM, BNW);
             const uint32_t a_lo0 = umma_desc_lo(smem_u32(smem));      // low words of the descriptors (see umma_bf16_lo)
             int kc = 0, j = 0;
             bool ok = true;
@@ -439,7 +440,7 @@ __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(cons
                     tc_fence_after();
                     const uint32_t a_lo = a_lo0 + s * (STAGE_BYTES >> 4), b_lo = a_lo + (A_BYTES >> 4);
 #pragma unroll
-                    for (int k = 0; k < TC_BK / 16; k++) umma_bf16_lo(tmem_base + b * TW_BN, a_lo + 2 * k, b_lo + 2 * k, idesc, (kb | k) != 0);
+                    for (int k = 0; k < TC_BK / 16; k++) umma_bf16_lo(tmem_base + b * BNW, a_lo + 2 * k, b_lo + 2 * k, idesc, (kb | k) != 0);
                     umma_commit(&empty[s]);
                 }
                 if (ok) umma_commit(&acc_full[b]);
@@ -466,10 +467,10 @@ __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(cons
             }
             if (ok && by_tma) {
                 tc_fence_after();
-                const uint32_t acc = lane_base + b * TW_BN;
+                const uint32_t acc = lane_base + b * BNW;
                 const int r_loc = quarter * 32 + lane;
 #pragma unroll 1
-                for (int c = half * (TW_BN / 2); c < (half + 1) * (TW_BN / 2); c += 32) {
+                for (int c = half * (BNW / 2); c < (half + 1) * (BNW / 2); c += 32) {
                     uint32_t r[32];
                     tmem_ld32(acc + c, r);
                     tmem_loaded(r);
@@ -483,7 +484,7 @@ __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(cons
                 asm volatile("bar.sync 2, 256;" ::: "memory");
                 if (warp == 2 && lane == 0) {
                     const int m0 = (t % tiles_m) * TC_BM;
-                    for (int c = 0; c < TW_BN; c += 32) {
+                    for (int c = 0; c < BNW; c += 32) {
                         if (n0 + c < N)
                             asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
                                          ::"l"(&map_out), "r"(smem_u32(smem + (c / 32) * (TC_BM * 128))), "r"(n0 + c), "r"(m0) : "memory");
@@ -493,13 +494,16 @@ __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(cons
                 }
             } else if (ok) {
                 tc_fence_after();
-                const uint32_t acc = lane_base + b * TW_BN;
+                const uint32_t acc = lane_base + b * BNW;
                 if (EPI == TC_SWIGLU) {
 #pragma unroll 1
-                    for (int c = half * (TW_BN / 4); c < (half + 1) * (TW_BN / 4); c += 32) {
+                    // the tile's gate columns in chunks of 32: the first of a lane quarter's two warps takes the first half of
+                    // them (rounded up), the second the rest
+                    constexpr int CHUNKS = BNW / 2 / 32, SPLIT = (CHUNKS + 1) / 2;
+                    for (int c = (half == 0 ? 0 : SPLIT) * 32; c < (half == 0 ? SPLIT : CHUNKS) * 32; c += 32) {
                         uint32_t gr[32], ur[32];
                         tmem_ld32_nowait(acc + c, gr);
-                        tmem_ld32_nowait(acc + TW_BN / 2 + c, ur);
+                        tmem_ld32_nowait(acc + BNW / 2 + c, ur);
                         tmem_wait_ld();
                         tmem_loaded(gr);
                         tmem_loaded(ur);
@@ -535,7 +539,7 @@ __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(cons
                     const int sl = row < M ? ex.slot[row] : -1;
                     const int p0 = row < M ? ex.positions[row] : 0;
 #pragma unroll 1
-                    for (int hh = half * (TW_BN / HDX / 2); hh < (half + 1) * (TW_BN / HDX / 2); hh++) {
+                    for (int hh = half * (BNW / HDX / 2); hh < (half + 1) * (BNW / HDX / 2); hh++) {
                         const int head = n0 / HDX + hh;
                         if (head >= ex.nh + 2 * ex.nkv) break;          // the same for the whole warp
                         const bool is_q = head < ex.nh, is_k = !is_q && head < ex.nh + ex.nkv;
@@ -587,7 +591,7 @@ __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(cons
                     }
                 } else {
 #pragma unroll 1
-                    for (int c = half * (TW_BN / 2); c < (half + 1) * (TW_BN / 2); c += 32) {
+                    for (int c = half * (BNW / 2); c < (half + 1) * (BNW / 2); c += 32) {
                         uint32_t r[32];
                         tmem_ld32(acc + c, r);
                         tmem_loaded(r);
@@ -646,7 +650,7 @@ __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(cons
     if (warp == 1) {
         if (failed) __nanosleep(200000);      // after a failed wait: let copies in flight land
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * TW_BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TM_COLS) : "memory");
     }
 }
 
@@ -719,19 +723,19 @@ static bool wide_takes(int M, int out_cols, int K, int tile_cols = TW_BN) {
     return K >= 2048 || tiles * 4 >= (long long)sm_count() * 5;
 }
 
-template <int EPI, int HD = 0>
+template <int EPI, int HD = 0, int BNW = TW_BN>
 static int launch_wide(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int M, int N, int K, int* error, cudaStream_t stream,
                        const TcExtra& ex = TcExtra{}) {
     const WaitCtl wc = wait_ctl(error, WAIT_FAMILY_LINEAR_WIDE);
-    const size_t smem = (size_t)TW_STAGES * (TC_BM * TC_BK * 2 + TW_BN * TC_BK * 2) + 1024 + 128;
+    const size_t smem = (size_t)TW_STAGES * (TC_BM * TC_BK * 2 + BNW * TC_BK * 2) + 1024 + 128;
     TcExtra exx = ex;
     CUtensorMap mo = mx;                               // (a valid map for the epilogues that do not use it)
     exx.tma_out = 0;
     if (EPI == TC_ACC && N % 4 == 0 && ((uintptr_t)out % 16 == 0) && make_out_map(&mo, out, M, N)) exx.tma_out = 1;
-    auto kern = linear_tcgen05_wide_kernel<EPI, HD>;
+    auto kern = linear_tcgen05_wide_kernel<EPI, HD, BNW>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    const int tile_cols = EPI == TC_SWIGLU ? TW_BN / 2 : TW_BN;
+    const int tile_cols = EPI == TC_SWIGLU ? BNW / 2 : BNW;
     const int cols = EPI == TC_SWIGLU ? ex.inter : N;
     const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((cols + tile_cols - 1) / tile_cols);
     const int grid = tiles < sm_count() ? (int)tiles : sm_count();
@@ -785,6 +789,15 @@ VK_API int vk_linear_tcgen05_swiglu(const void* x, const void* w, void* out, int
     TcExtra ex{};
     ex.inter = inter;
     if (wide_takes(M, inter, K, TW_BN / 2)) {
+        // Tiles of 128 x 96 output columns (192 weight rows) where they come out sooner than tiles of 128 x 128: a block
+        // walks through ceil(tiles / blocks) tiles, and at the 135M and 360M sizes the last round of the wider tile is
+        // mostly empty (192 tiles on 148 multiprocessors: two rounds of 256 columns against two of 192).
+        const long long tiles_m = (M + TC_BM - 1) / TC_BM, sms = sm_count();
+        const long long rounds256 = (tiles_m * ((inter + 127) / 128) + sms - 1) / sms, rounds192 = (tiles_m * ((inter + 95) / 96) + sms - 1) / sms;
+        if (rounds192 * 192 < rounds256 * 256) {
+            if (!make_map(&mx, x, M, K, ldx, TC_BM) || !make_map(&mw, w, 2 * inter, K, K, 96)) return VK_BAD_SHAPE;
+            return launch_wide<TC_SWIGLU, 0, 192>(mx, mw, out, M, 2 * inter, K, error, stream, ex);
+        }
         if (!make_map(&mx, x, M, K, ldx, TC_BM) || !make_map(&mw, w, 2 * inter, K, K, TW_BN / 2)) return VK_BAD_SHAPE;
         return launch_wide<TC_SWIGLU>(mx, mw, out, M, 2 * inter, K, error, stream, ex);
     }
