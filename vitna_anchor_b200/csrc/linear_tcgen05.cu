@@ -358,11 +358,10 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
 // epilogue warps drain one tile while the tensor core fills the next.  A 128 x 256 tile reads a quarter fewer bytes
 // a flop from the second-level cache than 128 x 128 (which that traffic bounded at about 60 % of the tensor peak),
 // and N = 256 instructions take the tensor core longer than they take their thread to issue.
-// SwiGLU: a tile is 128 gate rows and the 128 up rows of the same columns.
-#ifndef TW_BN_V
-#define TW_BN_V 256
-#endif
-constexpr int TW_BN = TW_BN_V, TW_STAGES = 4, TW_THREADS = 320;      // warps 0 and 1 feed and issue; eight warps drain the accumulators
+// SwiGLU: a tile is 128 gate rows and the 128 up rows of the same columns.  BNW, the tile's width in weight rows, is a
+// parameter of the kernel: 256, or 192 (96 gate and 96 up rows) where the launcher finds that a block's last round of
+// the wider tile would be mostly empty.
+constexpr int TW_BN = 256, TW_STAGES = 4, TW_THREADS = 320;      // warps 0 and 1 feed and issue; eight warps drain the accumulators
 
 template <int EPI, int HD = 0, int BNW = TW_BN>
 __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x,
