@@ -37,6 +37,7 @@ struct MmaParams {
     void* out;
     int M, N, K, ldx, kc, ks;    // kc: columns staged at a time (a multiple of 32 * ks); ks: warps = splits of K
     int xstride;                 // elements of bfloat16 between two staged rows
+    int xoff;                    // where in a staged row its bfloat16 values begin (elements; not 0: behind the float32 values of the staged norm)
     int tpb;                     // most tiles of eight units a block works through (tile = blockIdx.x + i * gridDim.x)
     int depth;                   // streaming kernel: batches of weights in flight for every lane
     const int32_t* positions;
@@ -299,7 +300,7 @@ __global__ void __launch_bounds__(256, MG <= 4 ? 2 : 1) skinny_mma_kernel(const 
         for (int m = warp; m < MG * 8; m += ks) {
             T* dst = xs + (size_t)m * xstride;
             if (m0 + m >= p.M) {
-                for (int k = lane * 8; k < K; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
+                for (int k = lane * 8; k < K; k += 256) *reinterpret_cast<uint4*>(dst + p.xoff + k) = make_uint4(0, 0, 0, 0);
                 continue;
             }
             const float* xf = reinterpret_cast<const float*>(dst);
@@ -310,6 +311,21 @@ __global__ void __launch_bounds__(256, MG <= 4 ? 2 : 1) skinny_mma_kernel(const 
             }
             ss = warp_sum(ss);
             const float inv = 1.0f / sqrtf(ss / (float)K + p.eps);
+            if (p.xoff) {
+                // the bfloat16 values have a place of their own behind the row's float32 values: one pass, nothing to wait for
+#pragma unroll 4
+                for (int k = lane * 4; k < K; k += 128) {
+                    const float4 xv = *reinterpret_cast<const float4*>(xf + k);
+                    const float4 wv = *reinterpret_cast<const float4*>(nw_s + k);
+                    __nv_bfloat162 lo = __floats2bfloat162_rn((xv.x * inv) * wv.x, (xv.y * inv) * wv.y);
+                    __nv_bfloat162 hi = __floats2bfloat162_rn((xv.z * inv) * wv.z, (xv.w * inv) * wv.w);
+                    uint2 v;
+                    v.x = *reinterpret_cast<uint32_t*>(&lo);
+                    v.y = *reinterpret_cast<uint32_t*>(&hi);
+                    *reinterpret_cast<uint2*>(dst + p.xoff + k) = v;
+                }
+                continue;
+            }
             // 128 columns at a time, upwards: the bfloat16 values of a run never reach float32 values not yet read
             for (int k0 = 0; k0 < K; k0 += 128) {
                 const int k = k0 + lane * 4;
@@ -389,7 +405,7 @@ __global__ void __launch_bounds__(256, MG <= 4 ? 2 : 1) skinny_mma_kernel(const 
                 if (b + i * ks < nblk) {
 #pragma unroll
                     for (int mg = 0; mg < MG; mg++) {
-                        const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)(mg * 8 + g) * xstride + (b + i * ks) * 32 + q * 8);
+                        const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)(mg * 8 + g) * xstride + p.xoff + (b + i * ks) * 32 + q * 8);
                         mma_bf16(d[mg], r[i].x, t[i].x, r[i].y, t[i].y, xv.x, xv.y);
                         mma_bf16(d[mg], r[i].z, t[i].z, r[i].w, t[i].w, xv.z, xv.w);
                     }
@@ -762,8 +778,16 @@ static int launch_mma(MmaParams p, cudaStream_t stream) {
     const int rows = mg * 8;
     int kc = p.K;
     size_t stride_bytes;
+    p.xoff = 0;
     if (NORM) {
         stride_bytes = (size_t)4 * p.K + 64;            // K is a multiple of 32: 4K is a multiple of 128
+        // Rows too long to be normed in registers get, where two blocks still share a multiprocessor, a place of their own
+        // for the bfloat16 values behind the float32 ones (the norm then needs no care about what it overwrites).
+        const size_t wide = (size_t)6 * p.K + ((6 * p.K) % 128 == 64 ? 0 : 64);
+        if (p.K > 640 && rows * wide + (size_t)4 * p.K + (size_t)ks * mg * 32 * 4 * sizeof(float) + 1024 <= 113 * 1024) {
+            stride_bytes = wide;
+            p.xoff = 2 * p.K;
+        }
     } else {
         const int fit = ((163840 / rows - 64) / 2) / (32 * ks) * (32 * ks);
         if (kc > fit) kc = fit;
@@ -840,7 +864,7 @@ VK_API int vk_linear_skinny_mma(const void* x, const int32_t* rows, const float*
             !slot || !cache)
             return VK_BAD_SHAPE;
     }
-    MmaParams p{x, rows, norm_w, eps, (const __nv_bfloat16*)w, out, M, N, K, ldx, 0, 0, 0, 1, 0, positions, cos_t, sin_t, slot,
+    MmaParams p{x, rows, norm_w, eps, (const __nv_bfloat16*)w, out, M, N, K, ldx, 0, 0, 0, 0, 1, 0, positions, cos_t, sin_t, slot,
                 (__nv_bfloat16*)cache, nh, nkv, hd, page_size};
     return norm_w ? mma_dispatch<true>(epi, p, stream) : mma_dispatch<false>(epi, p, stream);
 }
