@@ -460,18 +460,20 @@ __global__ void __launch_bounds__(256, MG <= 4 ? 2 : 1) skinny_mma_kernel(const 
 
 
 // ---------------------------------------------------------------------------------------------------------------
-// The streaming variant, for weights large enough that a block works through several tiles or a long row.
+// The streaming variant, for long rows and for launches in which a block works through several tiles.
 //
-// The kernel above asks for a tile's weights, waits, multiplies, lets the warps' sums meet and only then asks for
-// the next tile: between two tiles a block has nothing on its way.  Measured alone over weights of 67 to 200 MB both
-// stream at 5.4 TB/s once they run (a library reduction reads at 5.9); this one starts and ends a little sooner
-// (4.4 against 7.4 microseconds of fixed time a launch).  Here a lane
+// The kernel above asks for a tile's weights (two batches of a warp's share before the wait on the kernel before it),
+// waits, multiplies, lets the warps' sums meet and only then asks for the next tile: between two tiles a block has
+// nothing on its way, and a row too long for two batches costs a trip to memory after the wait.  Measured alone over
+// weights larger than the second-level cache, this one reads 67 MB (gate and up at the 1.7B sizes, eight rows) in 14.7
+// microseconds (4.6 TB/s) and the 201 MB of that model's output matrix at 5.6 TB/s (a library reduction over 1 GiB
+// reads at 5.9), the kernel above in 19.9 and at 4.5.  Here a lane
 // keeps `depth` batches of its own weights (four runs of 32 columns, two rows: 128 bytes) on their way into a ring in
 // shared memory that only this lane reads back (cp.async; consecutive lanes write consecutive 16 bytes), across
 // tiles and across the meeting of the warps.  One block a multiprocessor; the ring takes what shared memory the
 // staged rows leave.  Which warp adds which run, and in which order, is as above, so the sums are the same bits.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int ST_UN = 4;
+constexpr int ST_UN = 4, ST_ROUND = 4;      // runs of 32 columns in a batch; tiles whose sums a warp keeps before the warps meet
 
 __device__ __forceinline__ void st_wait_pending(int n) {        // until at most n of the lane's latest batches are on their way
     switch (n) {
@@ -498,7 +500,7 @@ __global__ void __launch_bounds__(256, 1) skinny_stream_kernel(const MmaParams p
     T* xs = reinterpret_cast<T*>(smem_raw);
     float* nw_s = reinterpret_cast<float*>(smem_raw + (size_t)MG * 8 * xstride * sizeof(T));
     float* red = nw_s + (NORM ? K : 0);                                        // [ks][MG][32][4]
-    uint4* ring = reinterpret_cast<uint4*>(red + (size_t)ks * MG * 32 * 4);    // [depth][ST_UN][2][nth]
+    uint4* ring = reinterpret_cast<uint4*>(red + (size_t)ks * ST_ROUND * MG * 32 * 4);    // [depth][ST_UN][2][nth]
     const int units = (EPI == ME_SWIGLU) ? p.N / 2 : (p.N + 1) / 2;
     const int total_tiles = (units + 7) / 8;
     const int n_my = (int)blockIdx.x < total_tiles ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
@@ -614,67 +616,84 @@ __global__ void __launch_bounds__(256, 1) skinny_stream_kernel(const MmaParams p
     }
 
     // ---- the side that multiplies -------------------------------------------------------------------------------
+    // ST_ROUND tiles a round: a warp keeps the sums of the round's tiles in registers, and the warps meet once a round
+    // (one pair of barriers for four tiles, and up to four warps finish a tile each) instead of once a tile: with
+    // short rows the meeting was most of a tile's time.
     const bool one_chunk = kc >= K;
     int slot = 0;
-    for (int it = 0; it < n_my; it++) {
-        int u, r0, r1; bool on, has1;
-        tile_rows(it, u, on, r0, r1, has1);
-        float d[MG][4];
+    for (int it0 = 0; it0 < n_my; it0 += ST_ROUND) {
+        float d[ST_ROUND][MG][4];
 #pragma unroll
-        for (int mg = 0; mg < MG; mg++) { d[mg][0] = d[mg][1] = d[mg][2] = d[mg][3] = 0.0f; }
-        for (int kb = 0; kb < K; kb += kc) {
-            const int kn = min(kc, K - kb);
-            if (!NORM && (it == 0 || !one_chunk)) {
-                __syncthreads();                        // the chunk before has been read
-                for (int m = warp; m < MG * 8; m += ks) {
-                    T* dst = xs + (size_t)m * xstride;
-                    if (m0 + m >= p.M) {
-                        for (int k = lane * 8; k < kn; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
-                    } else {
-                        const T* xr = reinterpret_cast<const T*>(p.x) + (size_t)(m0 + m) * p.ldx + kb;
-                        for (int k = lane * 8; k < kn; k += 256) mm_cp_async16(dst + k, xr + k);
-                    }
-                }
-                // the rows came last: the batches of weights asked for before them are here too, and the count of
-                // batches on their way starts again from none
-                asm volatile("cp.async.commit_group;" ::: "memory");
-                asm volatile("cp.async.wait_group 0;" ::: "memory");
-                __syncthreads();
-            }
-            const int nblk = kn / 32;
-            int b = warp;
-            do {
-                st_wait_pending(depth - 1);             // the oldest batch on its way is the one used now
+        for (int tt = 0; tt < ST_ROUND; tt++) {
 #pragma unroll
-                for (int i = 0; i < ST_UN; i++) {
-                    const int bb = b + i * ks;
-                    if (bb < nblk) {
-                        const uint4* src = ring + ((size_t)(slot * ST_UN + i) * 2) * nth + tid;
-                        const uint4 r = src[0], t = src[nth];
+            for (int mg = 0; mg < MG; mg++) { d[tt][mg][0] = d[tt][mg][1] = d[tt][mg][2] = d[tt][mg][3] = 0.0f; }
+        }
 #pragma unroll
-                        for (int mg = 0; mg < MG; mg++) {
-                            const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)(mg * 8 + g) * xstride + bb * 32 + q * 8);
-                            mma_bf16(d[mg], r.x, t.x, r.y, t.y, xv.x, xv.y);
-                            mma_bf16(d[mg], r.z, t.z, r.w, t.w, xv.z, xv.w);
+        for (int tt = 0; tt < ST_ROUND; tt++) {
+            const int it = it0 + tt;
+            if (it >= n_my) break;                      // the same for the whole block
+            for (int kb = 0; kb < K; kb += kc) {
+                const int kn = min(kc, K - kb);
+                if (!NORM && (it == 0 || !one_chunk)) {
+                    __syncthreads();                    // the chunk before has been read
+                    for (int m = warp; m < MG * 8; m += ks) {
+                        T* dst = xs + (size_t)m * xstride;
+                        if (m0 + m >= p.M) {
+                            for (int k = lane * 8; k < kn; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
+                        } else {
+                            const T* xr = reinterpret_cast<const T*>(p.x) + (size_t)(m0 + m) * p.ldx + kb;
+                            for (int k = lane * 8; k < kn; k += 256) mm_cp_async16(dst + k, xr + k);
                         }
                     }
+                    // the rows came last: the batches of weights asked for before them are here too, and the count of
+                    // batches on their way starts again from none
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");
+                    __syncthreads();
                 }
-                ask(slot);                              // the place just read takes the batch `depth` further on
-                slot = slot + 1 == depth ? 0 : slot + 1;
-                b += ST_UN * ks;
-            } while (b < nblk);
-        }
-        // the warps' sums meet, as above
+                const int nblk = kn / 32;
+                int b = warp;
+                do {
+                    st_wait_pending(depth - 1);         // the oldest batch on its way is the one used now
 #pragma unroll
-        for (int mg = 0; mg < MG; mg++)
-            *reinterpret_cast<float4*>(red + (((size_t)warp * MG + mg) * 32 + lane) * 4) = make_float4(d[mg][0], d[mg][1], d[mg][2], d[mg][3]);
+                    for (int i = 0; i < ST_UN; i++) {
+                        const int bb = b + i * ks;
+                        if (bb < nblk) {
+                            const uint4* src = ring + ((size_t)(slot * ST_UN + i) * 2) * nth + tid;
+                            const uint4 r = src[0], t = src[nth];
+#pragma unroll
+                            for (int mg = 0; mg < MG; mg++) {
+                                const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)(mg * 8 + g) * xstride + bb * 32 + q * 8);
+                                mma_bf16(d[tt][mg], r.x, t.x, r.y, t.y, xv.x, xv.y);
+                                mma_bf16(d[tt][mg], r.z, t.z, r.w, t.w, xv.z, xv.w);
+                            }
+                        }
+                    }
+                    ask(slot);                          // the place just read takes the batch `depth` further on
+                    slot = slot + 1 == depth ? 0 : slot + 1;
+                    b += ST_UN * ks;
+                } while (b < nblk);
+            }
+        }
+        // the warps' sums of the round's tiles meet; warp w then finishes the pairs (tile, row group) w, w + ks, ...
+#pragma unroll
+        for (int tt = 0; tt < ST_ROUND; tt++) {
+#pragma unroll
+            for (int mg = 0; mg < MG; mg++)
+                *reinterpret_cast<float4*>(red + ((((size_t)warp * ST_ROUND + tt) * MG + mg) * 32 + lane) * 4) =
+                    make_float4(d[tt][mg][0], d[tt][mg][1], d[tt][mg][2], d[tt][mg][3]);
+        }
         __syncthreads();
-        for (int mg = warp; mg < MG; mg += ks) {
+        for (int idx = warp; idx < ST_ROUND * MG; idx += ks) {
+            const int tt = idx / MG, mg = idx % MG, it = it0 + tt;
+            if (it >= n_my) continue;
             float4 s = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             for (int w = 0; w < ks; w++) {
-                const float4 v = *reinterpret_cast<const float4*>(red + (((size_t)w * MG + mg) * 32 + lane) * 4);
+                const float4 v = *reinterpret_cast<const float4*>(red + ((((size_t)w * ST_ROUND + tt) * MG + mg) * 32 + lane) * 4);
                 s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
             }
+            int u, r0, r1; bool on, has1;
+            tile_rows(it, u, on, r0, r1, has1);
             if (!on) continue;
             const int m = m0 + mg * 8 + 2 * q;
             if (m < p.M) mma_finish<EPI>(p, u, r0, r1, has1, m, s.x, s.z, false, 0, 1.0f, 0.0f, nullptr);
@@ -685,7 +704,7 @@ __global__ void __launch_bounds__(256, 1) skinny_stream_kernel(const MmaParams p
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
-// 0: never the streaming kernel, 1: whenever its sizes fit, 2 (default): large weights with long rows (see launch_stream).
+// 0: never the streaming kernel, 1: whenever its sizes fit, 2 (default): long rows or several tiles a block (see launch_stream).
 static int g_stream_mode = -1;
 static int stream_mode() {
     if (g_stream_mode < 0) {
@@ -704,13 +723,16 @@ static int launch_stream(MmaParams p, int mg, int ks, cudaStream_t stream) {
     const int ychunks = (p.M + 8 * mg - 1) / (8 * mg);
     const int per_chunk = 148 / ychunks > 0 ? 148 / ychunks : 1;
     const int blocks = tiles < per_chunk ? tiles : per_chunk;
-    // Measured inside decode steps: it wins (a tenth of the kernel's time) where the weights are large and the rows long
-    // (the 1.7B sizes); with small weights the kernel above, two blocks a multiprocessor and room beside the kernels
-    // before and after it, is the faster one, and so it is when the batch rows are split over blocks.
-    if (stream_mode() == 2 && !((size_t)p.N * p.K * 2 >= ((size_t)16 << 20) && p.K >= 2048 && ychunks == 1)) return -1;
+    // Measured inside decode steps (batch 8, milliseconds a step with and without): it wins where the rows are long
+    // (K >= 2,048: the kernel above has two batches of a warp's weights on their way before the wait, and a third costs a
+    // trip after it; 360M 1.135 -> 1.029, 1.7B 1.850 -> 1.814) and where a block walks through two tiles or more (the
+    // output matrix).  With short rows and few tiles the kernel above, two blocks a multiprocessor and room beside
+    // the kernels before and after it, is the faster one (135M with K >= 1,024 streamed: 0.659 against 0.645), and so
+    // it is when the batch rows are split over blocks.
+    if (stream_mode() == 2 && !(ychunks == 1 && (p.K >= 2048 || tiles >= 2 * 148))) return -1;
     const int rows = mg * 8, nth = 32 * ks;
     const size_t stage = (size_t)ST_UN * 2 * 16 * nth;                  // a batch of every lane
-    const size_t red = (size_t)ks * mg * 32 * 4 * sizeof(float);
+    const size_t red = (size_t)ks * ST_ROUND * mg * 32 * 4 * sizeof(float);
     const size_t budget = 224 * 1024;
     int kc = p.K;
     size_t stride_bytes, fixed;
