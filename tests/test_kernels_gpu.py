@@ -280,7 +280,10 @@ def test_sampling_proportions(ops):
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("nh,nkv,hd,ps,window", [(4, 2, 16, 4, 0), (3, 1, 32, 8, 0), (9, 3, 64, 16, 0), (6, 2, 48, 16, 0),
                                                  (2, 2, 80, 5, 0), (18, 2, 128, 16, 0), (8, 1, 256, 16, 0), (4, 2, 16, 4, 5),
-                                                 (3, 3, 64, 16, 300), (9, 3, 64, 16, 700)])
+                                                 (3, 3, 64, 16, 300), (9, 3, 64, 16, 700),
+                                                 # groups of 5, 7 and 8 heads: the routine with the keys as rows, its last
+                                                 # pair of heads half used, and full; 12: the one with the heads as rows
+                                                 (10, 2, 64, 16, 0), (7, 1, 32, 16, 0), (16, 2, 64, 8, 300), (12, 1, 64, 16, 0)])
 def test_attention_decode_split_keys(ops, dtype, nh, nkv, hd, ps, window):
     """Single decoded tokens at contexts that end inside the first run of 256 keys, exactly on a run's edge,
     just past it, and far beyond; one key made to stand out in each; listed among tokens that are not run."""

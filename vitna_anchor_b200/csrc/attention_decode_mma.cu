@@ -16,6 +16,11 @@
 //   meet      the eight warps' unnormalised parts are weighted by exp(own maximum - row maximum) and added in
 //             warp order
 //
+// A tile of at most eight heads (every group of this architecture's published sizes) turns the products over: the
+// keys are the 16 rows and the heads the 8 columns, S^T = K Q^T and O^T = V^T P^T, with the probabilities
+// transposed in registers (movmatrix) on their way into the 8-column operand.  Half the products and
+// exponentials; the parts that the warp leaves have the same layout either way.
+//
 // Instantiated for head sizes 16, 32, 64, 96 and 128; attention_decode.cu takes the others and float32.
 #include "common.cuh"
 
@@ -175,6 +180,128 @@ __device__ __forceinline__ void dm_load_q(const DmArgs& a, const DmItem& it, uin
     }
 }
 
+__device__ __forceinline__ uint32_t dm_movmatrix_trans(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+
+// A warp's 32 keys for a tile of AT MOST EIGHT query heads, with the keys (not the heads) as the 16 rows of the products:
+// S^T[16 keys x 8 heads] = K Q^T (the keys' rows come with ldmatrix, the queries straight from global memory as the
+// 8-column operand) and O^T[16 dims x 8 heads] = V^T P^T (V^T by a transposing ldmatrix; the probabilities go from
+// the score registers through movmatrix into the 8-column operand, again as a high and a low bfloat16 part).  Half the
+// products and half the exponentials of the routine with the heads as rows, which wastes thirteen of sixteen rows on
+// a group of three heads.  Leaves the warp's maxima and sums in wml and its unnormalised output [head][HD] in wo.
+template <int HD>
+__device__ __forceinline__ void dm_warp_few_heads(const DmArgs& a, const DmItem& it, const __nv_bfloat16* sk, const __nv_bfloat16* sv,
+                                                  float* wml, float* wo, float scale_log2) {
+    typedef __nv_bfloat16 T;
+    constexpr int LD = HD + 8, KSTEPS = HD / 16, HB = HD / 16;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gq = lane >> 2, qd = lane & 3;
+    const int wk0 = it.k0 + warp * 32, pos = it.pos, lo = it.lo, gt = it.gt;
+    // the queries as the 8-column operand: lane (gq, qd) holds head gq, dims 2qd, 2qd+1 and +8 of each k-step
+    uint32_t qb[KSTEPS][2];
+    {
+        const T* qr = a.q + ((size_t)it.t * a.nh + it.h0 + gq) * HD + 2 * qd;
+        const bool on = gq < gt;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ks++) {
+            qb[ks][0] = on ? *reinterpret_cast<const uint32_t*>(qr + ks * 16) : 0u;
+            qb[ks][1] = on ? *reinterpret_cast<const uint32_t*>(qr + ks * 16 + 8) : 0u;
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+    // ---- scores: two blocks of 16 keys; lane (gq, qd) gets keys gq and gq+8 of a block for heads 2qd, 2qd+1 ----------
+    float s[2][4];
+#pragma unroll
+    for (int kb = 0; kb < 2; kb++) {
+        s[kb][0] = s[kb][1] = s[kb][2] = s[kb][3] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ks++) {
+            uint32_t af[4];
+            dm_ldsm_x4(af[0], af[1], af[2], af[3], sk + (warp * 32 + kb * 16 + (lane & 15)) * LD + ks * 16 + (lane >> 4) * 8);
+            dm_mma(s[kb], af, qb[ks][0], qb[ks][1]);
+        }
+    }
+    const bool edge = wk0 + 31 > pos || wk0 < lo;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int kb = 0; kb < 2; kb++) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            float v = s[kb][e] * scale_log2;
+            if (edge) {
+                const int kk = wk0 + kb * 16 + gq + (e >> 1) * 8;
+                if (!(kk <= pos && kk >= lo)) v = -INFINITY;
+            }
+            s[kb][e] = v;
+            mx[e & 1] = fmaxf(mx[e & 1], v);
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; h++) {                       // over the eight lanes that hold the head's other keys
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 4));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 8));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 16));
+    }
+    float rs[2] = {0.0f, 0.0f};
+    uint32_t ph[2][2], pl[2][2];                        // the 8-column operand of the two blocks of 16 keys, high and low parts
+#pragma unroll
+    for (int kb = 0; kb < 2; kb++) {
+#pragma unroll
+        for (int half = 0; half < 2; half++) {          // keys gq (0) and gq+8 (1) of the block
+            const float p0 = dm_ex2(s[kb][2 * half] - mx[0]), p1 = dm_ex2(s[kb][2 * half + 1] - mx[1]);
+            rs[0] += p0;
+            rs[1] += p1;
+            const __nv_bfloat162 hv = __floats2bfloat162_rn(p0, p1);
+            const uint32_t hi = *reinterpret_cast<const uint32_t*>(&hv);
+            const uint32_t lw = dm_pack(p0 - __bfloat162float(hv.x), p1 - __bfloat162float(hv.y));
+            // [key][heads 2qd, 2qd+1] -> [head][keys 2qd, 2qd+1]: what the 8-column operand wants
+            ph[kb][half] = dm_movmatrix_trans(hi);
+            pl[kb][half] = dm_movmatrix_trans(lw);
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 4);
+        rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 8);
+        rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 16);
+    }
+    if (gq == 0) {
+        *reinterpret_cast<float2*>(wml + (warp * DM_ROWS + 2 * qd) * 2) = make_float2(mx[0], rs[0]);
+        *reinterpret_cast<float2*>(wml + (warp * DM_ROWS + 2 * qd + 1) * 2) = make_float2(mx[1], rs[1]);
+    }
+    // ---- O^T = V^T P^T: blocks of 16 dims; lane (gq, qd) gets dims gq and gq+8 of a block for heads 2qd, 2qd+1 ----------
+    float o[HB][4];
+#pragma unroll
+    for (int hb = 0; hb < HB; hb++) { o[hb][0] = o[hb][1] = o[hb][2] = o[hb][3] = 0.0f; }
+#pragma unroll
+    for (int kb = 0; kb < 2; kb++) {
+#pragma unroll
+        for (int hb = 0; hb < HB; hb++) {
+            uint32_t af[4];
+            dm_ldsm_x4_trans(af[0], af[1], af[2], af[3],
+                             sv + (warp * 32 + kb * 16 + (lane & 7) + ((lane >> 4) << 3)) * LD + hb * 16 + ((lane >> 3) & 1) * 8);
+            dm_mma(o[hb], af, ph[kb][0], ph[kb][1]);
+            dm_mma(o[hb], af, pl[kb][0], pl[kb][1]);
+        }
+    }
+    __syncwarp();                                       // every lane is past its reads of the warp's keys
+#pragma unroll
+    for (int hb = 0; hb < HB; hb++) {
+        const int d = hb * 16 + gq;
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            const int head = 2 * qd + e;
+            if (head < gt) {
+                wo[head * HD + d] = o[hb][e];
+                wo[head * HD + d + 8] = o[hb][2 + e];
+            }
+        }
+    }
+}
+
 // Shared memory of a block: keys [256][HD+8], values [256][HD+8] and the warps' maxima and sums [8][16][2].  A warp's unnormalised output [16][HD] float32 lies over its own 32 keys,
 // dead once it has its scores.  74 KB at HD = 64: three blocks a multiprocessor.
 template <int HD> struct DmSmem {
@@ -217,7 +344,11 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 3 : 1) attention_decode
     let_dependents_start();
 
     float* wo = reinterpret_cast<float*>(sk + warp * 32 * LD);       // [16][HD], over the warp's own keys
-    if (warp_on) {
+    if (warp_on && gt <= 8) {
+        dm_copy_own<HD>(a, it, own_page, sk, sv);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        dm_warp_few_heads<HD>(a, it, sk, sv, wml, wo, scale_log2);
+    } else if (warp_on) {
         dm_copy_own<HD>(a, it, own_page, sk, sv);
         asm volatile("cp.async.commit_group;" ::: "memory");
         uint32_t qf[KSTEPS][4];
