@@ -734,6 +734,9 @@ def test_attention_prefill_tcgen05_gives_up_a_wait_and_says_so(ops, prefill_kern
     (3, 3, 16, 300, [10, 299, 300, 301, 900, 2000]),
     (9, 3, 16, 700, [2048, 1700, 701]),
     (9, 3, 16, 0, [int(n) for n in np.random.default_rng(3).integers(1, 2300, 200)]),     # many more units than warps: the ring runs across units
+    (16, 2, 16, 0, [40, 513, 1100]),                          # groups of 8, 7 and 5 heads: the keys as rows, all eight columns
+    (7, 1, 16, 200, [64, 450, 1800]),                         # in use, and the last pair of heads half used
+    (10, 2, 32, 0, [33, 700, 2049]),
 ])
 def test_attention_decode_tma_streams_the_pages(ops, nh, nkv, ps, window, lens):
     """The persistent decode kernel (TMA boxes from the pages, a warp a unit, online softmax over chunks of 32 keys),
@@ -784,9 +787,13 @@ def test_attention_decode_tma_streams_the_pages(ops, nh, nkv, ps, window, lens):
     scale = max(1.0, float(np.abs(want).max()))
     outs = {}
     before = ops.set_decode_tma(1)
+    few_before = ops.set_decode_tma_few(1)
     try:
-        for mode in (1, 0, 1):            # the streaming kernel, the separate kernel, the streaming kernel again on the same scratch
-            ops.set_decode_tma(mode)
+        # the streaming kernel (keys as rows for groups of at most eight), the separate kernel, the streaming kernel again on
+        # the same scratch, and the streaming kernel with the heads as rows for every group
+        for mode in (1, 0, 1, 3):
+            ops.set_decode_tma(min(mode, 1))
+            ops.set_decode_tma_few(0 if mode == 3 else 1)
             out = torch.full((T, nh * hd), 5.0, dtype=dtype, device="cuda")
             reach = -(-max(lens) // 256) * 256
             ops.attention_decode(*args, out, scratch, T, nh, nkv, hd, 1.0 / math.sqrt(hd), max_ctx, reach if mode else max_ctx, window)
@@ -798,7 +805,9 @@ def test_attention_decode_tma_streams_the_pages(ops, nh, nkv, ps, window, lens):
             outs.setdefault(mode, got)
     finally:
         ops.set_decode_tma(before)
+        ops.set_decode_tma_few(few_before)
     assert np.abs(outs[1] - outs[0]).max() <= 1e-2 * scale
+    assert np.abs(outs[3] - outs[0]).max() <= 1e-2 * scale
 
 
 def _rope_oracle(x, w, positions, cos, sin, slots, nh, nkv, hd, ps, pages):

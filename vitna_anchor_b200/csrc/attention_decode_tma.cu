@@ -22,6 +22,9 @@
 // keys are masked only in chunks that touch the position or the window's edge, and the running output is rescaled
 // only when a chunk raises a row's maximum.
 //
+// Launches whose head groups have at most eight heads take the kernel's FEW form, which halves that arithmetic again:
+// the chunk's keys are the 16 rows of the products and the heads the 8 columns.
+//
 // The separate launch-per-unit kernel leaves the memory pipe idle while a block sets up, meets and counts; here the
 // copies never stop.  Chosen for head size 64 and launches with at least half as many units as the grid has
 // warps; smaller launches keep the kernel that puts eight warps on one unit.
@@ -74,6 +77,11 @@ __device__ __forceinline__ float dt_ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ uint32_t dt_movmatrix_trans(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t dt_pack(float x, float y) {
     __nv_bfloat162 v = __floats2bfloat162_rn(x, y);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -81,10 +89,16 @@ __device__ __forceinline__ uint32_t dt_pack(float x, float y) {
 // Row r (a key of the chunk), 16-byte piece j of a 128-byte row, as TMA's 128-byte swizzle lays it down.
 __device__ __forceinline__ uint32_t dt_sw(uint32_t base, int row, int piece) { return base + row * 128 + ((piece ^ (row & 7)) << 4); }
 
+// FEW: every tile has at most eight heads (a group of at most eight), and the products are turned over as in
+// attention_decode_mma.cu: the chunk's keys are the 16 rows and the heads the 8 columns, S^T = K Q^T and O^T = V^T P^T,
+// the probabilities transposed in registers (movmatrix) on their way into the 8-column operand.  Half the products
+// and exponentials of a chunk, and half the registers for the queries and the running output.
+template <bool FEW>
 __global__ void __launch_bounds__(DT_THREADS, 1) attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const DtArgs a,
                                                                              const WaitCtl wc) {
     typedef __nv_bfloat16 T;
     constexpr int HD = DT_HD, KSTEPS = HD / 16, DBLK = HD / 8;
+    constexpr int QR = FEW ? 2 : 4, OB = FEW ? HD / 16 : HD / 8;      // registers of a k-step's queries; blocks of the running output
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DT_WARPS * DT_STAGES * DT_STAGE_BYTES);      // [warps][stages]
@@ -177,16 +191,22 @@ __global__ void __launch_bounds__(DT_THREADS, 1) attention_decode_tma_kernel(con
         return pg0 + lane <= pg_end ? it.bt[pg0 + lane] : 0;
     };
     // The queries of the unit's heads as the 16-row operand: lane (gq, qd) holds rows gq and gq+8.
-    auto load_q = [&](const DtUnit& it, uint32_t (*qf)[4]) {
+    // (FEW: as the 8-column operand, lane (gq, qd) holds head gq, dims 2qd, 2qd+1 and +8 of each k-step.)
+    auto load_q = [&](const DtUnit& it, uint32_t (*qf)[QR]) {
         const T* r0 = a.q + ((size_t)it.t * a.nh + it.h0 + gq) * HD + 2 * qd;
         const T* r1 = r0 + (size_t)8 * HD;
         const bool on0 = gq < it.gt, on1 = gq + 8 < it.gt;
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ks++) {
-            qf[ks][0] = on0 ? *reinterpret_cast<const uint32_t*>(r0 + ks * 16) : 0u;
-            qf[ks][1] = on1 ? *reinterpret_cast<const uint32_t*>(r1 + ks * 16) : 0u;
-            qf[ks][2] = on0 ? *reinterpret_cast<const uint32_t*>(r0 + ks * 16 + 8) : 0u;
-            qf[ks][3] = on1 ? *reinterpret_cast<const uint32_t*>(r1 + ks * 16 + 8) : 0u;
+            if constexpr (FEW) {
+                qf[ks][0] = on0 ? *reinterpret_cast<const uint32_t*>(r0 + ks * 16) : 0u;
+                qf[ks][1] = on0 ? *reinterpret_cast<const uint32_t*>(r0 + ks * 16 + 8) : 0u;
+            } else {
+                qf[ks][0] = on0 ? *reinterpret_cast<const uint32_t*>(r0 + ks * 16) : 0u;
+                qf[ks][1] = on1 ? *reinterpret_cast<const uint32_t*>(r1 + ks * 16) : 0u;
+                qf[ks][2] = on0 ? *reinterpret_cast<const uint32_t*>(r0 + ks * 16 + 8) : 0u;
+                qf[ks][3] = on1 ? *reinterpret_cast<const uint32_t*>(r1 + ks * 16 + 8) : 0u;
+            }
         }
     };
 
@@ -195,7 +215,7 @@ __global__ void __launch_bounds__(DT_THREADS, 1) attention_decode_tma_kernel(con
     int iu = my_first;                          // unit being issued, and its next chunk
     DtUnit iunit = have ? unit_of(iu) : DtUnit{};
     int ic = iunit.c0;
-    uint32_t qn[KSTEPS][4];                     // the queries of the unit the issuing cursor has reached
+    uint32_t qn[KSTEPS][QR];                    // the queries of the unit the issuing cursor has reached
     int issued = 0, consumed = 0;               // chunks so far: stage = count % DT_STAGES, parity = (count / DT_STAGES) & 1
     int cu = my_first;                          // unit being consumed
     bool ok = true;
@@ -231,17 +251,20 @@ __global__ void __launch_bounds__(DT_THREADS, 1) attention_decode_tma_kernel(con
 
     while (cu < n_units && ok) {
         const DtUnit it = cu == iu && !ipending ? iunit : unit_of(cu);
-        uint32_t qf[KSTEPS][4];
+        uint32_t qf[KSTEPS][QR];
         if (cu == iu && !ipending) {
 #pragma unroll
-            for (int ks = 0; ks < KSTEPS; ks++) { qf[ks][0] = qn[ks][0]; qf[ks][1] = qn[ks][1]; qf[ks][2] = qn[ks][2]; qf[ks][3] = qn[ks][3]; }
+            for (int ks = 0; ks < KSTEPS; ks++) {
+#pragma unroll
+                for (int r = 0; r < QR; r++) qf[ks][r] = qn[ks][r];
+            }
         } else {
             load_q(it, qf);                     // the issuing cursor is past this unit: its queries are gone from qn
         }
         float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
-        float o[DBLK][4];
+        float o[OB][4];
 #pragma unroll
-        for (int db = 0; db < DBLK; db++) { o[db][0] = o[db][1] = o[db][2] = o[db][3] = 0.0f; }
+        for (int db = 0; db < OB; db++) { o[db][0] = o[db][1] = o[db][2] = o[db][3] = 0.0f; }
 
         for (int c = it.c0; c <= it.c1 && ok; c++) {
             // keep the ring full
@@ -278,80 +301,152 @@ __global__ void __launch_bounds__(DT_THREADS, 1) attention_decode_tma_kernel(con
                 __syncwarp();
             }
 
-            // ---- scores of the chunk's 32 keys: four blocks of 8 keys ----------------------------------------------
-            float sc[4][4];
-#pragma unroll
-            for (int nb = 0; nb < 4; nb++) { sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.0f; }
-#pragma unroll
-            for (int ks = 0; ks < KSTEPS; ks++) {
-#pragma unroll
-                for (int nb2 = 0; nb2 < 2; nb2++) {
-                    uint32_t b0, b1, b2, b3;
-                    dt_ldsm_x4(b0, b1, b2, b3, dt_sw(kbase, nb2 * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
-                    dt_mma(sc[nb2 * 2], qf[ks], b0, b1);
-                    dt_mma(sc[nb2 * 2 + 1], qf[ks], b2, b3);
-                }
-            }
-            // scale (base 2) and, in a chunk that touches the position or the window's edge, mask; rows gq and gq+8
-            // (heads), keys kc0 + nb*8 + 2*qd + {0,1}
-            float mx[2] = {-INFINITY, -INFINITY};
             const bool edge = kc0 + DT_CHUNK - 1 > it.pos || kc0 < it.lo;
+            if constexpr (FEW) {
+                // ---- scores: two blocks of 16 keys; lane (gq, qd) gets keys gq and gq+8 of a block for heads 2qd, 2qd+1 ----
+                float sc[2][4];
 #pragma unroll
-            for (int nb = 0; nb < 4; nb++) {
+                for (int kb = 0; kb < 2; kb++) {
+                    sc[kb][0] = sc[kb][1] = sc[kb][2] = sc[kb][3] = 0.0f;
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    float v = sc[nb][e] * scale_log2;
-                    if (edge) {
-                        const int kk = kc0 + nb * 8 + qd * 2 + (e & 1);
-                        if (!(kk <= it.pos && kk >= it.lo)) v = -INFINITY;
+                    for (int ks = 0; ks < KSTEPS; ks++) {
+                        uint32_t af[4];
+                        dt_ldsm_x4(af[0], af[1], af[2], af[3], dt_sw(kbase, kb * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+                        dt_mma(sc[kb], af, qf[ks][0], qf[ks][1]);
                     }
-                    sc[nb][e] = v;
-                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
                 }
-            }
+                float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int r = 0; r < 2; r++) {           // finite: the chunk has at least one key that every row counts
-                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            }
-            if (__any_sync(0xffffffffu, mx[0] > m_run[0] || mx[1] > m_run[1])) {
-                // a row's maximum rises (always in the unit's first chunk): what has been summed so far is rescaled
-                float alpha[2];
+                for (int kb = 0; kb < 2; kb++) {
 #pragma unroll
-                for (int r = 0; r < 2; r++) {
-                    const float m_new = fmaxf(m_run[r], mx[r]);
-                    alpha[r] = dt_ex2(m_run[r] - m_new);        // 0 for the unit's first chunk
-                    m_run[r] = m_new;
-                    l_run[r] *= alpha[r];
+                    for (int e = 0; e < 4; e++) {
+                        float v = sc[kb][e] * scale_log2;
+                        if (edge) {
+                            const int kk = kc0 + kb * 16 + gq + (e >> 1) * 8;
+                            if (!(kk <= it.pos && kk >= it.lo)) v = -INFINITY;
+                        }
+                        sc[kb][e] = v;
+                        mx[e & 1] = fmaxf(mx[e & 1], v);
+                    }
                 }
 #pragma unroll
-                for (int db = 0; db < DBLK; db++) { o[db][0] *= alpha[0]; o[db][1] *= alpha[0]; o[db][2] *= alpha[1]; o[db][3] *= alpha[1]; }
-            }
-            uint32_t ph[2][4], pl[2][4];            // the 16-row operand of the two k-steps of 16 keys, high and low parts
+                for (int h = 0; h < 2; h++) {           // over the eight lanes that hold the head's other keys; finite as below
+                    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 4));
+                    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 8));
+                    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 16));
+                }
+                if (__any_sync(0xffffffffu, mx[0] > m_run[0] || mx[1] > m_run[1])) {
+                    float alpha[2];
 #pragma unroll
-            for (int nb = 0; nb < 4; nb++) {
-                const float p0 = dt_ex2(sc[nb][0] - m_run[0]), p1 = dt_ex2(sc[nb][1] - m_run[0]);
-                const float p2 = dt_ex2(sc[nb][2] - m_run[1]), p3 = dt_ex2(sc[nb][3] - m_run[1]);
-                l_run[0] += p0 + p1;                // this lane's share of the row's sum; the quad meets at the unit's end
-                l_run[1] += p2 + p3;
-                const __nv_bfloat162 h01 = __floats2bfloat162_rn(p0, p1), h23 = __floats2bfloat162_rn(p2, p3);
-                const int kk = nb >> 1, hi = (nb & 1) * 2;
-                ph[kk][hi] = *reinterpret_cast<const uint32_t*>(&h01);
-                ph[kk][hi + 1] = *reinterpret_cast<const uint32_t*>(&h23);
-                pl[kk][hi] = dt_pack(p0 - __bfloat162float(h01.x), p1 - __bfloat162float(h01.y));
-                pl[kk][hi + 1] = dt_pack(p2 - __bfloat162float(h23.x), p3 - __bfloat162float(h23.y));
-            }
-            // ---- p * v over the chunk's keys, all head dimensions --------------------------------------------------
+                    for (int h = 0; h < 2; h++) {
+                        const float m_new = fmaxf(m_run[h], mx[h]);
+                        alpha[h] = dt_ex2(m_run[h] - m_new);        // 0 for the unit's first chunk
+                        m_run[h] = m_new;
+                        l_run[h] *= alpha[h];
+                    }
 #pragma unroll
-            for (int kk = 0; kk < 2; kk++) {
+                    for (int hb = 0; hb < OB; hb++) { o[hb][0] *= alpha[0]; o[hb][1] *= alpha[1]; o[hb][2] *= alpha[0]; o[hb][3] *= alpha[1]; }
+                }
+                uint32_t ph[2][2], pl[2][2];            // the 8-column operand of the two blocks of 16 keys, high and low parts
 #pragma unroll
-                for (int db = 0; db < DBLK; db += 2) {
-                    uint32_t b0, b1, b2, b3;
-                    dt_ldsm_x4_trans(b0, b1, b2, b3, dt_sw(vbase, kk * 16 + (lane & 15), db + (lane >> 4)));
-                    dt_mma(o[db], ph[kk], b0, b1);
-                    dt_mma(o[db], pl[kk], b0, b1);
-                    dt_mma(o[db + 1], ph[kk], b2, b3);
-                    dt_mma(o[db + 1], pl[kk], b2, b3);
+                for (int kb = 0; kb < 2; kb++) {
+#pragma unroll
+                    for (int half = 0; half < 2; half++) {      // keys gq (0) and gq+8 (1) of the block
+                        const float p0 = dt_ex2(sc[kb][2 * half] - m_run[0]), p1 = dt_ex2(sc[kb][2 * half + 1] - m_run[1]);
+                        l_run[0] += p0;                 // this lane's share of the heads' sums; the lanes meet at the unit's end
+                        l_run[1] += p1;
+                        const __nv_bfloat162 hv = __floats2bfloat162_rn(p0, p1);
+                        // [key][heads 2qd, 2qd+1] -> [head][keys 2qd, 2qd+1]: what the 8-column operand wants
+                        ph[kb][half] = dt_movmatrix_trans(*reinterpret_cast<const uint32_t*>(&hv));
+                        pl[kb][half] = dt_movmatrix_trans(dt_pack(p0 - __bfloat162float(hv.x), p1 - __bfloat162float(hv.y)));
+                    }
+                }
+                // ---- O^T += V^T P^T: blocks of 16 dims; lane (gq, qd) gets dims gq and gq+8 of a block for heads 2qd, 2qd+1 ----
+#pragma unroll
+                for (int kb = 0; kb < 2; kb++) {
+#pragma unroll
+                    for (int hb = 0; hb < OB; hb++) {
+                        uint32_t af[4];
+                        dt_ldsm_x4_trans(af[0], af[1], af[2], af[3], dt_sw(vbase, kb * 16 + (lane & 7) + ((lane >> 4) << 3), hb * 2 + ((lane >> 3) & 1)));
+                        dt_mma(o[hb], af, ph[kb][0], ph[kb][1]);
+                        dt_mma(o[hb], af, pl[kb][0], pl[kb][1]);
+                    }
+                }
+            } else {
+                // ---- scores of the chunk's 32 keys: four blocks of 8 keys ----------------------------------------------
+                float sc[4][4];
+#pragma unroll
+                for (int nb = 0; nb < 4; nb++) { sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.0f; }
+#pragma unroll
+                for (int ks = 0; ks < KSTEPS; ks++) {
+#pragma unroll
+                    for (int nb2 = 0; nb2 < 2; nb2++) {
+                        uint32_t b0, b1, b2, b3;
+                        dt_ldsm_x4(b0, b1, b2, b3, dt_sw(kbase, nb2 * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
+                        dt_mma(sc[nb2 * 2], qf[ks], b0, b1);
+                        dt_mma(sc[nb2 * 2 + 1], qf[ks], b2, b3);
+                    }
+                }
+                // scale (base 2) and, in a chunk that touches the position or the window's edge, mask; rows gq and gq+8
+                // (heads), keys kc0 + nb*8 + 2*qd + {0,1}
+                float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int nb = 0; nb < 4; nb++) {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        float v = sc[nb][e] * scale_log2;
+                        if (edge) {
+                            const int kk = kc0 + nb * 8 + qd * 2 + (e & 1);
+                            if (!(kk <= it.pos && kk >= it.lo)) v = -INFINITY;
+                        }
+                        sc[nb][e] = v;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < 2; r++) {           // finite: the chunk has at least one key that every row counts
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                }
+                if (__any_sync(0xffffffffu, mx[0] > m_run[0] || mx[1] > m_run[1])) {
+                    // a row's maximum rises (always in the unit's first chunk): what has been summed so far is rescaled
+                    float alpha[2];
+#pragma unroll
+                    for (int r = 0; r < 2; r++) {
+                        const float m_new = fmaxf(m_run[r], mx[r]);
+                        alpha[r] = dt_ex2(m_run[r] - m_new);        // 0 for the unit's first chunk
+                        m_run[r] = m_new;
+                        l_run[r] *= alpha[r];
+                    }
+#pragma unroll
+                    for (int db = 0; db < DBLK; db++) { o[db][0] *= alpha[0]; o[db][1] *= alpha[0]; o[db][2] *= alpha[1]; o[db][3] *= alpha[1]; }
+                }
+                uint32_t ph[2][4], pl[2][4];            // the 16-row operand of the two k-steps of 16 keys, high and low parts
+#pragma unroll
+                for (int nb = 0; nb < 4; nb++) {
+                    const float p0 = dt_ex2(sc[nb][0] - m_run[0]), p1 = dt_ex2(sc[nb][1] - m_run[0]);
+                    const float p2 = dt_ex2(sc[nb][2] - m_run[1]), p3 = dt_ex2(sc[nb][3] - m_run[1]);
+                    l_run[0] += p0 + p1;                // this lane's share of the row's sum; the quad meets at the unit's end
+                    l_run[1] += p2 + p3;
+                    const __nv_bfloat162 h01 = __floats2bfloat162_rn(p0, p1), h23 = __floats2bfloat162_rn(p2, p3);
+                    const int kk = nb >> 1, hi = (nb & 1) * 2;
+                    ph[kk][hi] = *reinterpret_cast<const uint32_t*>(&h01);
+                    ph[kk][hi + 1] = *reinterpret_cast<const uint32_t*>(&h23);
+                    pl[kk][hi] = dt_pack(p0 - __bfloat162float(h01.x), p1 - __bfloat162float(h01.y));
+                    pl[kk][hi + 1] = dt_pack(p2 - __bfloat162float(h23.x), p3 - __bfloat162float(h23.y));
+                }
+                // ---- p * v over the chunk's keys, all head dimensions --------------------------------------------------
+#pragma unroll
+                for (int kk = 0; kk < 2; kk++) {
+#pragma unroll
+                    for (int db = 0; db < DBLK; db += 2) {
+                        uint32_t b0, b1, b2, b3;
+                        dt_ldsm_x4_trans(b0, b1, b2, b3, dt_sw(vbase, kk * 16 + (lane & 15), db + (lane >> 4)));
+                        dt_mma(o[db], ph[kk], b0, b1);
+                        dt_mma(o[db], pl[kk], b0, b1);
+                        dt_mma(o[db + 1], ph[kk], b2, b3);
+                        dt_mma(o[db + 1], pl[kk], b2, b3);
+                    }
                 }
             }
             __syncwarp();                           // every lane is past its reads of the stage
@@ -360,29 +455,62 @@ __global__ void __launch_bounds__(DT_THREADS, 1) attention_decode_tma_kernel(con
         if (!ok) break;
 
         // ---- the unit's partial (or, for a single split, the result) --------------------------------------------
-        float l[2];
-#pragma unroll
-        for (int r = 0; r < 2; r++) {
-            l[r] = l_run[r] + __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-        }
         const bool single = it.n_active == 1;
+        if constexpr (FEW) {
+            float l[2];
 #pragma unroll
-        for (int e = 0; e < 2; e++) {
-            const int row = gq + 8 * e;
-            if (row >= it.gt) continue;
-            if (single) {
-                const float inv = 1.0f / l[e];
-                T* dst = a.out + ((size_t)it.t * a.nh + it.h0 + row) * HD + qd * 2;
+            for (int h = 0; h < 2; h++) {
+                l[h] = l_run[h] + __shfl_xor_sync(0xffffffffu, l_run[h], 4);
+                l[h] += __shfl_xor_sync(0xffffffffu, l[h], 8);
+                l[h] += __shfl_xor_sync(0xffffffffu, l[h], 16);
+            }
 #pragma unroll
-                for (int db = 0; db < DBLK; db++)
-                    *reinterpret_cast<uint32_t*>(dst + db * 8) = dt_pack(o[db][2 * e] * inv, o[db][2 * e + 1] * inv);
-            } else {
-                const size_t slot = ((size_t)it.zi * a.nh + it.h0 + row) * a.max_splits + it.split;
-                float* dst = a.part_o + slot * HD + qd * 2;
+            for (int e = 0; e < 2; e++) {               // head 2qd + e: this lane has its dims gq and gq+8 of every block of 16
+                const int row = 2 * qd + e;
+                if (row >= it.gt) continue;
+                if (single) {
+                    const float inv = 1.0f / l[e];
+                    T* dst = a.out + ((size_t)it.t * a.nh + it.h0 + row) * HD + gq;
 #pragma unroll
-                for (int db = 0; db < DBLK; db++) *reinterpret_cast<float2*>(dst + db * 8) = make_float2(o[db][2 * e], o[db][2 * e + 1]);
-                if (qd == 0) *reinterpret_cast<float2*>(a.part_ml + slot * 2) = make_float2(m_run[e], l[e]);
+                    for (int hb = 0; hb < OB; hb++) {
+                        dst[hb * 16] = __float2bfloat16_rn(o[hb][e] * inv);
+                        dst[hb * 16 + 8] = __float2bfloat16_rn(o[hb][2 + e] * inv);
+                    }
+                } else {
+                    const size_t slot = ((size_t)it.zi * a.nh + it.h0 + row) * a.max_splits + it.split;
+                    float* dst = a.part_o + slot * HD + gq;
+#pragma unroll
+                    for (int hb = 0; hb < OB; hb++) {
+                        dst[hb * 16] = o[hb][e];
+                        dst[hb * 16 + 8] = o[hb][2 + e];
+                    }
+                    if (gq == 0) *reinterpret_cast<float2*>(a.part_ml + slot * 2) = make_float2(m_run[e], l[e]);
+                }
+            }
+        } else {
+            float l[2];
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                l[r] = l_run[r] + __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+                l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+            }
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int row = gq + 8 * e;
+                if (row >= it.gt) continue;
+                if (single) {
+                    const float inv = 1.0f / l[e];
+                    T* dst = a.out + ((size_t)it.t * a.nh + it.h0 + row) * HD + qd * 2;
+#pragma unroll
+                    for (int db = 0; db < DBLK; db++)
+                        *reinterpret_cast<uint32_t*>(dst + db * 8) = dt_pack(o[db][2 * e] * inv, o[db][2 * e + 1] * inv);
+                } else {
+                    const size_t slot = ((size_t)it.zi * a.nh + it.h0 + row) * a.max_splits + it.split;
+                    float* dst = a.part_o + slot * HD + qd * 2;
+#pragma unroll
+                    for (int db = 0; db < DBLK; db++) *reinterpret_cast<float2*>(dst + db * 8) = make_float2(o[db][2 * e], o[db][2 * e + 1]);
+                    if (qd == 0) *reinterpret_cast<float2*>(a.part_ml + slot * 2) = make_float2(m_run[e], l[e]);
+                }
             }
         }
         if (!single) {
@@ -464,6 +592,18 @@ static int decode_tma_mode() {
     return g_decode_tma_mode;
 }
 
+// Whether launches whose head groups have at most eight heads take the kernel with the keys as rows (1, the default) or
+// the one with the heads as rows (0).  VITNA_DECODE_TMA_FEW=0 in the environment, or vk_set_decode_tma_few.
+static int g_decode_tma_few = -1;
+
+static int decode_tma_few() {
+    if (g_decode_tma_few < 0) {
+        const char* e = getenv("VITNA_DECODE_TMA_FEW");
+        g_decode_tma_few = e && e[0] == '0' ? 0 : 1;
+    }
+    return g_decode_tma_few;
+}
+
 // Whether this kernel takes the launch, and is the better choice for it: head size 64, pages of 8, 16 or a multiple of 32
 // slots, and at least half as many units (at most: the grid's splits may not all be in use) as the grid has warps.
 bool decode_tma_takes(int n_tokens, int nh, int nkv, int hd, int page_size, int pages, int grid_splits, const void* q, const void* cache,
@@ -486,7 +626,8 @@ int launch_decode_tma(const void* q, const void* cache, const int32_t* bt, const
     DtArgs a{(const __nv_bfloat16*)q, bt, token_seg, positions, tok_list, (__nv_bfloat16*)out, part_o, part_ml, counters,
              n_tokens, nh, nkv, page_size, max_blocks, splits, grid_splits, counter_tiles, scale, window};
     const size_t smem = (size_t)DT_WARPS * DT_STAGES * DT_STAGE_BYTES + DT_WARPS * DT_STAGES * 8 + (DT_MAX_TOKENS + 1) * 4 + 1024;
-    auto kern = attention_decode_tma_kernel;
+    const bool few = nh / nkv <= 8 && decode_tma_few() == 1;
+    auto kern = few ? attention_decode_tma_kernel<true> : attention_decode_tma_kernel<false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     int sms = 148, dev = 0;
@@ -502,6 +643,13 @@ int launch_decode_tma(const void* q, const void* cache, const int32_t* bt, const
 
 // Which launches the persistent TMA kernel takes: 0 none, 1 all whose sizes it takes, 2 those the size rule gives it
 // (the default).  Returns the mode that was in force.
+// Whether head groups of at most eight take the routine with the keys as rows (1) or the general one (0).  Returns what was in force.
+VK_API int vk_set_decode_tma_few(int mode) {
+    const int before = vk::decode_tma_few();
+    if (mode == 0 || mode == 1) vk::g_decode_tma_few = mode;
+    return before;
+}
+
 VK_API int vk_set_decode_tma(int mode) {
     const int before = vk::decode_tma_mode();
     if (mode >= 0 && mode <= 2) vk::g_decode_tma_mode = mode;

@@ -251,6 +251,13 @@ def set_decode_tma(mode: int) -> int:
     return int(lib().vk_set_decode_tma(int(mode)))
 
 
+def set_decode_tma_few(mode: int) -> int:
+    """Whether the persistent TMA decode attention takes head groups of at most eight with the keys as the rows of its
+    products (1, the default; VITNA_DECODE_TMA_FEW=0 sets the other at start) or with the heads as rows (0), as it takes
+    larger groups.  Returns what was in force."""
+    return int(lib().vk_set_decode_tma_few(int(mode)))
+
+
 def set_skinny_stream(mode: int) -> int:
     """Which few-rows products the streaming tensor-core kernel takes: 0 none, 1 all whose sizes it takes, 2 those its
     size rule gives it (the default; VITNA_SKINNY_STREAM sets the initial mode).  Returns the mode that was in force."""
